@@ -1,0 +1,656 @@
+// ar_device.cuh — device side of the collective library (sm_100a).
+//
+// One stream-ordered kernel per collective.  A rank pushes its data into its
+// peers' slot memory with plain 16-byte stores over NVLink, publishes a per-channel
+// sequence flag with system-scope release semantics, waits (bounded) for the same
+// flag from every peer, and reduces the N copies in rank order 0..N-1 in fp32 with
+// one final rounding, so every rank produces identical bits.
+//
+// This replaces, in one launch, the reference's k_copy_sig + RDMA write + stream
+// wait-value + k_acc sequence (step4/libtbvcoll.cpp:126-166, 181-204, 456-503) and
+// its diagnostic kernels k_waitflag / k_tagchk / k_mark (:143-161): the wait, the
+// tag check and the breadcrumbs live inside the collective kernel.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "tbvcoll.h"
+
+namespace tbv {
+
+constexpr int kTraceN = 1024;  // per-call timing ring entries (power of two)
+
+// Device-resident per-rank state.  The sequence number lives here (not in launch
+// parameters) so that a captured CUDA graph replays correctly.
+struct DevState {
+  unsigned long long seq;   // last completed collective on this rank
+  unsigned int arrive;      // CTA completion counter of the running kernel
+  unsigned int err;         // sticky: first device-side error code
+  unsigned int tag_bad;     // seq-stamp mismatches seen (debug mode)
+  unsigned int pad;
+};
+
+struct TraceRec {
+  unsigned long long seq, t_enter, t_ready, t_done;
+  unsigned long long nbytes;
+  unsigned int algo, nchan;
+};
+
+// Host-mapped mirror written by kernels, read by the host without a sync.
+struct HostMirror {
+  unsigned int err;       // same code as DevState::err
+  unsigned int where;     // wait site that gave up (kWhere*)
+  unsigned int peer;      // rank that did not arrive
+  unsigned int chan;
+  unsigned long long err_seq;
+  unsigned long long bc[8];  // breadcrumbs: 0 enter, 1 pushed, 2 wait-pass, 3 done (seq values)
+  unsigned long long tag_bad;
+  TraceRec ring[kTraceN];
+};
+
+enum : unsigned { kErrNone = 0, kErrTimeout = 1, kErrTag = 2 };
+enum : unsigned { kWherePhase0 = 1, kWherePhase1 = 2, kWhereFused = 3 };
+
+// Everything a kernel needs to talk to the other ranks; passed by value.
+struct RankCtx {
+  int rank, world, nslot, debug_tag;
+  unsigned long long cap;          // bytes per (slot, source-rank) region
+  unsigned long long slot_stride;  // bytes per slot = (world + 1) * cap
+  unsigned long long wdog_ns;      // bound on every device-side wait
+  char* data[TBV_MAXRANK];         // data[p]: rank p's slot memory as mapped here
+  unsigned int* flags[TBV_MAXRANK];
+  char* mc_data;                   // multicast (NVLS) mapping of the slot memory, or null
+  DevState* st;
+  HostMirror* hm;
+};
+
+__device__ __forceinline__ size_t flag_index(const RankCtx& c, int slot, int phase, int src,
+                                             int chan) {
+  return ((size_t(slot) * 2 + phase) * c.world + src) * TBV_MAXCHAN + chan;
+}
+__device__ __forceinline__ char* slot_region(const RankCtx& c, int peer, int slot, int region) {
+  return c.data[peer] + size_t(slot) * c.slot_stride + size_t(region) * c.cap;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_sys() {
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+}
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void report_error(const RankCtx& c, unsigned code, unsigned where,
+                                             int peer, int chan, unsigned long long seq) {
+  if (atomicCAS(&c.st->err, 0u, code) == 0u) {
+    c.hm->where = where;
+    c.hm->peer = unsigned(peer);
+    c.hm->chan = unsigned(chan);
+    c.hm->err_seq = seq;
+    __threadfence_system();
+    c.hm->err = code;
+    __threadfence_system();
+  }
+}
+
+// Bounded wait for `*f` to reach `want` (wrap-safe).  A few thousand fast polls,
+// then timed polls with a short sleep.  On expiry: record the error and return
+// false; the caller carries on so that the kernel always terminates.
+__device__ __forceinline__ bool wait_flag(const RankCtx& c, const unsigned* f, unsigned want,
+                                          unsigned where, int peer, int chan,
+                                          unsigned long long seq) {
+  unsigned spins = 0;
+  unsigned long long t0 = 0;
+  while (int(ld_acquire_sys(f) - want) < 0) {
+    if (++spins > 4096u) {
+      unsigned long long now = globaltimer();
+      if (t0 == 0) {
+        t0 = now;
+        // A sticky error from an earlier call means the peer is gone: do not
+        // spend the whole watchdog period again.
+        if (*(volatile unsigned*)&c.st->err != 0u) return false;
+      } else if (now - t0 > c.wdog_ns) {
+        report_error(c, kErrTimeout, where, peer, chan, seq);
+        return false;
+      }
+      __nanosleep(128);
+    }
+  }
+  return true;
+}
+
+// ---- element packs ---------------------------------------------------------------
+template <typename T> struct Pack;  // 16 bytes of T <-> fp32 lanes
+template <> struct Pack<float> {
+  static constexpr int N = 4;
+  __device__ static void unpack(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+  }
+  __device__ static uint4 pack(const float* f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
+                      __float_as_uint(f[3]));
+  }
+  __device__ static float to_f(float x) { return x; }
+  __device__ static float from_f(float x) { return x; }
+};
+template <> struct Pack<__half> {
+  static constexpr int N = 8;
+  __device__ static void unpack(const uint4& v, float* f) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) { float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+  }
+  __device__ static uint4 pack(const float* f) {
+    uint4 v; __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+  }
+  __device__ static float to_f(__half x) { return __half2float(x); }
+  __device__ static __half from_f(float x) { return __float2half_rn(x); }
+};
+template <> struct Pack<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void unpack(const uint4& v, float* f) {
+    // bf16 -> fp32 is a 16-bit shift
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+  }
+  __device__ static uint4 pack(const float* f) {
+    uint4 v; __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+  }
+  __device__ static float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+  __device__ static __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+};
+
+// ---- per-kernel prologue / epilogue ------------------------------------------------
+struct CallInfo {
+  unsigned long long seq;
+  unsigned want;  // low 32 bits of seq: the flag value of this call
+  int slot;
+};
+
+// Every CTA reads the device sequence; the kernel that ran before this one on the
+// stream left it at "last completed".
+__device__ __forceinline__ CallInfo call_begin(const RankCtx& c, unsigned long long* sh_seq) {
+  if (threadIdx.x == 0) *sh_seq = *(volatile unsigned long long*)&c.st->seq + 1ull;
+  __syncthreads();
+  CallInfo ci;
+  ci.seq = *sh_seq;
+  ci.want = unsigned(ci.seq);
+  ci.slot = int(ci.seq % (unsigned long long)c.nslot);
+  return ci;
+}
+
+// Last CTA to finish publishes the new sequence and the timing record.
+__device__ __forceinline__ void call_end(const RankCtx& c, const CallInfo& ci, unsigned nctas,
+                                         unsigned long long t_enter, unsigned long long t_ready,
+                                         unsigned long long nbytes, unsigned algo) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    unsigned old = atomicAdd(&c.st->arrive, 1u);
+    if (old == nctas - 1) {
+      c.st->arrive = 0;
+      TraceRec* r = &c.hm->ring[ci.seq & (kTraceN - 1)];
+      r->t_enter = t_enter; r->t_ready = t_ready; r->t_done = globaltimer();
+      r->nbytes = nbytes; r->algo = algo; r->nchan = nctas;
+      r->seq = ci.seq;
+      c.hm->bc[3] = ci.seq;
+      __threadfence();
+      *(volatile unsigned long long*)&c.st->seq = ci.seq;
+    }
+  }
+}
+
+// publish: all threads' stores are done (caller did __syncthreads); thread 0 fences
+// at system scope once and then stores the flag to every peer.
+__device__ __forceinline__ void publish(const RankCtx& c, const CallInfo& ci, int phase, int chan) {
+  if (threadIdx.x == 0) {
+    fence_sys();
+    for (int p = 0; p < c.world; p++) {
+      if (p == c.rank) continue;
+      st_relaxed_sys(c.flags[p] + flag_index(c, ci.slot, phase, c.rank, chan), ci.want);
+    }
+  }
+}
+// threads 0..world-1 each wait for one source rank; then the CTA synchronises.
+__device__ __forceinline__ void wait_all(const RankCtx& c, const CallInfo& ci, int phase, int chan,
+                                         unsigned where) {
+  if (threadIdx.x < unsigned(c.world) && int(threadIdx.x) != c.rank) {
+    wait_flag(c, c.flags[c.rank] + flag_index(c, ci.slot, phase, threadIdx.x, chan), ci.want,
+              where, threadIdx.x, chan, ci.seq);
+  }
+  __syncthreads();
+}
+
+// ---- one-shot all-reduce ------------------------------------------------------------
+// VEC: 16-byte units (pointers 16-byte aligned, nbytes % 16 == 0); otherwise one
+// element per unit.
+template <typename T, bool VEC>
+__device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* out, size_t nbytes,
+                                int nchan, int chan, unsigned long long* sh_seq) {
+  unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
+  CallInfo ci = call_begin(c, sh_seq);
+  const size_t unit_bytes = VEC ? 16 : sizeof(T);
+  const size_t units = nbytes / unit_bytes;
+  const size_t per = (units + nchan - 1) / nchan;
+  const size_t u0 = per * chan;
+  const size_t u1 = (u0 + per < units) ? (u0 + per) : units;
+  if (chan == 0 && threadIdx.x == 0) c.hm->bc[0] = ci.seq;
+
+  // push my range to every peer's [slot][src = me] region
+  for (size_t u = u0 + threadIdx.x; u < u1; u += blockDim.x) {
+    if (VEC) {
+      uint4 v = reinterpret_cast<const uint4*>(in)[u];
+      for (int p = 0; p < c.world; p++)
+        if (p != c.rank) reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, c.rank))[u] = v;
+    } else {
+      T v = in[u];
+      for (int p = 0; p < c.world; p++)
+        if (p != c.rank) reinterpret_cast<T*>(slot_region(c, p, ci.slot, c.rank))[u] = v;
+    }
+  }
+  if (c.debug_tag && chan == 0 && threadIdx.x == 0) {
+    // seq stamp behind the payload (debug): the receiver checks it after the flag
+    for (int p = 0; p < c.world; p++)
+      if (p != c.rank)
+        *reinterpret_cast<unsigned long long*>(slot_region(c, p, ci.slot, c.rank) + c.cap - 8) = ci.seq;
+  }
+  __syncthreads();
+  publish(c, ci, 0, chan);
+  if (chan == 0 && threadIdx.x == 0) c.hm->bc[1] = ci.seq;
+  wait_all(c, ci, 0, chan, kWherePhase0);
+  unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
+  if (chan == 0 && threadIdx.x == 0) {
+    c.hm->bc[2] = ci.seq;
+    if (c.debug_tag) {
+      for (int p = 0; p < c.world; p++) {
+        if (p == c.rank) continue;
+        unsigned long long tag = *reinterpret_cast<volatile unsigned long long*>(
+            slot_region(c, c.rank, ci.slot, p) + c.cap - 8);
+        if (tag != ci.seq) { atomicAdd(&c.st->tag_bad, 1u); c.hm->tag_bad += 1; }
+      }
+    }
+  }
+
+  // reduce in rank order, fp32, one rounding
+  for (size_t u = u0 + threadIdx.x; u < u1; u += blockDim.x) {
+    if (VEC) {
+      float acc[Pack<T>::N];
+#pragma unroll
+      for (int i = 0; i < Pack<T>::N; i++) acc[i] = 0.f;
+      uint4 mine = reinterpret_cast<const uint4*>(in)[u];
+      for (int r = 0; r < c.world; r++) {
+        uint4 v = (r == c.rank)
+                      ? mine
+                      : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, ci.slot, r)) + u);
+        float f[Pack<T>::N];
+        Pack<T>::unpack(v, f);
+#pragma unroll
+        for (int i = 0; i < Pack<T>::N; i++) acc[i] = (r == 0) ? f[i] : acc[i] + f[i];
+      }
+      reinterpret_cast<uint4*>(out)[u] = Pack<T>::pack(acc);
+    } else {
+      float acc = 0.f;
+      for (int r = 0; r < c.world; r++) {
+        float f = (r == c.rank)
+                      ? Pack<T>::to_f(in[u])
+                      : Pack<T>::to_f(*(reinterpret_cast<volatile const T*>(slot_region(c, c.rank, ci.slot, r)) + u));
+        acc = (r == 0) ? f : acc + f;
+      }
+      out[u] = Pack<T>::from_f(acc);
+    }
+  }
+  call_end(c, ci, nchan, t_enter, t_ready, nbytes, TBV_ALGO_ONESHOT);
+}
+
+// ---- two-shot all-reduce (reduce-scatter + all-gather over peer stores) --------------
+// Rank r owns chunk r.  Phase 0: every rank pushes chunk p of its input to rank p.
+// Rank r reduces chunk r (rank order, fp32, one rounding) — a single reducer per
+// element, so all ranks end with identical bits by construction — and pushes the
+// result into every peer's result region.  Phase 1: copy the gathered result out.
+// mode: 0 = all-reduce, 1 = reduce-scatter only (out holds chunk `rank`),
+//       2 = all-gather only (in holds this rank's chunk).
+template <typename T, bool VEC>
+__device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* out, size_t nbytes,
+                                int nchan, int chan, int mode, unsigned long long* sh_seq) {
+  unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
+  CallInfo ci = call_begin(c, sh_seq);
+  const size_t unit_bytes = VEC ? 16 : sizeof(T);
+  const size_t units = nbytes / unit_bytes;              // whole (gathered) tensor
+  const size_t cu = (units + c.world - 1) / c.world;     // units per rank chunk
+  const size_t per = (cu + nchan - 1) / nchan;           // units per channel inside a chunk
+  const int W = c.world, me = c.rank;
+  if (chan == 0 && threadIdx.x == 0) c.hm->bc[0] = ci.seq;
+  const int R = W;  // index of the result region inside a slot
+  unsigned long long t_ready = 0;
+
+  auto chunk_len = [&](int r) -> size_t {
+    size_t b = cu * r;
+    return b >= units ? 0 : ((units - b < cu) ? units - b : cu);
+  };
+  auto sub_begin = [&](size_t len) -> size_t { size_t b = per * chan; return b < len ? b : len; };
+  auto sub_end = [&](size_t len) -> size_t { size_t e = per * chan + per; return e < len ? e : len; };
+
+  if (mode != 2) {
+    // phase 0 push: chunk p of my input -> rank p, region [src = me], chunk-relative offsets
+    for (int d = 1; d < W; d++) {
+      int p = (me + d) % W;
+      size_t len = chunk_len(p), b = sub_begin(len), e = sub_end(len);
+      for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) {
+        if (VEC) reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, me))[i] =
+                     reinterpret_cast<const uint4*>(in)[cu * p + i];
+        else reinterpret_cast<T*>(slot_region(c, p, ci.slot, me))[i] = in[cu * p + i];
+      }
+    }
+    __syncthreads();
+    publish(c, ci, 0, chan);
+    if (chan == 0 && threadIdx.x == 0) c.hm->bc[1] = ci.seq;
+    wait_all(c, ci, 0, chan, kWherePhase0);
+    if (threadIdx.x == 0 && chan == 0) { t_ready = globaltimer(); c.hm->bc[2] = ci.seq; }
+  }
+
+  {
+    // reduce my chunk; write it out and (all-reduce) push it to every peer's result region
+    size_t len = chunk_len(me), b = sub_begin(len), e = sub_end(len);
+    for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) {
+      if (VEC) {
+        uint4 res;
+        if (mode == 2) {
+          res = reinterpret_cast<const uint4*>(in)[i];
+        } else {
+          float acc[Pack<T>::N];
+#pragma unroll
+          for (int k = 0; k < Pack<T>::N; k++) acc[k] = 0.f;
+          for (int r = 0; r < W; r++) {
+            uint4 v = (r == me) ? reinterpret_cast<const uint4*>(in)[cu * me + i]
+                                : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, me, ci.slot, r)) + i);
+            float f[Pack<T>::N];
+            Pack<T>::unpack(v, f);
+#pragma unroll
+            for (int k = 0; k < Pack<T>::N; k++) acc[k] = (r == 0) ? f[k] : acc[k] + f[k];
+          }
+          res = Pack<T>::pack(acc);
+        }
+        if (mode == 1) {
+          reinterpret_cast<uint4*>(out)[i] = res;
+        } else {
+          reinterpret_cast<uint4*>(out)[cu * me + i] = res;
+          for (int d = 1; d < W; d++) {
+            int p = (me + d) % W;
+            reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, R))[cu * me + i] = res;
+          }
+        }
+      } else {
+        T res;
+        if (mode == 2) {
+          res = in[i];
+        } else {
+          float acc = 0.f;
+          for (int r = 0; r < W; r++) {
+            float f = (r == me) ? Pack<T>::to_f(in[cu * me + i])
+                                : Pack<T>::to_f(*(reinterpret_cast<volatile const T*>(slot_region(c, me, ci.slot, r)) + i));
+            acc = (r == 0) ? f : acc + f;
+          }
+          res = Pack<T>::from_f(acc);
+        }
+        if (mode == 1) {
+          out[i] = res;
+        } else {
+          out[cu * me + i] = res;
+          for (int d = 1; d < W; d++) {
+            int p = (me + d) % W;
+            reinterpret_cast<T*>(slot_region(c, p, ci.slot, R))[cu * me + i] = res;
+          }
+        }
+      }
+    }
+  }
+
+  if (mode != 1) {
+    __syncthreads();
+    publish(c, ci, 1, chan);
+    wait_all(c, ci, 1, chan, kWherePhase1);
+    if (mode == 2 && threadIdx.x == 0 && chan == 0) t_ready = globaltimer();
+    // copy the peers' reduced chunks from my result region to the output
+    for (int d = 1; d < W; d++) {
+      int p = (me + d) % W;
+      size_t len = chunk_len(p), b = sub_begin(len), e = sub_end(len);
+      for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) {
+        if (VEC) reinterpret_cast<uint4*>(out)[cu * p + i] =
+                     ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, me, ci.slot, R)) + cu * p + i);
+        else out[cu * p + i] = *(reinterpret_cast<volatile const T*>(slot_region(c, me, ci.slot, R)) + cu * p + i);
+      }
+    }
+  }
+  call_end(c, ci, nchan, t_enter, t_ready, nbytes, TBV_ALGO_TWOSHOT);
+}
+
+// ---- NVLS all-reduce (multimem through the NVSwitch) -----------------------------------
+// Stage the input in this rank's own slot memory (same offset on every rank), flag,
+// wait for all; rank r then reduces chunk r with one multimem.ld_reduce per 16 bytes
+// (the switch reads all N copies and adds them, fp32 accumulate for 16-bit types) and
+// broadcasts it with multimem.st into every rank's result region.  A single reduction
+// per element: all ranks get identical bits.  16-byte units only.
+template <typename T> struct Multimem;
+template <> struct Multimem<float> {
+  __device__ static uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+};
+template <> struct Multimem<__half> {
+  __device__ static uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+};
+template <> struct Multimem<__nv_bfloat16> {
+  __device__ static uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+};
+__device__ __forceinline__ void multimem_st_v4(void* p, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+template <typename T>
+__device__ void ar_nvls_body(const RankCtx& c, const T* __restrict__ in, T* out, size_t nbytes,
+                             int nchan, int chan, unsigned long long* sh_seq) {
+  unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
+  CallInfo ci = call_begin(c, sh_seq);
+  const size_t units = nbytes / 16;
+  const size_t cu = (units + c.world - 1) / c.world;
+  const size_t per = (cu + nchan - 1) / nchan;
+  const int W = c.world, me = c.rank;
+  const int R = W;
+  if (chan == 0 && threadIdx.x == 0) c.hm->bc[0] = ci.seq;
+  // stage: region 0 of my own slot memory; channel `chan` stages its sub-range of EVERY chunk
+  uint4* stage = reinterpret_cast<uint4*>(slot_region(c, me, ci.slot, 0));
+  for (int r = 0; r < W; r++) {
+    size_t base = cu * r;
+    size_t len = base >= units ? 0 : ((units - base < cu) ? units - base : cu);
+    size_t b = per * chan; if (b > len) b = len;
+    size_t e = per * chan + per; if (e > len) e = len;
+    for (size_t i = b + threadIdx.x; i < e; i += blockDim.x)
+      stage[base + i] = reinterpret_cast<const uint4*>(in)[base + i];
+  }
+  __syncthreads();
+  publish(c, ci, 0, chan);
+  if (chan == 0 && threadIdx.x == 0) c.hm->bc[1] = ci.seq;
+  wait_all(c, ci, 0, chan, kWherePhase0);
+  unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
+  {
+    size_t base = cu * me;
+    size_t len = base >= units ? 0 : ((units - base < cu) ? units - base : cu);
+    size_t b = per * chan; if (b > len) b = len;
+    size_t e = per * chan + per; if (e > len) e = len;
+    const char* mc_stage = c.mc_data + size_t(ci.slot) * c.slot_stride;
+    char* mc_res = c.mc_data + size_t(ci.slot) * c.slot_stride + size_t(R) * c.cap;
+    for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) {
+      uint4 v = Multimem<T>::ld_reduce(mc_stage + (base + i) * 16);
+      multimem_st_v4(mc_res + (base + i) * 16, v);
+    }
+  }
+  __syncthreads();
+  publish(c, ci, 1, chan);
+  wait_all(c, ci, 1, chan, kWherePhase1);
+  const uint4* res = reinterpret_cast<const uint4*>(slot_region(c, me, ci.slot, R));
+  for (int r = 0; r < W; r++) {
+    size_t base = cu * r;
+    size_t len = base >= units ? 0 : ((units - base < cu) ? units - base : cu);
+    size_t b = per * chan; if (b > len) b = len;
+    size_t e = per * chan + per; if (e > len) e = len;
+    for (size_t i = b + threadIdx.x; i < e; i += blockDim.x)
+      reinterpret_cast<uint4*>(out)[base + i] = ld_volatile_v4(res + base + i);
+  }
+  call_end(c, ci, nchan, t_enter, t_ready, nbytes, TBV_ALGO_NVLS);
+}
+
+// ---- RMSNorm row math shared by the fused collective and the plain op -------------------
+// The thread mapping and the reduction tree are the same wherever this is used, so a
+// fused and an unfused pipeline produce the same bits.
+// Semantics (HF Llama): var = mean(h^2) in fp32 over bf16-rounded h; y = bf16(h * rsqrt(var + eps));
+// out = bf16(gamma * y).
+constexpr int kNormMaxUnits = 4;  // 16-byte units per thread: hidden <= 8 * 4 * 1024
+
+__device__ __forceinline__ float block_sum_fixed(float v, float* sh /* >= 32 floats */) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();  // protect sh from the previous use
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; i++) t += sh[i];  // every thread adds in the same order
+  return t;
+}
+
+// h: this thread's values of one row (units u = threadIdx.x + k*blockDim.x), already
+// rounded to bf16 precision.  Writes the normalised row.
+__device__ __forceinline__ void rmsnorm_row_store(const float (*h)[8], int nunits_row, int hidden,
+                                                  float eps, const uint4* __restrict__ gamma,
+                                                  uint4* y_row, float* sh) {
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < kNormMaxUnits; k++) {
+    int u = threadIdx.x + k * blockDim.x;
+    if (u < nunits_row) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) ss += h[k][i] * h[k][i];
+    }
+  }
+  float tot = block_sum_fixed(ss, sh);
+  float rs = rsqrtf(tot / float(hidden) + eps);
+#pragma unroll
+  for (int k = 0; k < kNormMaxUnits; k++) {
+    int u = threadIdx.x + k * blockDim.x;
+    if (u < nunits_row) {
+      float g[8], o[8];
+      Pack<__nv_bfloat16>::unpack(gamma[u], g);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        float n = __bfloat162float(__float2bfloat16_rn(h[k][i] * rs));
+        o[i] = g[i] * n;
+      }
+      y_row[u] = Pack<__nv_bfloat16>::pack(o);
+    }
+  }
+}
+
+// ---- fused all-reduce + residual add + RMSNorm (one-shot, bf16) ---------------------------
+// Channel c owns rows c, c + nchan, ...  It pushes those rows, flags once, waits once,
+// then for each row: s = bf16(sum in rank order); h = bf16(s + residual);
+// residual_out = h; y = RMSNorm(h) * gamma.
+__device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __restrict__ x,
+                                       const __nv_bfloat16* residual,
+                                       const __nv_bfloat16* __restrict__ gamma,
+                                       __nv_bfloat16* residual_out, __nv_bfloat16* y, int tokens,
+                                       int hidden, float eps, int nchan, int chan,
+                                       unsigned long long* sh_seq, float* sh_red) {
+  unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
+  CallInfo ci = call_begin(c, sh_seq);
+  const int upr = hidden / 8;  // 16-byte units per row
+  if (chan == 0 && threadIdx.x == 0) c.hm->bc[0] = ci.seq;
+  for (int row = chan; row < tokens; row += nchan) {
+    const uint4* src = reinterpret_cast<const uint4*>(x) + size_t(row) * upr;
+    for (int u = threadIdx.x; u < upr; u += blockDim.x) {
+      uint4 v = src[u];
+      for (int p = 0; p < c.world; p++)
+        if (p != c.rank)
+          reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, c.rank))[size_t(row) * upr + u] = v;
+    }
+  }
+  __syncthreads();
+  publish(c, ci, 0, chan);
+  if (chan == 0 && threadIdx.x == 0) c.hm->bc[1] = ci.seq;
+  wait_all(c, ci, 0, chan, kWhereFused);
+  unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
+  for (int row = chan; row < tokens; row += nchan) {
+    float h[kNormMaxUnits][8];
+#pragma unroll
+    for (int k = 0; k < kNormMaxUnits; k++) {
+      int u = threadIdx.x + k * blockDim.x;
+      if (u < upr) {
+        size_t off = size_t(row) * upr + u;
+        float acc[8];
+        uint4 mine = reinterpret_cast<const uint4*>(x)[off];
+        for (int r = 0; r < c.world; r++) {
+          uint4 v = (r == c.rank) ? mine
+                                  : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, ci.slot, r)) + off);
+          float f[8];
+          Pack<__nv_bfloat16>::unpack(v, f);
+#pragma unroll
+          for (int i = 0; i < 8; i++) acc[i] = (r == 0) ? f[i] : acc[i] + f[i];
+        }
+        float res[8];
+        Pack<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(residual)[off], res);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          float s = __bfloat162float(__float2bfloat16_rn(acc[i]));
+          h[k][i] = __bfloat162float(__float2bfloat16_rn(s + res[i]));
+        }
+        reinterpret_cast<uint4*>(residual_out)[off] = Pack<__nv_bfloat16>::pack(h[k]);
+      }
+    }
+    rmsnorm_row_store(h, upr, hidden, eps, reinterpret_cast<const uint4*>(gamma),
+                      reinterpret_cast<uint4*>(y) + size_t(row) * upr, sh_red);
+  }
+  call_end(c, ci, nchan, t_enter, t_ready, size_t(tokens) * hidden * 2, TBV_ALGO_ONESHOT);
+}
+
+}  // namespace tbv
