@@ -21,6 +21,7 @@
 #include <mutex>
 
 #include "comm.h"
+#include "ops/ops.h"
 
 using namespace tbv;
 
@@ -158,29 +159,29 @@ struct LocalPtrs {
 };
 
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(1024) k_ar_oneshot(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
+__global__ void __launch_bounds__(512) k_ar_oneshot(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
   __shared__ unsigned long long sh_seq;
   ar_oneshot_body<T, VEC>(c, in, out, nbytes, gridDim.x, blockIdx.x, &sh_seq);
 }
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(1024) k_ar_oneshot_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p, size_t nbytes) {
+__global__ void __launch_bounds__(512) k_ar_oneshot_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p, size_t nbytes) {
   __shared__ unsigned long long sh_seq;
   ar_oneshot_body<T, VEC>(ctxs[blockIdx.y], static_cast<const T*>(p.in[blockIdx.y]), static_cast<T*>(p.out[blockIdx.y]),
                           nbytes, gridDim.x, blockIdx.x, &sh_seq);
 }
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(1024) k_ar_twoshot(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes, int mode) {
+__global__ void __launch_bounds__(512) k_ar_twoshot(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes, int mode) {
   __shared__ unsigned long long sh_seq;
   ar_twoshot_body<T, VEC>(c, in, out, nbytes, gridDim.x, blockIdx.x, mode, &sh_seq);
 }
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(1024) k_ar_twoshot_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p, size_t nbytes, int mode) {
+__global__ void __launch_bounds__(512) k_ar_twoshot_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p, size_t nbytes, int mode) {
   __shared__ unsigned long long sh_seq;
   ar_twoshot_body<T, VEC>(ctxs[blockIdx.y], static_cast<const T*>(p.in[blockIdx.y]), static_cast<T*>(p.out[blockIdx.y]),
                           nbytes, gridDim.x, blockIdx.x, mode, &sh_seq);
 }
 template <typename T>
-__global__ void __launch_bounds__(1024) k_ar_nvls(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
+__global__ void __launch_bounds__(512) k_ar_nvls(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
   __shared__ unsigned long long sh_seq;
   ar_nvls_body<T>(c, in, out, nbytes, gridDim.x, blockIdx.x, &sh_seq);
 }
@@ -669,9 +670,7 @@ static int gpu_ar_rmsnorm(tbv_comm* c, const void* const* xs, const void* const*
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   note_stream(c, stream);
   const int upr = hidden / 8;
-  int threads = std::min(1024, (upr + 31) / 32 * 32);
-  if (upr > 1024) threads = ((upr + kNormMaxUnits - 1) / kNormMaxUnits + 31) / 32 * 32;
-  if (upr >= 512 && upr <= 1024 && (upr % 64) == 0) threads = upr / 2 >= 256 ? upr / 2 : upr;  // 2 units/thread: fewer, fatter threads
+  const int threads = tbvops::norm_threads(hidden);  // same mapping as the plain norm op: identical bits
   int maxchan = c->local ? std::max(1, std::min(TBV_MAXCHAN, c->sm_count / c->world)) : TBV_MAXCHAN;
   int nchan = std::min(tokens, c->knobs.nchan > 0 ? std::min(c->knobs.nchan, maxchan) : maxchan);
   cudaError_t e;

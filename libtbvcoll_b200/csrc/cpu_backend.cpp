@@ -16,7 +16,7 @@
 namespace tbv {
 
 // ---- scalar conversions -----------------------------------------------------------
-float bf16_to_f32(uint16_t h) {
+float bf16_to_f32(uint16_t h) {  // small enough to inline in the loops below
   uint32_t u = uint32_t(h) << 16;
   float f;
   memcpy(&f, &u, 4);
@@ -270,13 +270,28 @@ void CpuBackend::execute(const CpuItem& it) {
       const char* mine = static_cast<const char*>(it.in);
       if (it.op == kOpReduceScatter) mine += size_t(rank_) * it.nbytes;
       // rank order 0..N-1 in fp32, one rounding: identical bits on every rank
-      for (size_t i = 0; i < n; i++) {
-        float acc = 0.f;
-        for (int r = 0; r < world_; r++) {
-          float f = load_elem(r == rank_ ? mine : region(rank_, slot, r), i, it.dtype);
-          acc = (r == 0) ? f : acc + f;
+      const void* srcs[TBV_MAXRANK];
+      for (int r = 0; r < world_; r++) srcs[r] = (r == rank_) ? static_cast<const void*>(mine) : region(rank_, slot, r);
+      if (it.dtype == TBV_F32) {
+        float* o = static_cast<float*>(it.out);
+        for (size_t i = 0; i < n; i++) {
+          float acc = static_cast<const float*>(srcs[0])[i];
+          for (int r = 1; r < world_; r++) acc += static_cast<const float*>(srcs[r])[i];
+          o[i] = acc;
         }
-        store_elem(it.out, i, it.dtype, acc);
+      } else if (it.dtype == TBV_BF16) {
+        uint16_t* o = static_cast<uint16_t*>(it.out);
+        for (size_t i = 0; i < n; i++) {
+          float acc = bf16_to_f32(static_cast<const uint16_t*>(srcs[0])[i]);
+          for (int r = 1; r < world_; r++) acc += bf16_to_f32(static_cast<const uint16_t*>(srcs[r])[i]);
+          o[i] = f32_to_bf16(acc);
+        }
+      } else {
+        for (size_t i = 0; i < n; i++) {
+          float acc = load_elem(srcs[0], i, it.dtype);
+          for (int r = 1; r < world_; r++) acc += load_elem(srcs[r], i, it.dtype);
+          store_elem(it.out, i, it.dtype, acc);
+        }
       }
     }
   }

@@ -1,0 +1,331 @@
+// gemm.cu — bf16 GEMM on tcgen05 tensor cores (TMA-fed, TMEM accumulators) with fused
+// epilogues, and its host-side launcher (tensor-map cache, tile/split heuristics).
+//
+// The reference has no GEMM of its own: linear layers run inside vLLM / PyTorch on
+// rocBLAS (reports/11_custom_engine.md:38 describes q/k/v -> qkv and gate/up -> gate_up
+// weight fusion in the absent engine).  These kernels are the sm_100a replacement for
+// that path: qkv, gate_up (+ SiLU-mul in the epilogue), o_proj, down_proj, lm_head.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "gemm.cuh"
+#include "ops.h"
+
+using namespace sm100;
+using gemm::Params;
+
+namespace {
+
+enum Epi : int { kEpiStore = 0, kEpiSiluMul = 1 };
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+// silu(g) * u with every intermediate rounded to bf16, which is what an unfused bf16
+// pipeline (gate, act(gate), act * up as separate bf16 tensors) produces.
+__device__ __forceinline__ float silu_mul_bf16(float g, float u) {
+  g = bf16_round(g);
+  u = bf16_round(u);
+  float s = bf16_round(g / (1.0f + __expf(-g)));
+  return s * u;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(gemm::kThreads, 1)
+k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ gemm::Smem s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * gemm::kBM, n0 = blockIdx.y * p.bn;
+  const int S = p.splits;
+  const int split = S > 1 ? int(cluster_ctarank()) : 0;
+  const int kb_per = (p.kb_total + S - 1) / S;
+  const int kb0 = split * kb_per;
+  int nkb = p.kb_total - kb0;
+  nkb = nkb < 0 ? 0 : (nkb > kb_per ? kb_per : nkb);
+
+  uint8_t* sm = gemm::mainloop(&tmA, &tmB, p, s, smem_raw, m0, n0, kb0, nkb);
+  volatile int* abortp = &s.abort_flag;
+  const int rows = (p.N - n0 < p.bn) ? (p.N - n0) : p.bn;  // valid tokens in this tile
+  constexpr int OUTW = EPI == kEpiSiluMul ? 64 : 128;       // output features per tile
+
+  if (warp >= 2) {
+    const int quarter = warp & 3;             // TMEM lane quarter this warp may read
+    const int ml = quarter * 32 + lane;       // feature row inside the tile
+    bool ok = nkb > 0 ? mbar_wait(smem_u32(&s.accum), 0, abortp, p.limit_ns) : true;
+    // lanes leave the polling loop at different times: reconverge before the warp-wide
+    // (.sync.aligned) TMEM loads, and make the decision to load warp-uniform
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    const float bias = (p.bias && m0 + ml < p.M) ? __bfloat162float(p.bias[m0 + ml]) : 0.f;
+    float* stage_f = reinterpret_cast<float*>(sm);
+    __nv_bfloat16* stage_h = reinterpret_cast<__nv_bfloat16*>(sm);
+    for (int c = 0; c < p.bn; c += 16) {
+      uint32_t r[16];
+      if (ok && nkb > 0) {
+        tmem_ld16(s.tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(c), r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j++) r[j] = 0u;
+      }
+      if (S > 1) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) stage_f[(c + j) * 128 + ml] = __uint_as_float(r[j]);
+      } else if (EPI == kEpiSiluMul) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          float v = __uint_as_float(r[j]) + bias;
+          float o = __shfl_xor_sync(0xffffffffu, v, 1);
+          if ((lane & 1) == 0) stage_h[(c + j) * 64 + (ml >> 1)] = __float2bfloat16_rn(silu_mul_bf16(v, o));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j++) stage_h[(c + j) * 128 + ml] = __float2bfloat16_rn(__uint_as_float(r[j]) + bias);
+      }
+    }
+    if (S == 1) {
+      // coalesced copy-out of the staged tile: 16-byte pieces, OUTW features per token row
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int te = threadIdx.x - 64;
+      constexpr int PPR = OUTW / 8;  // 16-byte pieces per row
+      const int out_m0 = EPI == kEpiSiluMul ? (m0 >> 1) : m0;
+      const int out_M = EPI == kEpiSiluMul ? (p.M >> 1) : p.M;
+      for (int idx = te; idx < rows * PPR; idx += 128) {
+        const int t = idx / PPR, pc = idx % PPR;
+        const int m = out_m0 + pc * 8;
+        if (m + 8 <= out_M) {
+          *reinterpret_cast<uint4*>(p.y + size_t(n0 + t) * p.ldy + m) =
+              *reinterpret_cast<const uint4*>(stage_h + t * OUTW + pc * 8);
+        } else {
+          for (int e = 0; e < 8 && m + e < out_M; e++) p.y[size_t(n0 + t) * p.ldy + m + e] = stage_h[t * OUTW + pc * 8 + e];
+        }
+      }
+    }
+  }
+
+  if (S > 1) {
+    // ---- deterministic split-K: CTA j of the cluster reduces feature slice j over all K ranges ----
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int te = threadIdx.x - 64;
+      const int fs = 128 / S;            // features per CTA
+      const int q4 = fs / 4;             // float4 pieces per row
+      const uint32_t stage_addr = smem_u32(sm);
+      for (int idx = te; idx < rows * q4; idx += 128) {
+        const int t = idx / q4, f = split * fs + (idx % q4) * 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < S; r++) {
+          float4 v = ld_dsmem_f32x4(mapa_shared(stage_addr + uint32_t((t * 128 + f) * 4), uint32_t(r)));
+          if (r == 0) acc = v;
+          else { acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
+        }
+        const int m = m0 + f;
+        if (p.bias) {
+          if (m + 0 < p.M) acc.x += __bfloat162float(p.bias[m + 0]);
+          if (m + 1 < p.M) acc.y += __bfloat162float(p.bias[m + 1]);
+          if (m + 2 < p.M) acc.z += __bfloat162float(p.bias[m + 2]);
+          if (m + 3 < p.M) acc.w += __bfloat162float(p.bias[m + 3]);
+        }
+        if (EPI == kEpiSiluMul) {
+          __nv_bfloat162 o = __floats2bfloat162_rn(silu_mul_bf16(acc.x, acc.y), silu_mul_bf16(acc.z, acc.w));
+          if (m + 4 <= p.M) *reinterpret_cast<__nv_bfloat162*>(p.y + size_t(n0 + t) * p.ldy + (m >> 1)) = o;
+        } else {
+          __nv_bfloat16* dst = p.y + size_t(n0 + t) * p.ldy + m;
+          if (m + 4 <= p.M) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(dst) = pk;
+          } else {
+            float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+            for (int e = 0; e < 4 && m + e < p.M; e++) dst[e] = __float2bfloat16_rn(a4[e]);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
+  }
+  __syncwarp();
+  gemm::teardown(p, s);
+}
+
+// ---- host side -------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_encode_once;
+
+struct MapKey {
+  const void* ptr;
+  unsigned long long rows, cols, ld;
+  unsigned box_rows;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ k.rows; h = h * 1000003u ^ k.cols; h = h * 1000003u ^ k.ld; h = h * 1000003u ^ k.box_rows;
+    return h;
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+std::mutex g_maps_mu;
+int* g_err_flag[16] = {nullptr};
+int g_sm_count[16] = {0};
+bool g_attr_done = false;
+
+}  // namespace
+
+namespace tbvops {
+
+// [rows, cols] bf16 row-major with row stride ld (elements); box = box_rows x 64, 128-byte swizzle.
+int make_tensor_map_bf16(CUtensorMap* out, const void* ptr, unsigned long long rows, unsigned long long cols,
+                         unsigned long long ld, unsigned box_rows) {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  });
+  if (!g_encode) return -1;
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> g(g_maps_mu);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return 0; }
+  }
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) || (ld * 2) % 16 || box_rows > 256 || box_rows == 0) return -2;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -3;
+  {
+    std::lock_guard<std::mutex> g(g_maps_mu);
+    if (g_maps.size() > 65536) g_maps.clear();
+    g_maps[key] = m;
+  }
+  *out = m;
+  return 0;
+}
+
+int* gemm_err_flag() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 15;
+  if (!g_err_flag[dev]) {
+    cudaMalloc(&g_err_flag[dev], sizeof(int));
+    cudaMemset(g_err_flag[dev], 0, sizeof(int));
+    cudaDeviceProp prop;
+    cudaGetDeviceProperties(&prop, dev);
+    g_sm_count[dev] = prop.multiProcessorCount;
+  }
+  return g_err_flag[dev];
+}
+int sm_count() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  gemm_err_flag();
+  return g_sm_count[dev & 15];
+}
+
+void gemm_config(int M, int N, int K, int splits_hint, int* bn_out, int* splits_out, int* stages_out) {
+  int bn = N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256)));
+  const int kb = (K + 63) / 64;
+  const int tiles = ((M + 127) / 128) * ((N + bn - 1) / bn);
+  const int sms = sm_count();
+  int splits = 1;
+  if (splits_hint > 0) {
+    splits = splits_hint;
+  } else {
+    while (splits < 8 && tiles * splits * 2 <= 2 * sms && kb / (splits * 2) >= 8) splits *= 2;
+  }
+  while (splits > 1 && (kb + splits - 1) / splits * (splits - 1) >= kb) splits /= 2;  // every split gets work
+  const int stage_bytes = gemm::kATileBytes + bn * 128;
+  const int budget = (tiles * splits > sms) ? 108 * 1024 : 200 * 1024;  // two CTAs per SM when the grid is larger than the GPU
+  int stages = budget / stage_bytes;
+  stages = stages < 2 ? 2 : (stages > gemm::kMaxStages ? gemm::kMaxStages : stages);
+  const int need = splits > 1 ? bn * 512 : bn * 256;  // epilogue staging reuses the ring
+  while (stages * stage_bytes < need) stages++;
+  *bn_out = bn; *splits_out = splits; *stages_out = stages;
+}
+
+}  // namespace tbvops
+
+extern "C" {
+
+// y[N, M(/2)] = epilogue(x[N, K] @ w[M, K]^T).  ldx / ldy: row strides in elements.
+// epi: 0 = store (+bias), 1 = SiLU-mul over row-interleaved gate/up weights (M = 2 * out features).
+int tbv_op_gemm(const void* w, const void* x, void* y, const void* bias, int M, int N, int K, int ldx, int ldy, int epi,
+                int splits_hint, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || (ldy % 8) || (reinterpret_cast<uintptr_t>(y) & 15u)) return -2;
+  if (epi == kEpiSiluMul && (M % 2)) return -2;
+  int bn, splits, stages;
+  tbvops::gemm_config(M, N, K, splits_hint, &bn, &splits, &stages);
+  CUtensorMap tmA, tmB;
+  if (tbvops::make_tensor_map_bf16(&tmA, w, M, K, K, 128) != 0) return -3;
+  if (tbvops::make_tensor_map_bf16(&tmB, x, N, K, ldx, bn) != 0) return -3;
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.bn = bn; p.splits = splits; p.stages = stages;
+  p.kb_total = (K + 63) / 64;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.y = static_cast<__nv_bfloat16*>(y);
+  p.limit_ns = 2000000000ull;
+  p.err = tbvops::gemm_err_flag();
+  const size_t smem = size_t(stages) * (gemm::kATileBytes + bn * 128) + 1024;
+  if (!g_attr_done) {
+    // 227 KB per CTA in total; the kernel's static shared state comes out of the same budget
+    cudaError_t a1 = cudaFuncSetAttribute(k_gemm<kEpiStore>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    cudaError_t a2 = cudaFuncSetAttribute(k_gemm<kEpiSiluMul>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    if (a1 != cudaSuccess || a2 != cudaSuccess) {
+      fprintf(stderr, "[tbvops] cudaFuncSetAttribute(max dynamic smem) failed: %s\n", cudaGetErrorString(a1 != cudaSuccess ? a1 : a2));
+      return -1;
+    }
+    g_attr_done = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((M + 127) / 128, (N + bn - 1) / bn, splits);
+  cfg.blockDim = dim3(gemm::kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = epi == kEpiSiluMul ? cudaLaunchKernelEx(&cfg, k_gemm<kEpiSiluMul>, tmA, tmB, p)
+                                     : cudaLaunchKernelEx(&cfg, k_gemm<kEpiStore>, tmA, tmB, p);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "[tbvops] gemm launch failed: %s (M=%d N=%d K=%d bn=%d splits=%d stages=%d)\n", cudaGetErrorString(e), M, N, K,
+            bn, splits, stages);
+    return -1;
+  }
+  return 0;
+}
+
+// 1 if any GEMM wait ever gave up on the current device (synchronises the device).
+int tbv_op_gemm_error(void) {
+  int v = 0;
+  cudaMemcpy(&v, tbvops::gemm_err_flag(), sizeof(int), cudaMemcpyDeviceToHost);
+  return v;
+}
+
+void tbv_op_gemm_config(int M, int N, int K, int splits_hint, int* bn, int* splits, int* stages) {
+  tbvops::gemm_config(M, N, K, splits_hint, bn, splits, stages);
+}
+
+}  // extern "C"

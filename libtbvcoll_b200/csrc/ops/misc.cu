@@ -1,0 +1,214 @@
+// misc.cu — the small memory-bound decode operators: RoPE + KV-cache write, SiLU-mul,
+// embedding gather (vocab-parallel), greedy argmax.
+//
+// The reference's engine layer is described only (TP weight sharding, RoPE, GQA, KV cache,
+// greedy: reports/11_custom_engine.md:10-20); these are the sm_100a kernels for it.  All
+// arithmetic follows HF Llama's bf16 semantics op by op (each elementwise op rounds to
+// bf16), so logits can be compared with a plain PyTorch reference.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+namespace {
+
+__device__ __forceinline__ float bfr(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// qkv: [T, (nq + 2*nkv) * D] (q heads, then k heads, then v heads).  Rotates q and k in
+// place (HF "rotate_half" pairing: i <-> i + D/2, cos/sin rounded to bf16, products and
+// the sum each rounded to bf16) and scatters k, v into the paged cache:
+// k_cache/v_cache: [num_blocks * block_size, nkv, D], row = slot_mapping[t] (< 0: skip).
+__global__ void k_rope_kv(__nv_bfloat16* qkv, const int* __restrict__ positions, const float* __restrict__ cos_sin,
+                          const long long* __restrict__ slot_mapping, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
+                          int nq, int nkv, int D, int max_pos) {
+  const int t = blockIdx.x;
+  const int half = D / 2;
+  int pos = positions[t];
+  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+  const float* cs = cos_sin + size_t(pos) * D;  // [cos(0..half-1), sin(0..half-1)]
+  __nv_bfloat16* row = qkv + size_t(t) * (nq + 2 * nkv) * D;
+  const long long slot = slot_mapping ? slot_mapping[t] : -1;
+  const int nrot = (nq + nkv) * half;
+  for (int i = threadIdx.x; i < nrot; i += blockDim.x) {
+    const int h = i / half, d = i % half;
+    __nv_bfloat16* v = row + h * D;
+    const float c = bfr(cs[d]), s = bfr(cs[half + d]);
+    const float x1 = __bfloat162float(v[d]), x2 = __bfloat162float(v[d + half]);
+    const float o1 = bfr(bfr(x1 * c) + bfr(-x2 * s));
+    const float o2 = bfr(bfr(x2 * c) + bfr(x1 * s));
+    const __nv_bfloat16 b1 = __float2bfloat16_rn(o1), b2 = __float2bfloat16_rn(o2);
+    v[d] = b1;
+    v[d + half] = b2;
+    if (h >= nq && slot >= 0) {
+      __nv_bfloat16* kc = k_cache + (size_t(slot) * nkv + (h - nq)) * D;
+      kc[d] = b1;
+      kc[d + half] = b2;
+    }
+  }
+  if (slot >= 0) {
+    const uint4* vs = reinterpret_cast<const uint4*>(row + (nq + nkv) * D);
+    uint4* vd = reinterpret_cast<uint4*>(v_cache + size_t(slot) * nkv * D);
+    for (int i = threadIdx.x; i < nkv * D / 8; i += blockDim.x) vd[i] = vs[i];
+  }
+}
+
+// out[t, i] = bf16( bf16(silu(gate)) * up ),  x: [T, 2*I] = [gate | up]
+__global__ void k_silu_mul(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int I) {
+  const size_t t = blockIdx.y;
+  const int i8 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i8 >= I) return;
+  const uint4 g4 = *reinterpret_cast<const uint4*>(x + t * 2 * I + i8);
+  const uint4 u4 = *reinterpret_cast<const uint4*>(x + t * 2 * I + I + i8);
+  const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&g4);
+  const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&u4);
+  uint4 o4;
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&o4);
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    const float gf = __bfloat162float(g[k]);
+    o[k] = __float2bfloat16_rn(bfr(gf / (1.0f + __expf(-gf))) * __bfloat162float(u[k]));
+  }
+  *reinterpret_cast<uint4*>(out + t * I + i8) = o4;
+}
+
+// out[t] = table[ids[t] - vocab_start] if in [vocab_start, vocab_end) else 0  (vocab-parallel shard)
+__global__ void k_embedding(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                            __nv_bfloat16* __restrict__ out, int hidden, long long vocab_start, long long vocab_end) {
+  const size_t t = blockIdx.x;
+  const long long id = ids[t];
+  const bool mine = id >= vocab_start && id < vocab_end;
+  const uint4* src = reinterpret_cast<const uint4*>(table + size_t(mine ? id - vocab_start : 0) * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(out + t * hidden);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = mine ? src[i] : make_uint4(0, 0, 0, 0);
+}
+
+// Greedy sampling over a vocab shard: per row the maximum logit and the smallest index
+// holding it.  Stage 1: `nblk` CTAs per row write partials; stage 2: the last CTA of a row
+// (atomic ticket) folds them in block order — deterministic, first index wins ties like
+// torch.argmax.
+__global__ void k_argmax(const __nv_bfloat16* __restrict__ logits, int vocab, int ld, long long index_offset,
+                         float* part_val, long long* part_idx, unsigned* tickets, float* out_val, long long* out_idx) {
+  const int row = blockIdx.y, nblk = gridDim.x;
+  const int per = (vocab + nblk - 1) / nblk;
+  const int v0 = blockIdx.x * per, v1 = min(vocab, v0 + per);
+  const __nv_bfloat16* x = logits + size_t(row) * ld;
+  float best = -FLT_MAX;
+  int bi = 0x7fffffff;
+  for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+    const float f = __bfloat162float(x[i]);
+    if (f > best) { best = f; bi = i; }  // ascending i per thread: first index kept on ties
+  }
+  __shared__ float sv[32];
+  __shared__ int si[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  __shared__ bool last;
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (blockDim.x + 31) / 32; w++)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+    part_val[row * nblk + blockIdx.x] = best;
+    part_idx[row * nblk + blockIdx.x] = bi;
+    __threadfence();
+    last = atomicAdd(&tickets[row], 1u) == unsigned(nblk - 1);
+  }
+  __syncthreads();
+  if (last && threadIdx.x == 0) {
+    __threadfence();
+    float b = -FLT_MAX;
+    long long i = 0x7fffffff;
+    for (int k = 0; k < nblk; k++) {
+      const float v = *(volatile float*)&part_val[row * nblk + k];
+      const long long vi = *(volatile long long*)&part_idx[row * nblk + k];
+      if (v > b || (v == b && vi < i)) { b = v; i = vi; }
+    }
+    out_val[row] = b;
+    out_idx[row] = i + index_offset;
+    tickets[row] = 0;  // ready for the next launch
+  }
+}
+
+// Fold per-rank (value, index) candidates gathered from all ranks: out[t] = index of the
+// largest value, lowest index on ties.  vals/idx: [world, T].
+__global__ void k_argmax_merge(const float* __restrict__ vals, const long long* __restrict__ idx, int world, int T,
+                               long long* __restrict__ out) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  float b = vals[t];
+  long long bi = idx[t];
+  for (int r = 1; r < world; r++) {
+    const float v = vals[size_t(r) * T + t];
+    const long long vi = idx[size_t(r) * T + t];
+    if (v > b || (v == b && vi < bi)) { b = v; bi = vi; }
+  }
+  out[t] = bi;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tbv_op_rope_kv(void* qkv, const void* positions, const void* cos_sin, const void* slot_mapping, void* k_cache, void* v_cache,
+                   int tokens, int nq, int nkv, int D, int max_pos, void* stream) {
+  if (tokens <= 0) return 0;
+  if (D % 16) return -2;
+  int threads = (nq + nkv) * D / 2;
+  threads = threads > 512 ? 512 : ((threads + 31) / 32 * 32);
+  k_rope_kv<<<tokens, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(qkv), static_cast<const int*>(positions), static_cast<const float*>(cos_sin),
+      static_cast<const long long*>(slot_mapping), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), nq,
+      nkv, D, max_pos);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int tbv_op_silu_mul(const void* x, void* out, int tokens, int inter, void* stream) {
+  if (tokens <= 0) return 0;
+  if (inter % 8) return -2;
+  dim3 grid((inter / 8 + 255) / 256, tokens);
+  k_silu_mul<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                   static_cast<__nv_bfloat16*>(out), inter);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int tbv_op_embedding(const void* ids, const void* table, void* out, int tokens, int hidden, long long vocab_start,
+                     long long vocab_end, void* stream) {
+  if (tokens <= 0) return 0;
+  if (hidden % 8) return -2;
+  k_embedding<<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const long long*>(ids),
+                                                                      static_cast<const __nv_bfloat16*>(table),
+                                                                      static_cast<__nv_bfloat16*>(out), hidden, vocab_start, vocab_end);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// workspace layout (caller-provided scratch, >= tbv_op_argmax_workspace(tokens) bytes, zeroed once):
+//   [tickets: tokens u32 (padded to 256 B)] [part_val: tokens*64 f32] [part_idx: tokens*64 i64]
+size_t tbv_op_argmax_workspace(int tokens) {
+  return ((size_t(tokens) * 4 + 255) & ~size_t(255)) + size_t(tokens) * 64 * 4 + size_t(tokens) * 64 * 8;
+}
+int tbv_op_argmax(const void* logits, int tokens, int vocab, int ld, long long index_offset, void* workspace, void* out_val,
+                  void* out_idx, void* stream) {
+  if (tokens <= 0) return 0;
+  int nblk = (vocab + 4095) / 4096;
+  nblk = nblk < 1 ? 1 : (nblk > 64 ? 64 : nblk);
+  char* ws = static_cast<char*>(workspace);
+  unsigned* tickets = reinterpret_cast<unsigned*>(ws);
+  float* pv = reinterpret_cast<float*>(ws + ((size_t(tokens) * 4 + 255) & ~size_t(255)));
+  long long* pi = reinterpret_cast<long long*>(reinterpret_cast<char*>(pv) + size_t(tokens) * 64 * 4);
+  k_argmax<<<dim3(nblk, tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), vocab, ld, index_offset, pv, pi, tickets, static_cast<float*>(out_val),
+      static_cast<long long*>(out_idx));
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int tbv_op_argmax_merge(const void* vals, const void* idx, int world, int tokens, void* out, void* stream) {
+  if (tokens <= 0) return 0;
+  k_argmax_merge<<<(tokens + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(vals), static_cast<const long long*>(idx), world, tokens, static_cast<long long*>(out));
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // extern "C"

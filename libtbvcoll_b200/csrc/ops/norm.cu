@@ -1,0 +1,65 @@
+// norm.cu — RMSNorm and fused residual-add + RMSNorm (bf16, HF Llama semantics).
+//
+// The absent engine of the reference describes a fused rms_norm that was NOT bit-identical
+// to HF (max abs diff 0.2188, reports/11_custom_engine.md:78-81) with an exact mode behind
+// ZB_EXACT_RMS=1.  This kernel is the exact form only: variance in fp32 over the bf16 input,
+// normalise, round to bf16, then multiply by gamma and round again.  The row math is the
+// device function shared with the fused all-reduce kernel (ar_device.cuh), same thread
+// mapping, so fused and unfused pipelines agree bit for bit.
+#include <cuda_runtime.h>
+
+#include "../ar_device.cuh"
+#include "ops.h"
+
+using namespace tbv;
+
+namespace {
+// one CTA per row
+template <bool ADD>
+__global__ void __launch_bounds__(1024) k_rmsnorm(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* residual,
+                                                  const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* residual_out,
+                                                  __nv_bfloat16* y, int hidden, float eps) {
+  __shared__ float sh[32];
+  const int upr = hidden / 8;
+  const size_t row = blockIdx.x;
+  float h[kNormMaxUnits][8];
+#pragma unroll
+  for (int k = 0; k < kNormMaxUnits; k++) {
+    int u = threadIdx.x + k * blockDim.x;
+    if (u < upr) {
+      size_t off = row * upr + u;
+      Pack<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(x)[off], h[k]);
+      if (ADD) {
+        float r[8];
+        Pack<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(residual)[off], r);
+#pragma unroll
+        for (int i = 0; i < 8; i++) h[k][i] = __bfloat162float(__float2bfloat16_rn(h[k][i] + r[i]));
+        reinterpret_cast<uint4*>(residual_out)[off] = Pack<__nv_bfloat16>::pack(h[k]);
+      }
+    }
+  }
+  rmsnorm_row_store(h, upr, hidden, eps, reinterpret_cast<const uint4*>(gamma), reinterpret_cast<uint4*>(y) + row * upr, sh);
+}
+}  // namespace
+
+extern "C" {
+// y = RMSNorm(x) * gamma.  x, y: [tokens, hidden] bf16 contiguous; hidden % 8 == 0, hidden <= 32768.
+int tbv_op_rmsnorm(const void* x, const void* gamma, void* y, int tokens, int hidden, float eps, void* stream) {
+  if (hidden % 8 || hidden > 8 * kNormMaxUnits * 1024 || tokens <= 0) return -2;
+  k_rmsnorm<false><<<tokens, tbvops::norm_threads(hidden), 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), nullptr, static_cast<const __nv_bfloat16*>(gamma), nullptr,
+      static_cast<__nv_bfloat16*>(y), hidden, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+// h = bf16(x + residual); residual_out = h; y = RMSNorm(h) * gamma.  Aliasing residual_out == residual
+// and y == x is allowed.
+int tbv_op_add_rmsnorm(const void* x, const void* residual, const void* gamma, void* residual_out, void* y, int tokens,
+                       int hidden, float eps, void* stream) {
+  if (hidden % 8 || hidden > 8 * kNormMaxUnits * 1024 || tokens <= 0) return -2;
+  k_rmsnorm<true><<<tokens, tbvops::norm_threads(hidden), 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
+      static_cast<const __nv_bfloat16*>(gamma), static_cast<__nv_bfloat16*>(residual_out), static_cast<__nv_bfloat16*>(y),
+      hidden, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+}

@@ -1,0 +1,18 @@
+// ops.h — internal declarations shared by the operator translation units.
+#pragma once
+#include <cuda.h>
+
+namespace tbvops {
+int make_tensor_map_bf16(CUtensorMap* out, const void* ptr, unsigned long long rows, unsigned long long cols,
+                         unsigned long long ld, unsigned box_rows);
+int* gemm_err_flag();
+int sm_count();
+void gemm_config(int M, int N, int K, int splits_hint, int* bn_out, int* splits_out, int* stages_out);
+// threads per CTA for the row-normalisation kernels; the fused collective uses the same
+// mapping so that both produce identical bits
+inline int norm_threads(int hidden) {
+  const int upr = hidden / 8;                 // 16-byte units per row
+  const int k = (upr + 1023) / 1024;          // units per thread
+  return ((upr + k - 1) / k + 31) / 32 * 32;
+}
+}  // namespace tbvops

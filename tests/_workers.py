@@ -47,6 +47,8 @@ def run_ranks(fn, world, *args, timeout=120, env=None):
 
 def _entry(fn, rank, world, q, args):
     try:
+        import torch
+        torch.set_num_threads(1)
         q.put((rank, True, fn(rank, world, *args)))
     except BaseException:
         q.put((rank, False, traceback.format_exc()))

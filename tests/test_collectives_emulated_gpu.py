@@ -1,0 +1,130 @@
+"""The multi-rank collective kernels on ONE GPU: N emulated ranks run as a single
+cooperative launch (blockIdx.y = rank), so the push/flag/wait/reduce protocol, the slot
+ring and the sequence numbering are exercised for world 2/4/8 without N GPUs.
+Oracle: fixed-order fp32 accumulate with one rounding, never another collective library
+(same stance as the reference's step4/test_exact.py:3-4)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def gen(seed, n, dtype):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return ((torch.rand(n, generator=g) - 0.5) * 10).to(dtype).to(DEV)
+
+
+def oracle(ts):
+    acc = ts[0].float().clone()
+    for t in ts[1:]:
+        acc += t.float()
+    return acc.to(ts[0].dtype)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot"])
+def test_exact_all_dtypes_sizes(world, algo):
+    from libtbvcoll_b200.tbvcoll import Comm
+    c = Comm.local(world, 0, cap_bytes=1 << 20)
+    c.set_algo(algo)
+    try:
+        for dtype in (torch.float32, torch.float16, torch.bfloat16):
+            es = torch.tensor([], dtype=dtype).element_size()
+            for nbytes in (16, 57344, 229376, 1048576, 4096 + 16 * 7, 2 * 33):   # incl. odd tails / scalar path
+                n = nbytes // es
+                ins = [gen(1234 + r, n, dtype) for r in range(world)]
+                outs = [torch.empty_like(t) for t in ins]
+                assert c.all_reduce_local(ins, outs)
+                torch.cuda.synchronize()
+                want = oracle(ins)
+                for r in range(world):
+                    assert torch.equal(outs[r], want), (dtype, nbytes, r)
+        assert not c.err()
+    finally:
+        c.destroy()
+
+
+@pytest.mark.parametrize("world,algo", [(2, "oneshot"), (8, "oneshot"), (4, "twoshot")])
+def test_stress_back_to_back_no_sync_4_slots(world, algo):
+    """Counterpart of step4/test_stress.py:23-42: many calls with no synchronisation in
+    between (slot reuse), every output checked afterwards."""
+    from libtbvcoll_b200.tbvcoll import Comm
+    c = Comm.local(world, 0, cap_bytes=57344)
+    c.set_algo(algo)
+    iters, n = 300, 57344 // 2
+    try:
+        ins = [[gen(it * world + r, n, torch.bfloat16) for r in range(world)] for it in range(iters)]
+        outs = [[torch.empty_like(t) for t in row] for row in ins]
+        for it in range(iters):
+            assert c.all_reduce_local(ins[it], outs[it])
+        torch.cuda.synchronize()
+        bad = sum(0 if all(torch.equal(o, oracle(ins[it])) for o in outs[it]) else 1 for it in range(iters))
+        assert bad == 0
+        pre, xfer, post, enq, drain, n_calls = c.stats5()
+        assert n_calls == iters and xfer >= 0
+    finally:
+        c.destroy()
+
+
+def test_in_place_unaligned_and_graph_replay():
+    from libtbvcoll_b200.tbvcoll import Comm
+    world = 4
+    c = Comm.local(world, 0, cap_bytes=1 << 16)
+    try:
+        base = [gen(50 + r, 1001, torch.bfloat16) for r in range(world)]
+        views = [b[1:].clone()[0:999] for b in base]            # aligned clones
+        un = [torch.empty(1001, dtype=torch.bfloat16, device=DEV)[1:1000] for _ in range(world)]  # 2-byte aligned views
+        for u, v in zip(un, views):
+            u.copy_(v)
+        want = oracle(views)
+        assert c.all_reduce_local(un)                            # in place, scalar path
+        torch.cuda.synchronize()
+        assert all(torch.equal(u, want) for u in un)
+        # CUDA graph: sequence numbers live on the device, so a captured call replays correctly
+        xs = [gen(70 + r, 4096, torch.bfloat16) for r in range(world)]
+        ys = [torch.empty_like(x) for x in xs]
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            c.all_reduce_local(xs, ys)                           # warm-up outside capture
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                c.all_reduce_local(xs, ys)
+            for rep in range(6):                                 # more replays than slots
+                for r in range(world):
+                    xs[r].copy_(gen(100 * rep + r, 4096, torch.bfloat16))
+                g.replay()
+                s.synchronize()
+                assert all(torch.equal(y, oracle(xs)) for y in ys)
+        assert not c.err()
+    finally:
+        c.destroy()
+
+
+@pytest.mark.parametrize("world,T,H", [(2, 8, 4096), (8, 3, 4096), (4, 16, 8192), (2, 1, 1024)])
+def test_fused_allreduce_residual_rmsnorm(world, T, H):
+    from libtbvcoll_b200.tbvcoll import Comm
+    from libtbvcoll_b200 import ops
+    from libtbvcoll_b200.ops import reference as ref
+    c = Comm.local(world, 0, cap_bytes=T * H * 2)
+    try:
+        xs = [gen(r, T * H, torch.bfloat16).view(T, H) * 0.1 for r in range(world)]
+        res = [gen(99, T * H, torch.bfloat16).view(T, H) for _ in range(world)]
+        gamma = gen(7, H, torch.bfloat16)
+        res_out = [torch.empty_like(x) for x in xs]
+        ys = [torch.empty_like(x) for x in xs]
+        assert c.all_reduce_rmsnorm_local(xs, res, gamma, 1e-5, res_out, ys)
+        torch.cuda.synchronize()
+        want_y, want_h = ref.ar_residual_rmsnorm(xs, res[0], gamma, 1e-5)
+        # the unfused pipeline (all-reduce, then the add+norm op) must give the same BITS
+        summed = [torch.empty_like(x) for x in xs]
+        c.all_reduce_local(xs, summed)
+        y_unf, h_unf = ops.add_rmsnorm(summed[0].clone(), res[0].clone(), gamma, 1e-5)
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert torch.equal(res_out[r], want_h)
+            assert torch.equal(ys[r], y_unf)
+            assert (ys[r].float() - want_y.float()).abs().max().item() <= 2 ** -6 * want_y.float().abs().max().item()
+    finally:
+        c.destroy()

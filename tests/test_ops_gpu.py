@@ -1,0 +1,159 @@
+"""Numerics of every sm_100a operator against a plain PyTorch fp32 statement of the same math."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from libtbvcoll_b200 import ops as o
+    o.lib()
+    return o
+
+
+from libtbvcoll_b200.ops import reference as ref  # noqa: E402
+
+DEV = "cuda"
+
+
+def rnd(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).to(DEV)
+
+
+@pytest.mark.parametrize("N,M,K,splits", [
+    (1, 128, 64, 1), (8, 256, 512, 1), (16, 4096, 2048, 0), (7, 384, 4096, 2), (33, 512, 1024, 4), (64, 4096, 7168, 0),
+    (8, 6144, 4096, 0), (200, 256, 320, 1), (300, 640, 1088, 1), (512, 1024, 2048, 1), (5, 16032, 512, 1), (24, 128, 8192, 8),
+])
+def test_gemm_matches_fp32(ops, N, M, K, splits):
+    x, w = rnd(N, K, seed=1), rnd(M, K, scale=0.05, seed=2)
+    y = ops.gemm(x, w, splits=splits)
+    torch.cuda.synchronize()
+    assert not ops.gemm_error()
+    want = ref.gemm(x, w)
+    err = (y.float() - want).abs().max().item()
+    tol = 0.01 * want.abs().max().item() + 1e-3
+    assert err <= tol, (err, tol, ops.gemm_config(M, N, K, splits))
+    # split-K is deterministic: same bits on a second run
+    y2 = ops.gemm(x, w, splits=splits)
+    assert torch.equal(y, y2)
+
+
+def test_gemm_bias_and_strided_rows(ops):
+    N, M, K = 12, 256, 512
+    big = rnd(N, K + 64, seed=3)
+    x = big[:, :K]                       # row stride K + 64
+    w, b = rnd(M, K, scale=0.05, seed=4), rnd(M, seed=5)
+    outbuf = torch.zeros(N, M + 128, dtype=torch.bfloat16, device=DEV)
+    y = ops.gemm(x, w, out=outbuf[:, :M], bias=b)
+    torch.cuda.synchronize()
+    want = ref.gemm(x, w, b)
+    assert (y.float() - want).abs().max().item() <= 0.01 * want.abs().max().item() + 1e-3
+    assert outbuf[:, M:].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("N,I,K,splits", [(8, 1024, 512, 1), (3, 7168, 4096, 0), (40, 256, 2048, 2), (260, 512, 256, 1)])
+def test_gemm_silu_mul_epilogue_equals_unfused_bits(ops, N, I, K, splits):
+    x, wg, wu = rnd(N, K, seed=6), rnd(I, K, scale=0.05, seed=7), rnd(I, K, scale=0.05, seed=8)
+    fused = ops.gemm(x, ops.interleave_gate_up(wg, wu), epi=ops.EPI_SILU_MUL, splits=splits)
+    gu = ops.gemm(x, torch.cat((wg, wu), 0).contiguous(), splits=splits)
+    unfused = ops.silu_mul(gu)
+    torch.cuda.synchronize()
+    assert torch.equal(fused, unfused)
+    want = ref.silu_mul(torch.cat((ref.gemm(x, wg), ref.gemm(x, wu)), -1))
+    assert (fused.float() - want).abs().max().item() <= 0.02 * want.abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("T,H", [(1, 4096), (9, 4096), (5, 8192), (3, 1024), (2, 12288), (4, 264)])
+def test_rmsnorm_and_add_rmsnorm_bit_exact(ops, T, H):
+    x, r, g = rnd(T, H, seed=9), rnd(T, H, seed=10), rnd(H, seed=11)
+    y = ops.rmsnorm(x, g, 1e-5)
+    want = ref.rmsnorm(x, g, 1e-5)
+    assert (y.float() - want.float()).abs().max().item() <= 2 ** -6 * want.float().abs().max().item()
+    y2, h2 = ops.add_rmsnorm(x.clone(), r.clone(), g, 1e-5)
+    want2, hw = ref.add_rmsnorm(x, r, g, 1e-5)
+    assert torch.equal(h2, hw)
+    assert (y2.float() - want2.float()).abs().max().item() <= 2 ** -6 * want2.float().abs().max().item()
+
+
+def test_rope_kv_writes_cache_and_matches_hf_rotation(ops):
+    T, nq, nkv, D, bs, nblocks = 11, 8, 2, 128, 16, 6
+    qkv = rnd(T, (nq + 2 * nkv) * D, seed=12)
+    pos = torch.arange(3, 3 + T, dtype=torch.int32, device=DEV)
+    cs = ops.rope_cos_sin(D, 64, 5e5, DEV)
+    slots = torch.randperm(bs * nblocks)[:T].to(DEV)
+    slots[2] = -1
+    kc = torch.zeros(bs * nblocks, nkv, D, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    orig = qkv.clone().view(T, nq + 2 * nkv, D)
+    ops.rope_kv(qkv, pos, cs, slots, kc, vc, nq, nkv, D)
+    got = qkv.view(T, nq + 2 * nkv, D)
+    want = ref.rope(orig[:, : nq + nkv], pos, cs)
+    assert torch.equal(got[:, : nq + nkv], want)
+    assert torch.equal(got[:, nq + nkv:], orig[:, nq + nkv:])
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        assert torch.equal(kc[s], got[t, nq: nq + nkv]) and torch.equal(vc[s], orig[t, nq + nkv:])
+    assert kc.abs().sum(dim=(1, 2)).ne(0).sum().item() == T - 1
+
+
+def test_silu_mul_embedding_argmax(ops):
+    x = rnd(5, 2 * 1000, seed=13)
+    assert torch.equal(ops.silu_mul(x), ref.silu_mul(x))
+    table = rnd(300, 256, seed=14)
+    ids = torch.tensor([0, 299, 100, 1000, 450, 399], device=DEV)
+    e = ops.embedding(ids, table, vocab_start=100)
+    want = torch.zeros(6, 256, dtype=torch.bfloat16, device=DEV)
+    want[1], want[2], want[5] = table[199], table[0], table[299]
+    assert torch.equal(e, want)
+    logits = rnd(7, 128256, seed=15)
+    logits[3, 77] = logits[3, 90000] = 50.0      # a tie: the lower index must win
+    ws = ops.argmax_workspace(7, DEV)
+    for _ in range(2):                            # second launch checks that the tickets were reset
+        v, i = ops.argmax(logits, ws, index_offset=1000)
+        wv, wi = ref.argmax_first(logits)
+        assert torch.equal(i, wi + 1000) and torch.equal(v, wv)
+    vals = torch.tensor([[1.0, 5.0], [3.0, 5.0], [2.0, 1.0]], device=DEV)
+    idx = torch.tensor([[10, 70], [20, 30], [5, 6]], device=DEV)
+    assert ops.argmax_merge(vals, idx).tolist() == [20, 30]
+
+
+@pytest.mark.parametrize("nq,nkv,splits", [(8, 2, 1), (8, 8, 3), (4, 2, 4), (16, 2, 2)])
+def test_paged_attention_decode(ops, nq, nkv, splits):
+    D, bs, B = 128, 16, 5
+    ctx = torch.tensor([1, 17, 100, 333, 64], dtype=torch.int32)
+    max_blocks = (int(ctx.max()) + bs - 1) // bs
+    nblocks = B * max_blocks + 3
+    kc, vc = rnd(nblocks * bs, nkv, D, seed=16), rnd(nblocks * bs, nkv, D, seed=17)
+    perm = torch.randperm(nblocks, generator=torch.Generator().manual_seed(1))
+    bt = perm[: B * max_blocks].view(B, max_blocks).to(torch.int32)
+    q = rnd(B, nq, D, seed=18)
+    out = torch.empty_like(q)
+    ws = ops.attn_workspace(B, nq, nkv, splits, DEV)
+    scale = 1 / math.sqrt(D)
+    for _ in range(2):
+        ops.paged_attention(q, kc, vc, bt.to(DEV), ctx.to(DEV), out, scale, bs, splits=splits, workspace=ws)
+    torch.cuda.synchronize()
+    for b in range(B):
+        rows = torch.cat([torch.arange(bs) + int(bt[b, j]) * bs for j in range(max_blocks)])[: int(ctx[b])].to(DEV)
+        want = ref.attention(q[b: b + 1], kc[rows], vc[rows], scale)
+        assert (out[b: b + 1].float() - want).abs().max().item() < 2e-2
+
+
+def test_paged_attention_as_causal_prefill(ops):
+    nq, nkv, D, bs, T = 8, 2, 128, 16, 70
+    kc, vc = rnd(8 * bs, nkv, D, seed=19), rnd(8 * bs, nkv, D, seed=20)
+    bt = torch.tensor([[3, 1, 6, 0, 2]], dtype=torch.int32, device=DEV)
+    q = rnd(T, nq, D, seed=21)
+    out = torch.empty_like(q)
+    ctx = torch.arange(1, T + 1, dtype=torch.int32, device=DEV)
+    seqof = torch.zeros(T, dtype=torch.int32, device=DEV)
+    ops.paged_attention(q, kc, vc, bt, ctx, out, 0.1, bs, seq_of_query=seqof)
+    rows = torch.cat([torch.arange(bs) + int(b) * bs for b in bt[0]])[:T].to(DEV)
+    want = ref.attention(q, kc[rows], vc[rows], 0.1, causal_offset=0)
+    assert (out.float() - want).abs().max().item() < 2e-2
