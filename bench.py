@@ -1,0 +1,265 @@
+#!/usr/bin/env python3
+"""Headline benchmark: tensor-parallel greedy decode tokens/s of a Llama-3-8B-shaped model
+(random-init bf16, batch 8, prompt 512 random token ids), one process per GPU.
+
+    python bench.py --gpus 1 --steps 64 --warmup 8
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 2 --steps 64 --warmup 8
+
+The quantity is the reference's headline (vLLM TP decode tok/s with its all-reduce hooked in,
+step3b/vllm_tp_bench.py:165-209; published 170.9 tok/s at batch 8 on 2 laptops,
+reports/10_tp_custom_allreduce.md:480).  Arms:
+  --impl ours       this repository's engine (sm_100a kernels + tbvcoll collectives)   [default]
+  --impl nccl       the path being replaced: stock PyTorch (cuBLAS) + NCCL all-reduce, CUDA-graphed
+  --impl reference  the unmodified reference: HIP + Thunderbolt ibverbs, cannot exist on this box
+Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REF_TOK_S_BATCH8 = 170.9   # reports/10_tp_custom_allreduce.md:480 (vLLM TP=2 + libtbvcoll, Qwen2.5-7B, 2x gfx1151)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "nccl", "reference"])
+    ap.add_argument("--model", default="llama3-8b")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end arm (0 = same as --steps)")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the line INVALID)")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of this rank's GPU, sampled every 200 ms."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max((float(r[2]) for r in self.rows if len(r) > 2 and r[2].replace('.', '', 1).isdigit()), default=None),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def reference_arm(args):
+    # The one offline install was attempted once:
+    #   pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref <reference>
+    # -> "Directory is not installable. Neither 'setup.py' nor 'pyproject.toml' found."
+    # Its only build recipe is `hipcc --offload-arch=gfx1151 ... -libverbs` (README.md:6-7): no hipcc, no
+    # libibverbs, no AMD GPU and no Thunderbolt RDMA device exist on a B200 box.
+    here = os.path.dirname(os.path.abspath(__file__))
+    if os.path.exists(os.path.join(here, "baseline", "_ref", "libtbvcoll.so")):
+        why = "baseline/_ref holds a library but it targets gfx1151 + ibverbs and cannot load on a CUDA box"
+    else:
+        why = ("reference is HIP (gfx1151) + Thunderbolt ibverbs with no setup.py/pyproject: pip install refuses it, "
+               "and hipcc/libibverbs/the tbv RDMA device do not exist on a B200 box")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def setup_dist(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs one process per GPU: launch with python -m torch.distributed.run "
+                             f"--nnodes=1 --nproc-per-node {args.gpus} --master-addr 127.0.0.1 --master-port P bench.py ...")
+        raise SystemExit(f"WORLD_SIZE={world} but --gpus {args.gpus}")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    import torch
+    if world == 1:
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world):
+    import torch
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def timed_replays(replay, steps, warmup, world):
+    """W untimed + K timed replays bracketed by barrier + synchronize; device time by CUDA events."""
+    import torch
+    for _ in range(warmup):
+        replay()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        replay()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier(world)
+    return max_over_ranks(e0.elapsed_time(e1), world) / steps
+
+
+def run_ours(args, rank, world, local):
+    import torch
+    from libtbvcoll_b200 import ops
+    from libtbvcoll_b200.engine.engine import Engine
+    from libtbvcoll_b200.models.config import get_config
+    from libtbvcoll_b200.parallel.tp import TPGroup
+    from libtbvcoll_b200.tbvcoll import Comm
+    cfg = get_config(args.model)
+    if args.layers:
+        cfg.num_layers = args.layers
+    B, L = args.batch, args.prompt_len
+    e2e_steps = args.e2e_steps or args.steps
+    new_tokens = max(256, args.steps + args.warmup + 2, e2e_steps + 2)
+    chunk = 2048
+    comm = None
+    if world > 1:
+        port = int(os.environ.get("MASTER_PORT", "29500")) + 101
+        comm = Comm(rank, world, local, os.environ.get("MASTER_ADDR", "127.0.0.1"), port, cap_bytes=chunk * cfg.hidden_size * 2)
+    tp = TPGroup(rank, world, comm)
+    eng = Engine(cfg, tp, device=f"cuda:{local}", seed=0, max_batch=B, max_seq_len=L + new_tokens + 16, prefill_chunk=chunk)
+    g = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(0, cfg.vocab_size, (L,), generator=g).tolist() for _ in range(B)]
+
+    # ---- device-timed decode steps: the captured step replayed back to back (device loop) ----
+    first = eng.prefill(prompts, new_tokens)
+    lens = [L] * B
+    splits = eng.attn_splits_for(B, L + new_tokens)
+    eng._load_decode_inputs(B, first, lens)
+    eng.step_counter.zero_()
+    graph = eng.capture(B, splits, True)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed_replays(graph.replay, args.steps, args.warmup, world)
+    clocks = sampler.stop()
+    value = B / (ms * 1e-3)
+
+    # ---- end to end through the public API: Engine.generate, host loop ----
+    eng.generate(prompts, 4)                       # warm the host-loop graph
+    barrier(world)
+    eng.generate(prompts, e2e_steps + 1)
+    e2e = B * e2e_steps / max_over_ranks(eng.last_stats["decode_s"], world)
+    fallbacks = tp.fallbacks
+    out = {
+        "metric": "tp_decode_tokens_per_s", "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": round(value / REF_TOK_S_BATCH8, 2), "dtype": "bf16", "data": "synthetic (random token ids, random-init weights)",
+        "impl": "ours",
+        "config": {"model": cfg.name + ("" if not args.layers else f"-INVALID-{args.layers}-layers"), "global_batch": B, "seq_len": L,
+                   "decode_context": f"{L}..{L + args.steps + args.warmup}", "parallelism": f"tp{world}",
+                   "l2": "inputs larger than L2: every step streams the rank's full weight shard "
+                         f"({cfg.param_count() * 2 / world / 1e9:.1f} GB) from HBM",
+                   "timing": "CUDA events around K graph replays, max over ranks", "attn_splits": splits},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e, 2), "unit": "tokens/s", "h2d_bytes_per_step": 24 * B, "d2h_bytes_per_step": 8 * B,
+                "steps": e2e_steps, "api": "Engine.generate(prompts, max_new_tokens) host loop: per step H2D of ids/positions/slots/"
+                                           "context lengths from pinned memory, graph replay, D2H of the sampled tokens"},
+        "gpu_launches": eng.launches_per_step * args.steps,
+        "launches_per_step": eng.launches_per_step,
+        "collective_fallbacks_to_nccl": fallbacks,
+        "baseline_note": "vs_baseline divides by the reference's published 170.9 tok/s (Qwen2.5-7B, vLLM TP=2, 2x gfx1151 laptops)",
+    }
+    if comm is not None:
+        comm.destroy()
+    return out
+
+
+def run_nccl(args, rank, world, local):
+    """Stock PyTorch TP decode step (cuBLAS + NCCL), CUDA-graphed; same shape, same timing rules."""
+    import torch
+    from libtbvcoll_b200.models.config import get_config
+    from libtbvcoll_b200.models.torch_baseline import GraphedTorchDecoder, TorchLlamaTP
+    from libtbvcoll_b200.utils.weights import RandomSource, shard_for_rank
+    cfg = get_config(args.model)
+    if args.layers:
+        cfg.num_layers = args.layers
+    B, L = args.batch, args.prompt_len
+    dev = f"cuda:{local}"
+    w = shard_for_rank(cfg, RandomSource(cfg, seed=0, device=dev), rank, world, dev, interleave_gate_up=False)
+    m = TorchLlamaTP(cfg, rank, world, w, dev, max_batch=B, max_seq_len=L + 64)
+    with torch.no_grad():
+        g = torch.Generator().manual_seed(1234)
+        prompts = torch.stack([torch.randint(0, cfg.vocab_size, (L,), generator=g) for _ in range(B)]).to(dev)
+        pos = torch.arange(L, device=dev, dtype=torch.int32)[None].expand(B, L)
+        m.forward(prompts, pos, 0)
+        dec = GraphedTorchDecoder(m, B, L)
+        dec.pos.fill_(L)
+        dec.capture()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed_replays(dec.replay, args.steps, args.warmup, world)
+    clocks = sampler.stop()
+    value = B / (ms * 1e-3)
+    return {"metric": "tp_decode_tokens_per_s", "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(value / REF_TOK_S_BATCH8, 2), "dtype": "bf16", "data": "synthetic", "impl": "nccl+cublas (stock PyTorch)",
+            "config": {"model": cfg.name, "global_batch": B, "seq_len": L, "parallelism": f"tp{world}",
+                       "note": "fixed context of prompt_len+1 per step (static shapes under CUDA graph)"},
+            "clocks": clocks, "gpu_launches": 0}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+    rank, world, local = setup_dist(args)
+    out = run_ours(args, rank, world, local) if args.impl == "ours" else run_nccl(args, rank, world, local)
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        import torch
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

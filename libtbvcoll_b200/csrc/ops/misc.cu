@@ -136,22 +136,55 @@ __global__ void k_argmax(const __nv_bfloat16* __restrict__ logits, int vocab, in
 // Fold per-rank (value, index) candidates gathered from all ranks: out[t] = index of the
 // largest value, lowest index on ties.  vals/idx: [world, T].
 __global__ void k_argmax_merge(const float* __restrict__ vals, const long long* __restrict__ idx, int world, int T,
-                               long long* __restrict__ out) {
+                               long long rank_stride_bytes, long long* __restrict__ out) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T) return;
   float b = vals[t];
   long long bi = idx[t];
   for (int r = 1; r < world; r++) {
-    const float v = vals[size_t(r) * T + t];
-    const long long vi = idx[size_t(r) * T + t];
+    const float v = *reinterpret_cast<const float*>(reinterpret_cast<const char*>(vals) + r * rank_stride_bytes + size_t(t) * 4);
+    const long long vi = *reinterpret_cast<const long long*>(reinterpret_cast<const char*>(idx) + r * rank_stride_bytes + size_t(t) * 8);
     if (v > b || (v == b && vi < bi)) { b = v; bi = vi; }
   }
   out[t] = bi;
 }
 
+// Device-side bookkeeping between two decode steps, so that a captured step can be
+// replayed back to back without the host: feed the sampled token back, advance position
+// and context length, look up the cache slot of the new position, log the token.
+__global__ void k_decode_advance(const long long* __restrict__ next_ids, long long* ids, int* positions, int* ctx_lens,
+                                 long long* slot_mapping, const int* __restrict__ block_tables, int max_blocks, int block_size,
+                                 int batch, long long* history, int* step_counter, int max_steps) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  const int step = *step_counter;
+  if (b < batch) {
+    const long long tok = next_ids[b];
+    ids[b] = tok;
+    if (history && step < max_steps) history[size_t(step) * batch + b] = tok;
+    const int pos = positions[b] + 1;
+    positions[b] = pos;
+    ctx_lens[b] = pos + 1;
+    const int blk = pos / block_size;
+    slot_mapping[b] = blk < max_blocks ? (long long)block_tables[size_t(b) * max_blocks + blk] * block_size + pos % block_size : -1;
+  }
+  __syncthreads();
+  if (b == 0) *step_counter = step + 1;
+}
+
 }  // namespace
 
 extern "C" {
+
+int tbv_op_decode_advance(const void* next_ids, void* ids, void* positions, void* ctx_lens, void* slot_mapping,
+                          const void* block_tables, int max_blocks, int block_size, int batch, void* history, void* step_counter,
+                          int max_steps, void* stream) {
+  if (batch <= 0 || batch > 1024) return -2;  // one CTA: the step counter is read before it is bumped
+  k_decode_advance<<<1, (batch + 31) / 32 * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const long long*>(next_ids), static_cast<long long*>(ids), static_cast<int*>(positions),
+      static_cast<int*>(ctx_lens), static_cast<long long*>(slot_mapping), static_cast<const int*>(block_tables), max_blocks,
+      block_size, batch, static_cast<long long*>(history), static_cast<int*>(step_counter), max_steps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
 
 int tbv_op_rope_kv(void* qkv, const void* positions, const void* cos_sin, const void* slot_mapping, void* k_cache, void* v_cache,
                    int tokens, int nq, int nkv, int D, int max_pos, void* stream) {
@@ -204,10 +237,13 @@ int tbv_op_argmax(const void* logits, int tokens, int vocab, int ld, long long i
       static_cast<long long*>(out_idx));
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
-int tbv_op_argmax_merge(const void* vals, const void* idx, int world, int tokens, void* out, void* stream) {
+// vals / idx point at rank 0's candidates; rank r's are rank_stride_bytes further on.
+int tbv_op_argmax_merge(const void* vals, const void* idx, int world, int tokens, long long rank_stride_bytes, void* out,
+                        void* stream) {
   if (tokens <= 0) return 0;
   k_argmax_merge<<<(tokens + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const float*>(vals), static_cast<const long long*>(idx), world, tokens, static_cast<long long*>(out));
+      static_cast<const float*>(vals), static_cast<const long long*>(idx), world, tokens, rank_stride_bytes,
+      static_cast<long long*>(out));
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

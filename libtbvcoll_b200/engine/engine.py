@@ -1,0 +1,201 @@
+"""Greedy TP decode engine: chunked prefill, paged KV cache, decode steps under CUDA graphs.
+
+Counterpart of the reference's undocumented-in-code engine (``engine.py`` / ``run_engine.py``
+in reports/11_custom_engine.md:8-23: TP=1/2 decode, greedy, KV cache) and of the vLLM call
+its bench makes (``LLM.generate`` with temperature 0 and ``ignore_eos=True``,
+step3b/vllm_tp_bench.py:148-171).  The reference measured 6.3-7.8 ms of CPU dispatch per
+step in its engine and 28.5 -> 7.1 us for a graph-captured segment (:61-72) but could not
+capture its CPU-driven collective (:74); here the whole step, collectives included, is one
+graph.
+
+Two decode loops over the same captured step:
+  * host loop  — every step copies the step's inputs (token ids, positions, cache slots,
+    context lengths) host -> device from pinned memory and reads the sampled tokens back;
+    this is what a serving front-end does and what ``generate`` uses by default;
+  * device loop — a small kernel inside the graph feeds the sampled token back and advances
+    positions/slots, so K steps replay back to back with no host round trip.
+"""
+from __future__ import annotations
+
+import math
+import time
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..models.config import ModelConfig
+from ..models.llama import LlamaTP
+from ..parallel.tp import TPGroup
+from ..utils.weights import RandomSource, shard_for_rank
+from .kv_cache import BlockManager
+
+
+class Engine:
+    def __init__(self, cfg: ModelConfig, tp: Optional[TPGroup] = None, device="cuda:0", weights: Optional[Dict[str, torch.Tensor]] = None,
+                 source=None, seed: int = 0, max_batch: int = 8, max_seq_len: int = 1024, block_size: int = 16,
+                 prefill_chunk: int = 2048, max_attn_splits: int = 16):
+        self.cfg = cfg
+        self.tp = tp or TPGroup()
+        self.device = torch.device(device)
+        self.max_batch, self.max_seq_len, self.block_size = max_batch, max_seq_len, block_size
+        self.prefill_chunk = prefill_chunk
+        if weights is None:
+            source = source or RandomSource(cfg, seed=seed, device=self.device)
+            weights = shard_for_rank(cfg, source, self.tp.rank, self.tp.world, self.device)
+        max_blocks_per_seq = (max_seq_len + block_size - 1) // block_size
+        num_blocks = max_batch * max_blocks_per_seq + 1
+        self.bm = BlockManager(num_blocks, block_size, max_batch, max_blocks_per_seq, self.device)
+        self.model = LlamaTP(cfg, self.tp, weights, self.device, max_tokens=max(prefill_chunk, max_batch), max_batch=max_batch,
+                             num_blocks=num_blocks, block_size=block_size, max_attn_splits=max_attn_splits)
+        dev, B = self.device, max_batch
+        # static decode inputs/outputs (graph-captured addresses) and their pinned mirrors
+        self.ids = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.positions = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.slots = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.ctx = torch.ones(B, dtype=torch.int32, device=dev)
+        self.out_tokens = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.step_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.history = torch.zeros(max_seq_len, B, dtype=torch.int64, device=dev)
+        pin = lambda n, dt: torch.zeros(n, dtype=dt).pin_memory()
+        self.ids_h, self.pos_h = pin(B, torch.int64), pin(B, torch.int32)
+        self.slots_h, self.ctx_h, self.out_h = pin(B, torch.int64), pin(B, torch.int32), pin(B, torch.int64)
+        self.graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+        self.launches_per_step = 0
+        self.last_stats: Dict[str, float] = {}
+
+    # ---- prefill ----------------------------------------------------------------------------
+    def prefill(self, prompts: Sequence[Sequence[int]], reserve_new: int) -> List[int]:
+        """Run the prompts through the model in chunks of at most ``prefill_chunk`` token rows
+        (a sequence may straddle chunks: attention reads earlier chunks from the cache).
+        Returns the first generated token of every sequence."""
+        B = len(prompts)
+        assert 0 < B <= self.max_batch
+        self.bm.release_all()
+        for b, p in enumerate(prompts):
+            if len(p) + reserve_new > self.max_seq_len:
+                raise ValueError("prompt + new tokens exceed max_seq_len")
+            self.bm.reserve(b, len(p) + reserve_new)
+        self.bm.sync_to_device()
+        rows = [(b, i, t) for b, p in enumerate(prompts) for i, t in enumerate(p)]
+        first = [0] * B
+        dev = self.device
+        for c0 in range(0, len(rows), self.prefill_chunk):
+            chunk = rows[c0:c0 + self.prefill_chunk]
+            T = len(chunk)
+            ids = torch.tensor([t for _, _, t in chunk], dtype=torch.int64)
+            pos = torch.tensor([i for _, i, _ in chunk], dtype=torch.int32)
+            seqof = torch.tensor([b for b, _, _ in chunk], dtype=torch.int32)
+            slots = torch.tensor([self.bm.slot(b, i) for b, i, _ in chunk], dtype=torch.int64)
+            last_rows = [(r, b) for r, (b, i, _) in enumerate(chunk) if i == len(prompts[b]) - 1]
+            n_log = len(last_rows)
+            out = torch.zeros(max(n_log, 1), dtype=torch.int64, device=dev)
+            logit_rows = torch.tensor([r for r, _ in last_rows] or [0], dtype=torch.int64).to(dev)
+            self.model.forward(T, ids.to(dev), pos.to(dev), slots.to(dev), self.bm.tables, (pos + 1).to(dev), seqof.to(dev),
+                               logit_rows, max(n_log, 1), out, attn_splits=1)
+            if n_log:
+                toks = out[:n_log].tolist()
+                for (r, b), t in zip(last_rows, toks):
+                    first[b] = t
+        return first
+
+    # ---- decode -------------------------------------------------------------------------------
+    def _decode_step(self, B: int, splits: int, advance: bool) -> None:
+        self.model.forward(B, self.ids[:B], self.positions[:B], self.slots[:B], self.bm.tables, self.ctx[:B], None, None, B,
+                           self.out_tokens, attn_splits=splits)
+        if advance:
+            ops.decode_advance(self.out_tokens[:B], self.ids[:B], self.positions[:B], self.ctx[:B], self.slots[:B], self.bm.tables,
+                               self.block_size, self.history, self.step_counter)
+
+    def attn_splits_for(self, B: int, max_ctx: int) -> int:
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        want = math.ceil(2 * sms / max(1, B * self.model.nkv))
+        return max(1, min(want, self.model.max_attn_splits, math.ceil(max_ctx / 256)))
+
+    def capture(self, B: int, splits: int, advance: bool) -> torch.cuda.CUDAGraph:
+        """Capture one decode step (all layers, both collectives per layer, sampling) as a graph."""
+        key = (B, splits, advance)
+        if key in self.graphs:
+            return self.graphs[key]
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self._decode_step(B, splits, False)      # eager warm-up: idempotent (no advance)
+            s.synchronize()
+            n0 = ops.launch_count + self.tp.launches
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                self._decode_step(B, splits, advance)
+            self.launches_per_step = ops.launch_count + self.tp.launches - n0
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        self.graphs[key] = g
+        return g
+
+    def _load_decode_inputs(self, B: int, tokens: Sequence[int], lens: Sequence[int]) -> None:
+        """positions = index of the token being fed (= tokens so far - 1 + ... ) for every row."""
+        for b in range(B):
+            pos = lens[b]                     # the fed token sits at position `lens[b]`
+            self.ids_h[b], self.pos_h[b] = tokens[b], pos
+            self.slots_h[b], self.ctx_h[b] = self.bm.slot(b, pos), pos + 1
+        self.ids[:B].copy_(self.ids_h[:B], non_blocking=True)
+        self.positions[:B].copy_(self.pos_h[:B], non_blocking=True)
+        self.slots[:B].copy_(self.slots_h[:B], non_blocking=True)
+        self.ctx[:B].copy_(self.ctx_h[:B], non_blocking=True)
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int, loop: str = "host", use_graph: bool = True,
+                 eos_id: Optional[int] = None) -> List[List[int]]:
+        """Greedy generation.  ``loop="host"``: per-step H2D inputs + D2H tokens (serving shape);
+        ``loop="device"``: steps chained on the device, tokens read back once at the end.
+        EOS is ignored unless ``eos_id`` is given (the reference bench sets ignore_eos)."""
+        B = len(prompts)
+        t0 = time.perf_counter()
+        first = self.prefill(prompts, max_new_tokens)
+        torch.cuda.synchronize(self.device)
+        t1 = time.perf_counter()
+        outs = [[t] for t in first]
+        lens = [len(p) for p in prompts]      # tokens already in the cache per row
+        steps = max_new_tokens - 1
+        if steps <= 0:
+            return outs
+        splits = self.attn_splits_for(B, max(lens) + max_new_tokens)
+        if loop == "device":
+            self._load_decode_inputs(B, first, lens)
+            self.step_counter.zero_()
+            g = self.capture(B, splits, True) if use_graph else None
+            for _ in range(steps):
+                if g is not None:
+                    g.replay()
+                else:
+                    self._decode_step(B, splits, True)
+            torch.cuda.synchronize(self.device)
+            hist = self.history.view(-1)[: steps * B].view(steps, B).cpu()   # the kernel logs rows of B tokens
+            for b in range(B):
+                outs[b].extend(hist[:, b].tolist())
+        else:
+            g = self.capture(B, splits, False) if use_graph else None
+            cur = list(first)
+            done = [False] * B
+            for _ in range(steps):
+                self._load_decode_inputs(B, cur, lens)
+                if g is not None:
+                    g.replay()
+                else:
+                    self._decode_step(B, splits, False)
+                self.out_h[:B].copy_(self.out_tokens[:B], non_blocking=True)
+                torch.cuda.current_stream(self.device).synchronize()
+                cur = self.out_h[:B].tolist()
+                for b in range(B):
+                    lens[b] += 1
+                    if not done[b]:
+                        outs[b].append(cur[b])
+                        if eos_id is not None and cur[b] == eos_id:
+                            done[b] = True
+                if eos_id is not None and all(done):
+                    break
+        t2 = time.perf_counter()
+        self.last_stats = {"prefill_s": t1 - t0, "decode_s": t2 - t1, "decode_steps": steps, "batch": B,
+                           "decode_tok_s": B * steps / max(t2 - t1, 1e-9), "attn_splits": splits,
+                           "launches_per_step": self.launches_per_step}
+        if ops.gemm_error():
+            raise RuntimeError("a GEMM barrier wait gave up on the device (see the kernel's watchdog)")
+        return outs

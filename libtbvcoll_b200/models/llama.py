@@ -1,0 +1,111 @@
+"""Llama-family decoder (Llama-3 8B/70B shapes, Qwen2 with qkv bias) for one tensor-parallel
+rank, built only from the hand-written sm_100a operators and the tbvcoll collectives.
+
+This is the model layer the reference documents but does not ship ("TP=1/2 decode engine:
+weight TP sharding, RoPE, GQA, KV cache, greedy", reports/11_custom_engine.md:10-20), with
+the weight fusions it names (q/k/v -> qkv, gate/up -> gate_up, :38).  Per layer:
+
+    qkv GEMM -> RoPE + KV-cache write -> paged attention -> o_proj GEMM (partial sums)
+    -> all-reduce + residual + RMSNorm (ONE kernel)  -> gate_up GEMM with SiLU-mul epilogue
+    -> down_proj GEMM (partial sums) -> all-reduce + residual + next RMSNorm (ONE kernel)
+
+i.e. 7 launches per layer and the two row-parallel all-reduces the reference's hook
+intercepts (2 per layer; step3b/vllm_tp_bench.py:87-124) never appear as separate kernels.
+All buffers are preallocated so a decode step can be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from .. import ops
+from ..parallel.tp import TPGroup
+from .config import ModelConfig
+
+
+class LlamaTP:
+    def __init__(self, cfg: ModelConfig, tp: TPGroup, weights: Dict[str, torch.Tensor], device, max_tokens: int,
+                 max_batch: int, num_blocks: int, block_size: int = 16, max_attn_splits: int = 16):
+        cfg.check_tp(tp.world)
+        self.cfg, self.tp, self.w, self.device = cfg, tp, weights, torch.device(device)
+        self.block_size, self.num_blocks = block_size, num_blocks
+        self.nq = cfg.num_heads // tp.world
+        self.nkv = cfg.kv_heads_per_rank(tp.world)
+        self.D = cfg.head_dim
+        self.ipr = cfg.intermediate_size // tp.world
+        self.vpr = cfg.vocab_size // tp.world
+        self.max_tokens, self.max_batch, self.max_attn_splits = max_tokens, max_batch, max_attn_splits
+        bf, dev, H = torch.bfloat16, self.device, cfg.hidden_size
+        qkv_dim = (self.nq + 2 * self.nkv) * self.D
+        # activations (row-prefix slices of these are what every call uses)
+        self.h = torch.zeros(max_tokens, H, dtype=bf, device=dev)        # residual stream
+        self.xn = torch.zeros(max_tokens, H, dtype=bf, device=dev)       # normalised input / partial sums
+        self.part = torch.zeros(max_tokens, H, dtype=bf, device=dev)     # partial sums / normalised
+        self.qkv = torch.zeros(max_tokens, qkv_dim, dtype=bf, device=dev)
+        self.attn = torch.zeros(max_tokens, self.nq * self.D, dtype=bf, device=dev)
+        self.act = torch.zeros(max_tokens, self.ipr, dtype=bf, device=dev)
+        self.xl = torch.zeros(max_batch, H, dtype=bf, device=dev)        # rows that get logits
+        self.logits = torch.zeros(max_batch, self.vpr, dtype=bf, device=dev)
+        self.argmax_ws = ops.argmax_workspace(max_batch, dev)
+        self.attn_ws = ops.attn_workspace(max_tokens, self.nq, self.nkv, max_attn_splits, dev)
+        idx_off, rec = ops.cand_layout(max_batch)
+        self.cand = torch.zeros(rec, dtype=torch.uint8, device=dev)
+        self.cand_all = torch.zeros(tp.world, rec, dtype=torch.uint8, device=dev)
+        self.cos_sin = ops.rope_cos_sin(self.D, cfg.max_position, cfg.rope_theta, dev, cfg.rope_scaling)
+        self.scale = 1.0 / math.sqrt(self.D)
+        # paged KV cache, one pair per layer: [num_blocks * block_size, nkv, D]
+        self.k_cache = [torch.zeros(num_blocks * block_size, self.nkv, self.D, dtype=bf, device=dev) for _ in range(cfg.num_layers)]
+        self.v_cache = [torch.zeros(num_blocks * block_size, self.nkv, self.D, dtype=bf, device=dev) for _ in range(cfg.num_layers)]
+
+    # -- one forward pass over T token rows ----------------------------------------------------
+    def forward(self, T: int, ids: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor, block_tables: torch.Tensor,
+                ctx_lens: torch.Tensor, seq_of_query: Optional[torch.Tensor], logit_rows: Optional[torch.Tensor], n_logits: int,
+                out_tokens: torch.Tensor, attn_splits: int = 1) -> torch.Tensor:
+        """ids/positions/slot_mapping/ctx_lens: [T]; logit_rows: int64 [n_logits] rows whose next
+        token is wanted (None = all T rows, decode).  Writes greedy tokens to out_tokens[:n_logits]."""
+        cfg, w, tp = self.cfg, self.w, self.tp
+        assert T <= self.max_tokens and n_logits <= self.max_batch
+        h, xn, part, qkv, attn, act = self.h[:T], self.xn[:T], self.part[:T], self.qkv[:T], self.attn[:T], self.act[:T]
+        q_view = qkv.view(T, self.nq + 2 * self.nkv, self.D)[:, : self.nq]
+        attn_view = attn.view(T, self.nq, self.D)
+
+        ops.embedding(ids, w["embed"], vocab_start=tp.rank * self.vpr, out=h)
+        tp.all_reduce(h)
+        ops.rmsnorm(h, w["layers.0.input_norm"], cfg.rms_eps, out=xn)
+        for l in range(cfg.num_layers):
+            p = f"layers.{l}."
+            ops.gemm(xn, w[p + "qkv.weight"], out=qkv, bias=w.get(p + "qkv.bias"))
+            ops.rope_kv(qkv, positions, self.cos_sin, slot_mapping, self.k_cache[l], self.v_cache[l], self.nq, self.nkv, self.D)
+            ops.paged_attention(q_view, self.k_cache[l], self.v_cache[l], block_tables, ctx_lens, attn_view, self.scale,
+                                self.block_size, seq_of_query=seq_of_query, splits=attn_splits, workspace=self.attn_ws)
+            ops.gemm(attn, w[p + "o.weight"], out=part)
+            tp.all_reduce_add_rmsnorm(part, h, w[p + "post_norm"], cfg.rms_eps)        # part := norm(h), h += sum
+            ops.gemm(part, w[p + "gate_up.weight"], out=act, epi=ops.EPI_SILU_MUL)
+            ops.gemm(act, w[p + "down.weight"], out=xn)
+            nxt = w[f"layers.{l + 1}.input_norm"] if l + 1 < cfg.num_layers else w["norm"]
+            tp.all_reduce_add_rmsnorm(xn, h, nxt, cfg.rms_eps)                          # xn := norm(h) for the next layer
+        if logit_rows is None:
+            xl = xn
+        else:
+            xl = self.xl[:n_logits]
+            torch.index_select(xn, 0, logit_rows, out=xl)
+        logits = self.logits[:n_logits]
+        ops.gemm(xl, w["lm_head"], out=logits)
+        return self.sample_greedy(logits, n_logits, out_tokens)
+
+    def sample_greedy(self, logits: torch.Tensor, n: int, out_tokens: torch.Tensor) -> torch.Tensor:
+        """argmax over the vocab shard, then (TP > 1) an all-gather of the per-rank candidates
+        and a merge: largest value wins, lowest token id on ties — every rank gets the same token."""
+        tp = self.tp
+        idx_off, rec = ops.cand_layout(self.max_batch)
+        vals = self.cand[: n * 4].view(torch.float32)
+        idx = self.cand[idx_off: idx_off + n * 8].view(torch.int64)
+        if tp.world == 1:
+            ops.argmax(logits, self.argmax_ws, 0, vals, out_tokens[:n])
+            return out_tokens
+        ops.argmax(logits, self.argmax_ws, tp.rank * self.vpr, vals, idx)
+        tp.all_gather(self.cand, self.cand_all)
+        ops.argmax_merge_packed(self.cand_all, tp.world, n, out_tokens[:n], max_batch=self.max_batch)
+        return out_tokens

@@ -42,7 +42,9 @@ def lib():
     l.tbv_op_argmax_workspace.argtypes = [I]
     l.tbv_op_argmax_workspace.restype = SZ
     l.tbv_op_argmax.argtypes = [c_vp, I, I, I, LL, c_vp, c_vp, c_vp, c_vp]
-    l.tbv_op_argmax_merge.argtypes = [c_vp, c_vp, I, I, c_vp, c_vp]
+    l.tbv_op_argmax_merge.argtypes = [c_vp, c_vp, I, I, LL, c_vp, c_vp]
+    l.tbv_op_decode_advance.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, c_vp, c_vp, I, c_vp]
+    l.tbv_op_decode_advance.restype = I
     l.tbv_op_attn_workspace.argtypes = [I, I, I, I]
     l.tbv_op_attn_workspace.restype = SZ
     l.tbv_op_paged_attention.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, I, I, I, I, F, c_vp]
@@ -199,13 +201,28 @@ def argmax(logits: torch.Tensor, workspace: torch.Tensor, index_offset: int = 0,
     return out_val, out_idx
 
 
-def argmax_merge(vals: torch.Tensor, idx: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """vals/idx: [world, T] candidates of every rank -> [T] winning indices."""
-    W, T = vals.shape
-    out = torch.empty(T, dtype=torch.int64, device=vals.device) if out is None else out
-    _chk(lib().tbv_op_argmax_merge(_p(vals), _p(idx), W, T, _p(out), _st()), "tbv_op_argmax_merge")
+def cand_layout(T: int):
+    """Byte layout of one rank's greedy candidates: fp32 values, then int64 indices."""
+    idx_off = (T * 4 + 15) // 16 * 16
+    return idx_off, idx_off + T * 8
+
+
+def argmax_merge_packed(gathered: torch.Tensor, world: int, T: int, out: torch.Tensor, max_batch: Optional[int] = None) -> torch.Tensor:
+    """gathered: uint8 [world, rec]; each record is laid out by ``cand_layout(max_batch or T)``
+    and its first T entries are merged."""
+    idx_off, rec = cand_layout(max_batch or T)
+    base = gathered.data_ptr()
+    _chk(lib().tbv_op_argmax_merge(c_vp(base), c_vp(base + idx_off), world, T, rec, _p(out), _st()), "tbv_op_argmax_merge")
     _count()
     return out
+
+
+def decode_advance(next_ids, ids, positions, ctx_lens, slot_mapping, block_tables, block_size, history, step_counter) -> None:
+    B = ids.shape[0]
+    _chk(lib().tbv_op_decode_advance(_p(next_ids), _p(ids), _p(positions), _p(ctx_lens), _p(slot_mapping), _p(block_tables),
+                                     block_tables.shape[1], block_size, B, _p(history), _p(step_counter),
+                                     history.shape[0] if history is not None else 0, _st()), "tbv_op_decode_advance")
+    _count()
 
 
 def attn_workspace(nq_rows: int, nq_heads: int, nkv: int, max_splits: int, device) -> torch.Tensor:

@@ -1,0 +1,90 @@
+"""Tensor-parallel collectives as the model sees them.
+
+``TPGroup`` owns a ``tbvcoll.Comm`` and implements the calls a row-parallel layer makes:
+all-reduce, all-reduce fused with residual-add + RMSNorm, all-gather, reduce-scatter.
+Whenever the library declines a call (returns False: over capacity, unsupported dtype,
+non-contiguous) the group falls back to ``torch.distributed`` exactly like the reference's
+vLLM hook does (step3b/vllm_tp_bench.py:108-124), and counts it.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..tbvcoll import Comm
+
+
+class TPGroup:
+    def __init__(self, rank: int = 0, world: int = 1, comm: Optional[Comm] = None, fallback_group=None,
+                 fused_norm_max_bytes: int = 1 << 20):
+        self.rank, self.world, self.comm = rank, world, comm
+        self.fallback_group = fallback_group
+        self.fused_norm_max_bytes = fused_norm_max_bytes
+        self.calls = 0
+        self.fallbacks = 0
+        self.launches = 0   # collective kernels launched (for the bench's gpu_launches claim)
+
+    # -- plain collectives ---------------------------------------------------------------
+    def _fallback_all_reduce(self, x: torch.Tensor) -> None:
+        self.fallbacks += 1
+        if self.fallback_group is None and not (torch.distributed.is_available() and torch.distributed.is_initialized()):
+            raise RuntimeError("tbvcoll declined the call and no torch.distributed fallback is initialised")
+        torch.distributed.all_reduce(x, group=self.fallback_group)
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """In place SUM."""
+        if self.world == 1:
+            return x
+        self.calls += 1
+        if self.comm is not None and self.comm.all_reduce(x):
+            self.launches += 1
+            return x
+        self._fallback_all_reduce(x)
+        return x
+
+    def all_gather(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            out.view(-1).copy_(x.view(-1))
+            return out
+        self.calls += 1
+        if self.comm is not None and self.comm.all_gather(x, out):
+            self.launches += 1
+            return out
+        self.fallbacks += 1
+        torch.distributed.all_gather_into_tensor(out, x, group=self.fallback_group)
+        return out
+
+    def reduce_scatter(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            out.view(-1).copy_(x.view(-1))
+            return out
+        self.calls += 1
+        if self.comm is not None and self.comm.reduce_scatter(x, out):
+            self.launches += 1
+            return out
+        self.fallbacks += 1
+        torch.distributed.reduce_scatter_tensor(out, x, group=self.fallback_group)
+        return out
+
+    # -- fused: all-reduce + residual + RMSNorm ---------------------------------------------
+    def all_reduce_add_rmsnorm(self, x: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor, eps: float):
+        """x: this rank's partial sums [T, H].  Afterwards ``residual`` holds
+        h = bf16(sum_ranks x) + residual and ``x`` holds RMSNorm(h) * gamma.  One kernel when the
+        message is small enough for the one-shot fused kernel, else all-reduce + add-norm."""
+        if self.world == 1:
+            ops.add_rmsnorm(x, residual, gamma, eps)
+            self.launches += 1
+            return x, residual
+        nbytes = x.numel() * x.element_size()
+        if self.comm is not None and nbytes <= self.fused_norm_max_bytes:
+            self.calls += 1
+            if self.comm.all_reduce_rmsnorm(x, residual, gamma, eps):
+                self.launches += 1
+                return x, residual
+            self.calls -= 1
+        self.all_reduce(x)
+        ops.add_rmsnorm(x, residual, gamma, eps)
+        self.launches += 1
+        return x, residual

@@ -118,9 +118,16 @@ def test_silu_mul_embedding_argmax(ops):
         v, i = ops.argmax(logits, ws, index_offset=1000)
         wv, wi = ref.argmax_first(logits)
         assert torch.equal(i, wi + 1000) and torch.equal(v, wv)
-    vals = torch.tensor([[1.0, 5.0], [3.0, 5.0], [2.0, 1.0]], device=DEV)
-    idx = torch.tensor([[10, 70], [20, 30], [5, 6]], device=DEV)
-    assert ops.argmax_merge(vals, idx).tolist() == [20, 30]
+    T, world = 2, 3
+    idx_off, rec = ops.cand_layout(T)
+    packed = torch.zeros(world, rec, dtype=torch.uint8, device=DEV)
+    vals = [[1.0, 5.0], [3.0, 5.0], [2.0, 1.0]]
+    idx = [[10, 70], [20, 30], [5, 6]]
+    for r in range(world):
+        packed[r, : T * 4] = torch.tensor(vals[r], dtype=torch.float32).view(torch.uint8).to(DEV)
+        packed[r, idx_off: idx_off + T * 8] = torch.tensor(idx[r], dtype=torch.int64).view(torch.uint8).to(DEV)
+    out = torch.empty(T, dtype=torch.int64, device=DEV)
+    assert ops.argmax_merge_packed(packed, world, T, out).tolist() == [20, 30]
 
 
 @pytest.mark.parametrize("nq,nkv,splits", [(8, 2, 1), (8, 8, 3), (4, 2, 4), (16, 2, 2)])
