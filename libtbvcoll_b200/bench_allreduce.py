@@ -1,0 +1,103 @@
+#!/usr/bin/env python3
+"""All-reduce latency / bandwidth sweep: tbvcoll (one-shot, two-shot, NVLS, auto) vs NCCL.
+
+bf16 [tokens, 4096], tokens in {1, 2, 4, ..., 8192} (8 KB - 64 MB), values N(0,1); every
+result of this library is checked bit for bit against a fixed-order fp32 oracle before it is
+timed.  Timing is stream-ordered like the reference's microbenchmark ("stream-ordered" mode of
+step4/allreduce2.cpp:188-200 and step4/test_tbvcoll.py:52-63): calls are issued back to back
+without host synchronisation, device time is taken with CUDA events around groups of calls,
+the p50 over groups is reported, and the maximum over ranks is what counts.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        --master-port 29511 -m libtbvcoll_b200.bench_allreduce [--max-tokens 8192] [--json out.json]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+import torch.distributed as dist
+
+
+def p50_us(fn, inner, groups, world):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(groups)]
+    for a, b in ev:
+        a.record()
+        for _ in range(inner):
+            fn()
+        b.record()
+    torch.cuda.synchronize()
+    us = [a.elapsed_time(b) * 1e3 / inner for a, b in ev]
+    t = torch.tensor([statistics.median(us), sorted(us)[int(0.99 * (len(us) - 1))]], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0]), float(t[1])
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--max-tokens", type=int, default=8192)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--json", default="")
+    ap.add_argument("--algos", default="auto,oneshot,twoshot,nvls")
+    args = ap.parse_args()
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", os.environ["RANK"]))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from libtbvcoll_b200.tbvcoll import Comm
+    cap = args.max_tokens * args.hidden * 2
+    port = int(os.environ.get("MASTER_PORT", "29500")) + 103
+    comm = Comm(rank, world, local, "127.0.0.1", port, cap_bytes=cap)
+    algos = [a for a in args.algos.split(",") if a != "nvls" or comm.has_nvls()]
+    rows = []
+    tokens = 1
+    while tokens <= args.max_tokens:
+        n = tokens * args.hidden
+        nbytes = n * 2
+        g = torch.Generator(device="cpu").manual_seed(1000 + rank)
+        x = torch.randn(n, generator=g).to(torch.bfloat16).cuda()
+        allx = []
+        for r in range(world):
+            gr = torch.Generator(device="cpu").manual_seed(1000 + r)
+            allx.append(torch.randn(n, generator=gr).to(torch.bfloat16).cuda())
+        acc = allx[0].float()
+        for t in allx[1:]:
+            acc = acc + t.float()
+        want = acc.to(torch.bfloat16)
+        del allx, acc
+        out = torch.empty_like(x)
+        inner = 20 if nbytes <= (1 << 20) else 5
+        groups = 40 if nbytes <= (4 << 20) else 12
+        row = {"tokens": tokens, "bytes": nbytes}
+        for algo in algos:
+            comm.set_algo(algo)
+            assert comm.all_reduce(x, out)
+            torch.cuda.synchronize()
+            exact = bool(torch.equal(out, want))
+            if algo != "nvls":
+                assert exact, f"{algo} not bit-exact at {nbytes} bytes"
+            p50, p99 = p50_us(lambda: comm.all_reduce(x, out), inner, groups, world)
+            row[algo] = {"p50_us": round(p50, 2), "p99_us": round(p99, 2), "exact_vs_fixed_order_oracle": exact,
+                         "busbw_GBs": round(2 * (world - 1) / world * nbytes / p50 / 1e3, 1)}
+        y = x.clone()
+        p50, p99 = p50_us(lambda: dist.all_reduce(y), inner, groups, world)
+        row["nccl"] = {"p50_us": round(p50, 2), "p99_us": round(p99, 2), "busbw_GBs": round(2 * (world - 1) / world * nbytes / p50 / 1e3, 1)}
+        rows.append(row)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+        tokens *= 2
+    if rank == 0 and args.json:
+        with open(args.json, "w") as f:
+            json.dump({"world": world, "dtype": "bf16", "hidden": args.hidden, "nvls": comm.has_nvls(), "rows": rows}, f, indent=1)
+    comm.destroy()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -22,6 +22,7 @@
 
 #include "comm.h"
 #include "ops/ops.h"
+#include "pdl.cuh"
 
 using namespace tbv;
 
@@ -161,28 +162,38 @@ struct LocalPtrs {
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(512) k_ar_oneshot(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
   __shared__ unsigned long long sh_seq;
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();  // before the device sequence number or any input is read
   ar_oneshot_body<T, VEC>(c, in, out, nbytes, gridDim.x, blockIdx.x, &sh_seq);
 }
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(512) k_ar_oneshot_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p, size_t nbytes) {
   __shared__ unsigned long long sh_seq;
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();  // before the device sequence number or any input is read
   ar_oneshot_body<T, VEC>(ctxs[blockIdx.y], static_cast<const T*>(p.in[blockIdx.y]), static_cast<T*>(p.out[blockIdx.y]),
                           nbytes, gridDim.x, blockIdx.x, &sh_seq);
 }
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(512) k_ar_twoshot(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes, int mode) {
   __shared__ unsigned long long sh_seq;
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();  // before the device sequence number or any input is read
   ar_twoshot_body<T, VEC>(c, in, out, nbytes, gridDim.x, blockIdx.x, mode, &sh_seq);
 }
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(512) k_ar_twoshot_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p, size_t nbytes, int mode) {
   __shared__ unsigned long long sh_seq;
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();  // before the device sequence number or any input is read
   ar_twoshot_body<T, VEC>(ctxs[blockIdx.y], static_cast<const T*>(p.in[blockIdx.y]), static_cast<T*>(p.out[blockIdx.y]),
                           nbytes, gridDim.x, blockIdx.x, mode, &sh_seq);
 }
 template <typename T>
 __global__ void __launch_bounds__(512) k_ar_nvls(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
   __shared__ unsigned long long sh_seq;
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();  // before the device sequence number or any input is read
   ar_nvls_body<T>(c, in, out, nbytes, gridDim.x, blockIdx.x, &sh_seq);
 }
 __global__ void __launch_bounds__(1024) k_ar_rmsnorm(const __grid_constant__ RankCtx c, const __nv_bfloat16* x,
@@ -190,12 +201,16 @@ __global__ void __launch_bounds__(1024) k_ar_rmsnorm(const __grid_constant__ Ran
                                                      __nv_bfloat16* residual_out, __nv_bfloat16* y, int tokens, int hidden,
                                                      float eps) {
   __shared__ unsigned long long sh_seq;
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();  // before the device sequence number or any input is read
   __shared__ float sh_red[32];
   ar_rmsnorm_body(c, x, residual, gamma, residual_out, y, tokens, hidden, eps, gridDim.x, blockIdx.x, &sh_seq, sh_red);
 }
 __global__ void __launch_bounds__(1024) k_ar_rmsnorm_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p,
                                                            const __nv_bfloat16* gamma, int tokens, int hidden, float eps) {
   __shared__ unsigned long long sh_seq;
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();  // before the device sequence number or any input is read
   __shared__ float sh_red[32];
   const int r = blockIdx.y;
   ar_rmsnorm_body(ctxs[r], static_cast<const __nv_bfloat16*>(p.in[r]), static_cast<const __nv_bfloat16*>(p.aux[r]), gamma,
@@ -559,16 +574,13 @@ static cudaError_t launch_ar_t(tbv_comm* c, int algo, bool vec, int nchan, int t
   const RankCtx& x = c->ranks[0].ctx;
   const T* i = static_cast<const T*>(in);
   T* o = static_cast<T*>(out);
-  if (algo == TBV_ALGO_NVLS) {
-    k_ar_nvls<T><<<nchan, threads, 0, st>>>(x, i, o, nbytes);
-  } else if (algo == TBV_ALGO_ONESHOT) {
-    if (vec) k_ar_oneshot<T, true><<<nchan, threads, 0, st>>>(x, i, o, nbytes);
-    else k_ar_oneshot<T, false><<<nchan, threads, 0, st>>>(x, i, o, nbytes);
-  } else {
-    if (vec) k_ar_twoshot<T, true><<<nchan, threads, 0, st>>>(x, i, o, nbytes, mode);
-    else k_ar_twoshot<T, false><<<nchan, threads, 0, st>>>(x, i, o, nbytes, mode);
-  }
-  return cudaGetLastError();
+  const dim3 g(nchan), b(threads);
+  if (algo == TBV_ALGO_NVLS) return pdl::launch(k_ar_nvls<T>, g, b, 0, st, 1, x, i, o, nbytes);
+  if (algo == TBV_ALGO_ONESHOT)
+    return vec ? pdl::launch(k_ar_oneshot<T, true>, g, b, 0, st, 1, x, i, o, nbytes)
+               : pdl::launch(k_ar_oneshot<T, false>, g, b, 0, st, 1, x, i, o, nbytes);
+  return vec ? pdl::launch(k_ar_twoshot<T, true>, g, b, 0, st, 1, x, i, o, nbytes, mode)
+             : pdl::launch(k_ar_twoshot<T, false>, g, b, 0, st, 1, x, i, o, nbytes, mode);
 }
 
 template <typename T>
@@ -684,12 +696,10 @@ static int gpu_ar_rmsnorm(tbv_comm* c, const void* const* xs, const void* const*
   } else if (c->world == 1) {
     return TBV_FALLBACK;  // nothing to reduce: the caller uses the plain fused add+norm op
   } else {
-    k_ar_rmsnorm<<<nchan, threads, 0, st>>>(c->ranks[0].ctx, static_cast<const __nv_bfloat16*>(xs[0]),
-                                            static_cast<const __nv_bfloat16*>(residuals[0]),
-                                            static_cast<const __nv_bfloat16*>(gamma),
-                                            static_cast<__nv_bfloat16*>(residual_outs[0]),
-                                            static_cast<__nv_bfloat16*>(ys[0]), tokens, hidden, eps);
-    e = cudaGetLastError();
+    e = pdl::launch(k_ar_rmsnorm, dim3(nchan), dim3(threads), 0, st, 1, c->ranks[0].ctx,
+                    static_cast<const __nv_bfloat16*>(xs[0]), static_cast<const __nv_bfloat16*>(residuals[0]),
+                    static_cast<const __nv_bfloat16*>(gamma), static_cast<__nv_bfloat16*>(residual_outs[0]),
+                    static_cast<__nv_bfloat16*>(ys[0]), tokens, hidden, eps);
   }
   if (e != cudaSuccess) {
     c->errmsg = std::string("kernel launch: ") + cudaGetErrorString(e);

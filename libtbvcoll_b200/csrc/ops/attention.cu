@@ -13,12 +13,14 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "../pdl.cuh"
+
 namespace {
 
 constexpr int kD = 128;        // head_dim
 constexpr int kThreads = 128;  // 8 half-warps
 constexpr int kHW = kThreads / 16;
-constexpr int kU = 2;          // tokens in flight per half-warp
+constexpr int kU = 4;          // tokens in flight per half-warp (8 x 16-byte loads per thread)
 constexpr float kNegBig = -1e30f;
 
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
@@ -45,6 +47,8 @@ struct AttnParams {
 
 template <int G>
 __global__ void __launch_bounds__(kThreads) k_paged_attn(const AttnParams p) {
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
   const int qi = blockIdx.x, h = blockIdx.y, sp = blockIdx.z;
   const int hw = threadIdx.x >> 4, l16 = threadIdx.x & 15;
   const int ctx = p.ctx_lens[qi];
@@ -223,14 +227,15 @@ int tbv_op_paged_attention(const void* q, const void* k_cache, const void* v_cac
   p.ldq = ldq; p.ldo = ldo; p.nkv = nkv; p.block_size = block_size; p.max_blocks = max_blocks; p.splits = splits;
   dim3 grid(nq_rows, nkv, splits);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaSuccess;
   switch (G) {
-    case 1: k_paged_attn<1><<<grid, kThreads, 0, st>>>(p); break;
-    case 2: k_paged_attn<2><<<grid, kThreads, 0, st>>>(p); break;
-    case 4: k_paged_attn<4><<<grid, kThreads, 0, st>>>(p); break;
-    case 8: k_paged_attn<8><<<grid, kThreads, 0, st>>>(p); break;
+    case 1: e = pdl::launch(k_paged_attn<1>, grid, dim3(kThreads), 0, st, 1, p); break;
+    case 2: e = pdl::launch(k_paged_attn<2>, grid, dim3(kThreads), 0, st, 1, p); break;
+    case 4: e = pdl::launch(k_paged_attn<4>, grid, dim3(kThreads), 0, st, 1, p); break;
+    case 8: e = pdl::launch(k_paged_attn<8>, grid, dim3(kThreads), 0, st, 1, p); break;
     default: return -2;
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  return e == cudaSuccess ? 0 : -1;
 }
 
 }  // extern "C"

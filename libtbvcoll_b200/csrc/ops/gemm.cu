@@ -295,20 +295,10 @@ int tbv_op_gemm(const void* w, const void* x, void* y, const void* bias, int M, 
     }
     g_attr_done = true;
   }
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((M + 127) / 128, (N + bn - 1) / bn, splits);
-  cfg.blockDim = dim3(gemm::kThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = splits;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = epi == kEpiSiluMul ? cudaLaunchKernelEx(&cfg, k_gemm<kEpiSiluMul>, tmA, tmB, p)
-                                     : cudaLaunchKernelEx(&cfg, k_gemm<kEpiStore>, tmA, tmB, p);
+  const dim3 grid((M + 127) / 128, (N + bn - 1) / bn, splits);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = epi == kEpiSiluMul ? pdl::launch(k_gemm<kEpiSiluMul>, grid, dim3(gemm::kThreads), smem, st, splits, tmA, tmB, p)
+                                     : pdl::launch(k_gemm<kEpiStore>, grid, dim3(gemm::kThreads), smem, st, splits, tmA, tmB, p);
   if (e != cudaSuccess) {
     fprintf(stderr, "[tbvops] gemm launch failed: %s (M=%d N=%d K=%d bn=%d splits=%d stages=%d)\n", cudaGetErrorString(e), M, N, K,
             bn, splits, stages);

@@ -12,6 +12,7 @@
 // CTAs of one cluster cover disjoint K ranges and reduce through distributed shared
 // memory in a fixed order (deterministic).
 #pragma once
+#include "../pdl.cuh"
 #include "sm100.cuh"
 
 namespace gemm {
@@ -80,6 +81,7 @@ __device__ __forceinline__ uint8_t* mainloop(const CUtensorMap* tmA, const CUten
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl::launch_dependents();  // the next kernel may set itself up while this one computes
   const uint32_t tmem_d = s.tmem_base;
   volatile int* abortp = &s.abort_flag;
 
@@ -88,7 +90,19 @@ __device__ __forceinline__ uint8_t* mainloop(const CUtensorMap* tmA, const CUten
     const uint64_t pol_w = policy_evict_first();  // weights are read once
     const uint64_t pol_x = policy_evict_last();   // activations are re-read by every M tile
     int issued = 0;
-    for (int i = 0; i < nkb; i++) {
+    // Weights are never written by any kernel: start streaming them into the ring before the
+    // preceding kernel has finished, then wait for it and fetch the activations.
+    const int pre = nkb < p.stages ? nkb : p.stages;
+    for (int i = 0; i < pre; i++) {
+      const uint32_t fb = smem_u32(&s.full[i]);
+      mbar_expect_tx(fb, kATileBytes + b_tile_bytes);
+      tma_load_2d_hint(a_base + i * kATileBytes, tmA, (kb0 + i) * kBK, m0, fb, pol_w);
+    }
+    pdl::grid_dependency_wait();
+    for (int i = 0; i < pre; i++)
+      tma_load_2d_hint(b_base + i * b_tile_bytes, tmB, (kb0 + i) * kBK, n0, smem_u32(&s.full[i]), pol_x);
+    issued = pre;
+    for (int i = pre; i < nkb; i++) {
       const int st = i % p.stages;
       const uint32_t ph = uint32_t(i / p.stages) & 1u;
       if (!mbar_wait(smem_u32(&s.empty[st]), ph ^ 1u, abortp, p.limit_ns)) break;

@@ -10,6 +10,8 @@
 #include <float.h>
 #include <stdint.h>
 
+#include "../pdl.cuh"
+
 namespace {
 
 __device__ __forceinline__ float bfr(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
@@ -21,17 +23,26 @@ __device__ __forceinline__ float bfr(float x) { return __bfloat162float(__float2
 __global__ void k_rope_kv(__nv_bfloat16* qkv, const int* __restrict__ positions, const float* __restrict__ cos_sin,
                           const long long* __restrict__ slot_mapping, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                           int nq, int nkv, int D, int max_pos) {
-  const int t = blockIdx.x;
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
+  // one CTA per (token, head): q heads and k heads rotate, v heads are copied to the cache
+  const int t = blockIdx.x, h = blockIdx.y;
   const int half = D / 2;
+  __nv_bfloat16* row = qkv + size_t(t) * (nq + 2 * nkv) * D;
+  const long long slot = slot_mapping ? slot_mapping[t] : -1;
+  if (h >= nq + nkv) {
+    if (slot >= 0) {
+      const uint4* vs = reinterpret_cast<const uint4*>(row + h * D);
+      uint4* vd = reinterpret_cast<uint4*>(v_cache + (size_t(slot) * nkv + (h - nq - nkv)) * D);
+      for (int i = threadIdx.x; i < D / 8; i += blockDim.x) vd[i] = vs[i];
+    }
+    return;
+  }
   int pos = positions[t];
   pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
   const float* cs = cos_sin + size_t(pos) * D;  // [cos(0..half-1), sin(0..half-1)]
-  __nv_bfloat16* row = qkv + size_t(t) * (nq + 2 * nkv) * D;
-  const long long slot = slot_mapping ? slot_mapping[t] : -1;
-  const int nrot = (nq + nkv) * half;
-  for (int i = threadIdx.x; i < nrot; i += blockDim.x) {
-    const int h = i / half, d = i % half;
-    __nv_bfloat16* v = row + h * D;
+  __nv_bfloat16* v = row + h * D;
+  for (int d = threadIdx.x; d < half; d += blockDim.x) {
     const float c = bfr(cs[d]), s = bfr(cs[half + d]);
     const float x1 = __bfloat162float(v[d]), x2 = __bfloat162float(v[d + half]);
     const float o1 = bfr(bfr(x1 * c) + bfr(-x2 * s));
@@ -45,15 +56,12 @@ __global__ void k_rope_kv(__nv_bfloat16* qkv, const int* __restrict__ positions,
       kc[d + half] = b2;
     }
   }
-  if (slot >= 0) {
-    const uint4* vs = reinterpret_cast<const uint4*>(row + (nq + nkv) * D);
-    uint4* vd = reinterpret_cast<uint4*>(v_cache + size_t(slot) * nkv * D);
-    for (int i = threadIdx.x; i < nkv * D / 8; i += blockDim.x) vd[i] = vs[i];
-  }
 }
 
 // out[t, i] = bf16( bf16(silu(gate)) * up ),  x: [T, 2*I] = [gate | up]
 __global__ void k_silu_mul(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int I) {
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
   const size_t t = blockIdx.y;
   const int i8 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i8 >= I) return;
@@ -74,6 +82,8 @@ __global__ void k_silu_mul(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* _
 // out[t] = table[ids[t] - vocab_start] if in [vocab_start, vocab_end) else 0  (vocab-parallel shard)
 __global__ void k_embedding(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                             __nv_bfloat16* __restrict__ out, int hidden, long long vocab_start, long long vocab_end) {
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
   const size_t t = blockIdx.x;
   const long long id = ids[t];
   const bool mine = id >= vocab_start && id < vocab_end;
@@ -88,6 +98,8 @@ __global__ void k_embedding(const long long* __restrict__ ids, const __nv_bfloat
 // torch.argmax.
 __global__ void k_argmax(const __nv_bfloat16* __restrict__ logits, int vocab, int ld, long long index_offset,
                          float* part_val, long long* part_idx, unsigned* tickets, float* out_val, long long* out_idx) {
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
   const int row = blockIdx.y, nblk = gridDim.x;
   const int per = (vocab + nblk - 1) / nblk;
   const int v0 = blockIdx.x * per, v1 = min(vocab, v0 + per);
@@ -137,6 +149,8 @@ __global__ void k_argmax(const __nv_bfloat16* __restrict__ logits, int vocab, in
 // largest value, lowest index on ties.  vals/idx: [world, T].
 __global__ void k_argmax_merge(const float* __restrict__ vals, const long long* __restrict__ idx, int world, int T,
                                long long rank_stride_bytes, long long* __restrict__ out) {
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T) return;
   float b = vals[t];
@@ -155,6 +169,8 @@ __global__ void k_argmax_merge(const float* __restrict__ vals, const long long* 
 __global__ void k_decode_advance(const long long* __restrict__ next_ids, long long* ids, int* positions, int* ctx_lens,
                                  long long* slot_mapping, const int* __restrict__ block_tables, int max_blocks, int block_size,
                                  int batch, long long* history, int* step_counter, int max_steps) {
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   const int step = *step_counter;
   if (b < batch) {
@@ -179,43 +195,42 @@ int tbv_op_decode_advance(const void* next_ids, void* ids, void* positions, void
                           const void* block_tables, int max_blocks, int block_size, int batch, void* history, void* step_counter,
                           int max_steps, void* stream) {
   if (batch <= 0 || batch > 1024) return -2;  // one CTA: the step counter is read before it is bumped
-  k_decode_advance<<<1, (batch + 31) / 32 * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const long long*>(next_ids), static_cast<long long*>(ids), static_cast<int*>(positions),
-      static_cast<int*>(ctx_lens), static_cast<long long*>(slot_mapping), static_cast<const int*>(block_tables), max_blocks,
-      block_size, batch, static_cast<long long*>(history), static_cast<int*>(step_counter), max_steps);
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  cudaError_t e = pdl::launch(k_decode_advance, dim3(1), dim3((batch + 31) / 32 * 32), 0, static_cast<cudaStream_t>(stream), 1,
+                              static_cast<const long long*>(next_ids), static_cast<long long*>(ids), static_cast<int*>(positions),
+                              static_cast<int*>(ctx_lens), static_cast<long long*>(slot_mapping),
+                              static_cast<const int*>(block_tables), max_blocks, block_size, batch,
+                              static_cast<long long*>(history), static_cast<int*>(step_counter), max_steps);
+  return e == cudaSuccess ? 0 : -1;
 }
 
 int tbv_op_rope_kv(void* qkv, const void* positions, const void* cos_sin, const void* slot_mapping, void* k_cache, void* v_cache,
                    int tokens, int nq, int nkv, int D, int max_pos, void* stream) {
   if (tokens <= 0) return 0;
   if (D % 16) return -2;
-  int threads = (nq + nkv) * D / 2;
-  threads = threads > 512 ? 512 : ((threads + 31) / 32 * 32);
-  k_rope_kv<<<tokens, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16*>(qkv), static_cast<const int*>(positions), static_cast<const float*>(cos_sin),
-      static_cast<const long long*>(slot_mapping), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), nq,
-      nkv, D, max_pos);
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  cudaError_t e = pdl::launch(k_rope_kv, dim3(tokens, nq + 2 * nkv), dim3(D / 2), 0, static_cast<cudaStream_t>(stream), 1,
+                              static_cast<__nv_bfloat16*>(qkv), static_cast<const int*>(positions), static_cast<const float*>(cos_sin),
+                              static_cast<const long long*>(slot_mapping), static_cast<__nv_bfloat16*>(k_cache),
+                              static_cast<__nv_bfloat16*>(v_cache), nq, nkv, D, max_pos);
+  return e == cudaSuccess ? 0 : -1;
 }
 
 int tbv_op_silu_mul(const void* x, void* out, int tokens, int inter, void* stream) {
   if (tokens <= 0) return 0;
   if (inter % 8) return -2;
   dim3 grid((inter / 8 + 255) / 256, tokens);
-  k_silu_mul<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x),
-                                                                   static_cast<__nv_bfloat16*>(out), inter);
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  cudaError_t e = pdl::launch(k_silu_mul, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), 1,
+                              static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), inter);
+  return e == cudaSuccess ? 0 : -1;
 }
 
 int tbv_op_embedding(const void* ids, const void* table, void* out, int tokens, int hidden, long long vocab_start,
                      long long vocab_end, void* stream) {
   if (tokens <= 0) return 0;
   if (hidden % 8) return -2;
-  k_embedding<<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const long long*>(ids),
-                                                                      static_cast<const __nv_bfloat16*>(table),
-                                                                      static_cast<__nv_bfloat16*>(out), hidden, vocab_start, vocab_end);
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  cudaError_t e = pdl::launch(k_embedding, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream), 1,
+                              static_cast<const long long*>(ids), static_cast<const __nv_bfloat16*>(table),
+                              static_cast<__nv_bfloat16*>(out), hidden, vocab_start, vocab_end);
+  return e == cudaSuccess ? 0 : -1;
 }
 
 // workspace layout (caller-provided scratch, >= tbv_op_argmax_workspace(tokens) bytes, zeroed once):
@@ -232,19 +247,19 @@ int tbv_op_argmax(const void* logits, int tokens, int vocab, int ld, long long i
   unsigned* tickets = reinterpret_cast<unsigned*>(ws);
   float* pv = reinterpret_cast<float*>(ws + ((size_t(tokens) * 4 + 255) & ~size_t(255)));
   long long* pi = reinterpret_cast<long long*>(reinterpret_cast<char*>(pv) + size_t(tokens) * 64 * 4);
-  k_argmax<<<dim3(nblk, tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(logits), vocab, ld, index_offset, pv, pi, tickets, static_cast<float*>(out_val),
-      static_cast<long long*>(out_idx));
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  cudaError_t e = pdl::launch(k_argmax, dim3(nblk, tokens), dim3(256), 0, static_cast<cudaStream_t>(stream), 1,
+                              static_cast<const __nv_bfloat16*>(logits), vocab, ld, index_offset, pv, pi, tickets,
+                              static_cast<float*>(out_val), static_cast<long long*>(out_idx));
+  return e == cudaSuccess ? 0 : -1;
 }
 // vals / idx point at rank 0's candidates; rank r's are rank_stride_bytes further on.
 int tbv_op_argmax_merge(const void* vals, const void* idx, int world, int tokens, long long rank_stride_bytes, void* out,
                         void* stream) {
   if (tokens <= 0) return 0;
-  k_argmax_merge<<<(tokens + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const float*>(vals), static_cast<const long long*>(idx), world, tokens, rank_stride_bytes,
-      static_cast<long long*>(out));
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  cudaError_t e = pdl::launch(k_argmax_merge, dim3((tokens + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream), 1,
+                              static_cast<const float*>(vals), static_cast<const long long*>(idx), world, tokens, rank_stride_bytes,
+                              static_cast<long long*>(out));
+  return e == cudaSuccess ? 0 : -1;
 }
 
 }  // extern "C"

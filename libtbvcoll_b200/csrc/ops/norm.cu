@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 
 #include "../ar_device.cuh"
+#include "../pdl.cuh"
 #include "ops.h"
 
 using namespace tbv;
@@ -20,6 +21,8 @@ __global__ void __launch_bounds__(1024) k_rmsnorm(const __nv_bfloat16* __restric
                                                   const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* residual_out,
                                                   __nv_bfloat16* y, int hidden, float eps) {
   __shared__ float sh[32];
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
   const int upr = hidden / 8;
   const size_t row = blockIdx.x;
   float h[kNormMaxUnits][8];
@@ -46,20 +49,20 @@ extern "C" {
 // y = RMSNorm(x) * gamma.  x, y: [tokens, hidden] bf16 contiguous; hidden % 8 == 0, hidden <= 32768.
 int tbv_op_rmsnorm(const void* x, const void* gamma, void* y, int tokens, int hidden, float eps, void* stream) {
   if (hidden % 8 || hidden > 8 * kNormMaxUnits * 1024 || tokens <= 0) return -2;
-  k_rmsnorm<false><<<tokens, tbvops::norm_threads(hidden), 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), nullptr, static_cast<const __nv_bfloat16*>(gamma), nullptr,
-      static_cast<__nv_bfloat16*>(y), hidden, eps);
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  cudaError_t e = pdl::launch(k_rmsnorm<false>, dim3(tokens), dim3(tbvops::norm_threads(hidden)), 0, static_cast<cudaStream_t>(stream), 1,
+                              static_cast<const __nv_bfloat16*>(x), nullptr, static_cast<const __nv_bfloat16*>(gamma), nullptr,
+                              static_cast<__nv_bfloat16*>(y), hidden, eps);
+  return e == cudaSuccess ? 0 : -1;
 }
 // h = bf16(x + residual); residual_out = h; y = RMSNorm(h) * gamma.  Aliasing residual_out == residual
 // and y == x is allowed.
 int tbv_op_add_rmsnorm(const void* x, const void* residual, const void* gamma, void* residual_out, void* y, int tokens,
                        int hidden, float eps, void* stream) {
   if (hidden % 8 || hidden > 8 * kNormMaxUnits * 1024 || tokens <= 0) return -2;
-  k_rmsnorm<true><<<tokens, tbvops::norm_threads(hidden), 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
-      static_cast<const __nv_bfloat16*>(gamma), static_cast<__nv_bfloat16*>(residual_out), static_cast<__nv_bfloat16*>(y),
-      hidden, eps);
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  cudaError_t e = pdl::launch(k_rmsnorm<true>, dim3(tokens), dim3(tbvops::norm_threads(hidden)), 0, static_cast<cudaStream_t>(stream), 1,
+                              static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
+                              static_cast<const __nv_bfloat16*>(gamma), static_cast<__nv_bfloat16*>(residual_out),
+                              static_cast<__nv_bfloat16*>(y), hidden, eps);
+  return e == cudaSuccess ? 0 : -1;
 }
 }

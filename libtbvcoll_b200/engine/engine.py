@@ -34,7 +34,7 @@ from .kv_cache import BlockManager
 class Engine:
     def __init__(self, cfg: ModelConfig, tp: Optional[TPGroup] = None, device="cuda:0", weights: Optional[Dict[str, torch.Tensor]] = None,
                  source=None, seed: int = 0, max_batch: int = 8, max_seq_len: int = 1024, block_size: int = 16,
-                 prefill_chunk: int = 2048, max_attn_splits: int = 16):
+                 prefill_chunk: int = 2048, max_attn_splits: int = 32):
         self.cfg = cfg
         self.tp = tp or TPGroup()
         self.device = torch.device(device)
@@ -109,8 +109,9 @@ class Engine:
 
     def attn_splits_for(self, B: int, max_ctx: int) -> int:
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        want = math.ceil(2 * sms / max(1, B * self.model.nkv))
-        return max(1, min(want, self.model.max_attn_splits, math.ceil(max_ctx / 256)))
+        # enough CTAs to fill the GPU about four times over, but at least 64 cached tokens each
+        want = math.ceil(4 * sms / max(1, B * self.model.nkv))
+        return max(1, min(want, self.model.max_attn_splits, math.ceil(max_ctx / 64)))
 
     def capture(self, B: int, splits: int, advance: bool) -> torch.cuda.CUDAGraph:
         """Capture one decode step (all layers, both collectives per layer, sampling) as a graph."""

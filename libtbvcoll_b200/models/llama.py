@@ -27,7 +27,7 @@ from .config import ModelConfig
 
 class LlamaTP:
     def __init__(self, cfg: ModelConfig, tp: TPGroup, weights: Dict[str, torch.Tensor], device, max_tokens: int,
-                 max_batch: int, num_blocks: int, block_size: int = 16, max_attn_splits: int = 16):
+                 max_batch: int, num_blocks: int, block_size: int = 16, max_attn_splits: int = 32):
         cfg.check_tp(tp.world)
         self.cfg, self.tp, self.w, self.device = cfg, tp, weights, torch.device(device)
         self.block_size, self.num_blocks = block_size, num_blocks
@@ -49,7 +49,7 @@ class LlamaTP:
         self.xl = torch.zeros(max_batch, H, dtype=bf, device=dev)        # rows that get logits
         self.logits = torch.zeros(max_batch, self.vpr, dtype=bf, device=dev)
         self.argmax_ws = ops.argmax_workspace(max_batch, dev)
-        self.attn_ws = ops.attn_workspace(max_tokens, self.nq, self.nkv, max_attn_splits, dev)
+        self.attn_ws = ops.attn_workspace(max_batch, self.nq, self.nkv, max_attn_splits, dev)   # kv splits are a decode-only device
         idx_off, rec = ops.cand_layout(max_batch)
         self.cand = torch.zeros(rec, dtype=torch.uint8, device=dev)
         self.cand_all = torch.zeros(tp.world, rec, dtype=torch.uint8, device=dev)

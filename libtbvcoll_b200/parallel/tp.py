@@ -74,8 +74,7 @@ class TPGroup:
         h = bf16(sum_ranks x) + residual and ``x`` holds RMSNorm(h) * gamma.  One kernel when the
         message is small enough for the one-shot fused kernel, else all-reduce + add-norm."""
         if self.world == 1:
-            ops.add_rmsnorm(x, residual, gamma, eps)
-            self.launches += 1
+            ops.add_rmsnorm(x, residual, gamma, eps)      # counted by the ops module
             return x, residual
         nbytes = x.numel() * x.element_size()
         if self.comm is not None and nbytes <= self.fused_norm_max_bytes:
@@ -86,5 +85,4 @@ class TPGroup:
             self.calls -= 1
         self.all_reduce(x)
         ops.add_rmsnorm(x, residual, gamma, eps)
-        self.launches += 1
         return x, residual

@@ -200,3 +200,172 @@ def cpu_never_joins(rank, world, port):
         return {"raised": False}
     except RuntimeError:
         return {"raised": True, "elapsed": time.time() - t0}
+
+
+# ---- real multi-GPU ranks (one process per GPU) ------------------------------------------
+def _gen_gpu(seed, n, dtype, dev):
+    import torch
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return ((torch.rand(n, generator=g) - 0.5) * 10).to(dtype).to(dev)
+
+
+def gpu_collectives(rank, world, port, mem):
+    """exactness (all dtypes, odd sizes, both algorithms), no-sync stress with slot reuse,
+    graph replay, fused all-reduce+norm, reduce-scatter / all-gather, statistics."""
+    import torch
+    os.environ["TBV_MEM"] = mem
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from libtbvcoll_b200 import ops
+    from libtbvcoll_b200.ops import reference as ref
+    from libtbvcoll_b200.tbvcoll import Comm
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    c = Comm(rank, world, rank, "127.0.0.1", port, cap_bytes=1 << 20)
+    res = {"bad": []}
+    for algo in ("oneshot", "twoshot"):
+        c.set_algo(algo)
+        for dtype in (torch.float32, torch.float16, torch.bfloat16):
+            es = torch.tensor([], dtype=dtype).element_size()
+            for nbytes in (16, 4096, 57344, 229376, 1048576, 4096 + 16 * 7, 2 * 33):
+                n = nbytes // es
+                x = _gen_gpu(1234 + rank, n, dtype, dev)
+                out = torch.empty_like(x)
+                assert c.all_reduce(x, out)
+                torch.cuda.synchronize()
+                want = oracle_sum([_gen_gpu(1234 + r, n, dtype, dev) for r in range(world)])
+                if not torch.equal(out, want):
+                    res["bad"].append((algo, str(dtype), nbytes))
+    # stress: 400 back-to-back calls, no sync, 4 slots
+    c.set_algo("auto")
+    n = 57344 // 2
+    ins = [_gen_gpu(it * world + rank, n, torch.bfloat16, dev) for it in range(400)]
+    outs = [torch.empty_like(t) for t in ins]
+    for it in range(400):
+        assert c.all_reduce(ins[it], outs[it])
+    torch.cuda.synchronize()
+    res["stress_bad"] = sum(0 if torch.equal(outs[it], oracle_sum([_gen_gpu(it * world + r, n, torch.bfloat16, dev) for r in range(world)])) else 1
+                            for it in range(0, 400, 7))
+    # graph replay
+    x = _gen_gpu(rank, 4096, torch.bfloat16, dev)
+    y = torch.empty_like(x)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    ok = True
+    with torch.cuda.stream(s):
+        c.all_reduce(x, y)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            c.all_reduce(x, y)
+        for rep in range(6):
+            x.copy_(_gen_gpu(100 * rep + rank, 4096, torch.bfloat16, dev))
+            g.replay()
+            s.synchronize()
+            ok &= bool(torch.equal(y, oracle_sum([_gen_gpu(100 * rep + r, 4096, torch.bfloat16, dev) for r in range(world)])))
+    torch.cuda.current_stream().wait_stream(s)
+    res["graph_ok"] = ok
+    # fused all-reduce + residual + RMSNorm == unfused bits == oracle
+    T, H = 8, 4096
+    xs = [(_gen_gpu(r, T * H, torch.bfloat16, dev) * 0.1).view(T, H) for r in range(world)]
+    resid = _gen_gpu(99, T * H, torch.bfloat16, dev).view(T, H)
+    gamma = _gen_gpu(7, H, torch.bfloat16, dev)
+    x1, r1 = xs[rank].clone(), resid.clone()
+    assert c.all_reduce_rmsnorm(x1, r1, gamma, 1e-5)
+    x2, r2 = xs[rank].clone(), resid.clone()
+    assert c.all_reduce(x2)
+    ops.add_rmsnorm(x2, r2, gamma, 1e-5)
+    torch.cuda.synchronize()
+    want_y, want_h = ref.ar_residual_rmsnorm(xs, resid, gamma, 1e-5)
+    res["fused_ok"] = bool(torch.equal(r1, want_h) and torch.equal(x1, x2) and torch.equal(r1, r2))
+    # reduce-scatter / all-gather
+    nrs = 4096
+    full = [_gen_gpu(500 + r, world * nrs, torch.bfloat16, dev) for r in range(world)]
+    o = torch.empty(nrs, dtype=torch.bfloat16, device=dev)
+    assert c.reduce_scatter(full[rank], o)
+    gat = torch.empty(world * nrs, dtype=torch.bfloat16, device=dev)
+    assert c.all_gather(o, gat)
+    torch.cuda.synchronize()
+    tot = oracle_sum(full)
+    res["rs_ok"] = bool(torch.equal(o, tot[rank * nrs:(rank + 1) * nrs]))
+    res["ag_ok"] = bool(torch.equal(gat, tot))
+    res["over_cap"] = c.all_reduce(torch.zeros(1 << 20, device=dev))   # 4 MiB > cap -> False
+    res["stats"] = c.stats5()
+    res["err"] = c.err()
+    res["nvls"] = c.has_nvls()
+    c.destroy()
+    return res
+
+
+def gpu_engine_tp(rank, world, port):
+    """TP engine on `world` GPUs: every rank emits the same tokens, all decode loops agree,
+    and the logits agree with the stock-PyTorch TP=1 model."""
+    import hashlib
+    import torch
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from libtbvcoll_b200.engine.engine import Engine
+    from libtbvcoll_b200.models.config import get_config
+    from libtbvcoll_b200.models.torch_baseline import TorchLlamaTP
+    from libtbvcoll_b200.parallel.tp import TPGroup
+    from libtbvcoll_b200.tbvcoll import Comm
+    from libtbvcoll_b200.utils.weights import RandomSource, shard_for_rank
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    cfg = get_config("tiny")
+    c = Comm(rank, world, rank, "127.0.0.1", port, cap_bytes=64 * cfg.hidden_size * 2)
+    tp = TPGroup(rank, world, c)
+    src = RandomSource(cfg, seed=3, device=dev)
+    eng = Engine(cfg, tp, device=dev, source=src, max_batch=4, max_seq_len=128, prefill_chunk=64)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (37, 5, 64, 20)]
+    a = eng.generate(prompts, 10, loop="host")
+    b = eng.generate(prompts, 10, loop="device")
+    cc = eng.generate(prompts, 10, loop="host", use_graph=False)
+    eng.prefill([prompts[0]], 1)
+    got = eng.model.logits[:1].float().clone()           # this rank's vocab shard
+    wt = shard_for_rank(cfg, src, 0, 1, dev, interleave_gate_up=False)
+    base = TorchLlamaTP(cfg, 0, 1, wt, dev, max_batch=1, max_seq_len=128)
+    with torch.no_grad():
+        want = base.forward(torch.tensor([prompts[0]], device=dev), torch.arange(37, device=dev, dtype=torch.int32)[None], 0)
+    vpr = cfg.vocab_size // world
+    err = (got - want[:, rank * vpr:(rank + 1) * vpr]).abs().max().item()
+    h = lambda o: hashlib.sha256(repr(o).encode()).hexdigest()
+    out = {"hash": h(a), "loops_equal": h(a) == h(b) == h(cc), "logit_err": err, "logit_scale": want.abs().max().item(),
+           "fallbacks": tp.fallbacks, "launches_per_step": eng.launches_per_step}
+    c.destroy()
+    return out
+
+
+def gpu_peer_skips(rank, world, port):
+    """Host-made failure: rank 1 drops one call between steps.  Rank 0's in-kernel wait runs out
+    after TBV_WDOG, the kernel returns, the host sees a sticky error; no GPU faults or hangs."""
+    import time
+    import torch
+    os.environ["TBV_WDOG"] = "0.5"
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from libtbvcoll_b200.tbvcoll import Comm
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    c = Comm(rank, world, rank, "127.0.0.1", port, cap_bytes=1 << 16)
+    x = torch.ones(1024, device=dev)
+    assert c.all_reduce(x)
+    torch.cuda.synchronize()
+    res = {"first": x[0].item()}
+    if rank == 1:
+        c.skip_next(1)
+    t0 = time.time()
+    c.all_reduce(torch.ones(1024, device=dev))
+    torch.cuda.synchronize()                       # returns: the wait is bounded
+    res["elapsed"] = time.time() - t0
+    res["err"] = c.err()
+    res["last"] = c.last_error()
+    refused = False
+    if rank == 0:
+        try:
+            c.all_reduce(torch.ones(1024, device=dev))
+        except RuntimeError:
+            refused = True
+    res["refused"] = refused
+    # the context is still usable after the timed-out kernel
+    res["alive"] = float((torch.ones(8, device=dev) * 2).sum().item())
+    time.sleep(1.0)
+    c.destroy()
+    return res
