@@ -40,6 +40,35 @@ def p50_us(fn, inner, groups, world):
     return float(t[0]), float(t[1])
 
 
+def graph_us(fn, inner, world):
+    """Device-only latency: `inner` calls captured in one CUDA graph (no host launch cost
+    between them), best-of-median over replays, max over ranks."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(inner):
+                fn()
+        g.replay()
+        s.synchronize()
+        dist.barrier()
+        us = []
+        for _ in range(15):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            g.replay()
+            e1.record(s)
+            s.synchronize()
+            us.append(e0.elapsed_time(e1) * 1e3 / inner)
+    torch.cuda.current_stream().wait_stream(s)
+    t = torch.tensor([statistics.median(us)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-tokens", type=int, default=8192)
@@ -83,11 +112,12 @@ def main():
             if algo != "nvls":
                 assert exact, f"{algo} not bit-exact at {nbytes} bytes"
             p50, p99 = p50_us(lambda: comm.all_reduce(x, out), inner, groups, world)
-            row[algo] = {"p50_us": round(p50, 2), "p99_us": round(p99, 2), "exact_vs_fixed_order_oracle": exact,
+            row[algo] = {"p50_us": round(p50, 2), "p99_us": round(p99, 2), "graph_us": round(graph_us(lambda: comm.all_reduce(x, out), inner, world), 2),
+                         "exact_vs_fixed_order_oracle": exact,
                          "busbw_GBs": round(2 * (world - 1) / world * nbytes / p50 / 1e3, 1)}
         y = x.clone()
         p50, p99 = p50_us(lambda: dist.all_reduce(y), inner, groups, world)
-        row["nccl"] = {"p50_us": round(p50, 2), "p99_us": round(p99, 2), "busbw_GBs": round(2 * (world - 1) / world * nbytes / p50 / 1e3, 1)}
+        row["nccl"] = {"p50_us": round(p50, 2), "p99_us": round(p99, 2), "graph_us": round(graph_us(lambda: dist.all_reduce(y), inner, world), 2), "busbw_GBs": round(2 * (world - 1) / world * nbytes / p50 / 1e3, 1)}
         rows.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)

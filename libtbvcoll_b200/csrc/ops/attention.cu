@@ -18,9 +18,9 @@
 namespace {
 
 constexpr int kD = 128;        // head_dim
-constexpr int kThreads = 128;  // 8 half-warps
-constexpr int kHW = kThreads / 16;
 constexpr int kU = 4;          // tokens in flight per half-warp (8 x 16-byte loads per thread)
+constexpr int kMaxSplits = 8;  // portable cluster size
+constexpr int kMaxBlocksPerCta = 64;  // block-table entries staged per pass
 constexpr float kNegBig = -1e30f;
 
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
@@ -28,6 +28,17 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
   f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
   f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
   f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(r) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 struct AttnParams {
@@ -38,23 +49,28 @@ struct AttnParams {
   const int* seq_of_query;  // [Nq] or null (identity)
   const int* ctx_lens;      // [Nq]: keys visible to this query row
   __nv_bfloat16* out;       // [Nq, nq, D], row stride ldo
-  float* part_o;            // [Nq, nkv, splits, G, D]   (scratch, splits > 1)
-  float* part_ml;           // [Nq, nkv, splits, G, 2]
-  unsigned* tickets;        // [Nq, nkv], zero between launches
   float scale_log2;         // softmax scale * log2(e)
   int ldq, ldo, nkv, block_size, max_blocks, splits;
 };
 
-template <int G>
+// grid (Nq, nkv, splits), cluster (1, 1, splits): the CTAs of one cluster cover disjoint
+// ranges of the cached tokens of one (query row, kv head) and merge their partial softmax
+// results through distributed shared memory in split order — no global scratch, no atomics.
+// kThreads: 256 (16 half-warps) while the per-half-warp partials fit in 48 KB of static shared memory, else 128.
+template <int G, int kThreads>
 __global__ void __launch_bounds__(kThreads) k_paged_attn(const AttnParams p) {
+  constexpr int kHW = kThreads / 16;
+  __shared__ float sh_o[kHW][G][kD];   // per half-warp partials, then [0] holds the CTA's result
+  __shared__ float sh_ml[kHW][G][2];
+  __shared__ int sh_bt[kMaxBlocksPerCta];
   pdl::launch_dependents();
   pdl::grid_dependency_wait();
-  const int qi = blockIdx.x, h = blockIdx.y, sp = blockIdx.z;
+  const int qi = blockIdx.x, h = blockIdx.y, sp = blockIdx.z, S = p.splits;
   const int hw = threadIdx.x >> 4, l16 = threadIdx.x & 15;
   const int ctx = p.ctx_lens[qi];
   const int seq = p.seq_of_query ? p.seq_of_query[qi] : qi;
   const int* bt = p.block_tables + size_t(seq) * p.max_blocks;
-  int chunk = (ctx + p.splits - 1) / p.splits;
+  int chunk = (ctx + S - 1) / S;
   chunk = (chunk + p.block_size - 1) / p.block_size * p.block_size;
   const int t0 = sp * chunk, t1 = min(ctx, t0 + chunk);
 
@@ -69,72 +85,79 @@ __global__ void __launch_bounds__(kThreads) k_paged_attn(const AttnParams p) {
     l[g] = 0.f;
   }
 
-  // The trip count is the same for every thread of the CTA (the shuffles below name the
-  // whole warp); tokens past the end are masked per half-warp.
-  for (int base = t0; base < t1; base += kHW * kU) {
-    const int tok = base + hw;
-    uint4 kv[kU], vv[kU];
-    bool valid[kU];
+  // Passes of up to kMaxBlocksPerCta cache blocks: their table entries are staged in shared
+  // memory first so that the K/V loads below depend on one global round trip, not two.
+  const int span = kMaxBlocksPerCta * p.block_size;
+  for (int pass0 = t0; pass0 < t1; pass0 += span) {
+    const int pass1 = min(t1, pass0 + span);
+    const int b0 = pass0 / p.block_size, nb = (pass1 - pass0 + p.block_size - 1) / p.block_size;
+    __syncthreads();
+    if (threadIdx.x < nb) sh_bt[threadIdx.x] = bt[b0 + threadIdx.x];
+    __syncthreads();
+    // The trip count is the same for every thread of the CTA (the shuffles below name the
+    // whole warp); tokens past the end are masked per half-warp.
+    for (int base = pass0; base < pass1; base += kHW * kU) {
+      const int tok = base + hw;
+      uint4 kv[kU], vv[kU];
+      bool valid[kU];
 #pragma unroll
-    for (int j = 0; j < kU; j++) {
-      const int tj = tok + j * kHW;
-      valid[j] = tj < t1;
-      if (valid[j]) {
-        const long long slot = (long long)bt[tj / p.block_size] * p.block_size + tj % p.block_size;
-        const size_t off = (size_t(slot) * p.nkv + h) * kD + l16 * 8;
-        kv[j] = *reinterpret_cast<const uint4*>(p.k_cache + off);
-        vv[j] = *reinterpret_cast<const uint4*>(p.v_cache + off);
-      } else {
-        kv[j] = make_uint4(0, 0, 0, 0);
-        vv[j] = make_uint4(0, 0, 0, 0);
+      for (int j = 0; j < kU; j++) {
+        const int tj = tok + j * kHW;
+        valid[j] = tj < pass1;
+        if (valid[j]) {
+          const long long slot = (long long)sh_bt[tj / p.block_size - b0] * p.block_size + tj % p.block_size;
+          const size_t off = (size_t(slot) * p.nkv + h) * kD + l16 * 8;
+          kv[j] = *reinterpret_cast<const uint4*>(p.k_cache + off);
+          vv[j] = *reinterpret_cast<const uint4*>(p.v_cache + off);
+        } else {
+          kv[j] = make_uint4(0, 0, 0, 0);
+          vv[j] = make_uint4(0, 0, 0, 0);
+        }
       }
-    }
-    float s[kU][G];
+      float s[kU][G];
 #pragma unroll
-    for (int j = 0; j < kU; j++) {
-      float kf[8];
-      unpack8(kv[j], kf);
+      for (int j = 0; j < kU; j++) {
+        float kf[8];
+        unpack8(kv[j], kf);
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+          float d = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; i++) d = fmaf(qf[g][i], kf[i], d);
+          s[j][g] = d;
+        }
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+        for (int j = 0; j < kU; j++)
+#pragma unroll
+          for (int g = 0; g < G; g++) s[j][g] += __shfl_xor_sync(0xffffffffu, s[j][g], o);
 #pragma unroll
       for (int g = 0; g < G; g++) {
-        float d = 0.f;
+        float mx = m[g];
 #pragma unroll
-        for (int i = 0; i < 8; i++) d = fmaf(qf[g][i], kf[i], d);
-        s[j][g] = d;
-      }
-    }
+        for (int j = 0; j < kU; j++) if (valid[j]) mx = fmaxf(mx, s[j][g]);
+        const float corr = exp2f(m[g] - mx);
+        float pj[kU], ps = 0.f;
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1)
+        for (int j = 0; j < kU; j++) { pj[j] = valid[j] ? exp2f(s[j][g] - mx) : 0.f; ps += pj[j]; }
+        l[g] = l[g] * corr + ps;
+        m[g] = mx;
 #pragma unroll
-      for (int j = 0; j < kU; j++)
+        for (int i = 0; i < 8; i++) acc[g][i] *= corr;
 #pragma unroll
-        for (int g = 0; g < G; g++) s[j][g] += __shfl_xor_sync(0xffffffffu, s[j][g], o);
-    float vf[kU][8];
+        for (int j = 0; j < kU; j++) {
+          float vf[8];
+          unpack8(vv[j], vf);
 #pragma unroll
-    for (int j = 0; j < kU; j++) unpack8(vv[j], vf[j]);
-#pragma unroll
-    for (int g = 0; g < G; g++) {
-      float mx = m[g];
-#pragma unroll
-      for (int j = 0; j < kU; j++) if (valid[j]) mx = fmaxf(mx, s[j][g]);
-      const float corr = exp2f(m[g] - mx);
-      float pj[kU], ps = 0.f;
-#pragma unroll
-      for (int j = 0; j < kU; j++) { pj[j] = valid[j] ? exp2f(s[j][g] - mx) : 0.f; ps += pj[j]; }
-      l[g] = l[g] * corr + ps;
-      m[g] = mx;
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        float a = acc[g][i] * corr;
-#pragma unroll
-        for (int j = 0; j < kU; j++) a = fmaf(pj[j], vf[j][i], a);
-        acc[g][i] = a;
+          for (int i = 0; i < 8; i++) acc[g][i] = fmaf(pj[j], vf[i], acc[g][i]);
+        }
       }
     }
   }
 
-  // combine the 8 half-warps
-  __shared__ float sh_o[kHW][G][kD];
-  __shared__ float sh_ml[kHW][G][2];
+  // combine the half-warps of this CTA
 #pragma unroll
   for (int g = 0; g < G; g++) {
 #pragma unroll
@@ -142,74 +165,86 @@ __global__ void __launch_bounds__(kThreads) k_paged_attn(const AttnParams p) {
     if (l16 == 0) { sh_ml[hw][g][0] = m[g]; sh_ml[hw][g][1] = l[g]; }
   }
   __syncthreads();
-  const int d = threadIdx.x;  // one thread per output dim
-  float o[G], lm[G], ll[G];
+  float res_o[(G * kD + kThreads - 1) / kThreads], res_m[(G * kD + kThreads - 1) / kThreads], res_l[(G * kD + kThreads - 1) / kThreads];
 #pragma unroll
-  for (int g = 0; g < G; g++) {
-    float mx = kNegBig;
-    for (int w = 0; w < kHW; w++) mx = fmaxf(mx, sh_ml[w][g][0]);
-    float a = 0.f, ls = 0.f;
-    for (int w = 0; w < kHW; w++) {
-      const float c = exp2f(sh_ml[w][g][0] - mx);
-      a = fmaf(sh_o[w][g][d], c, a);
-      ls = fmaf(sh_ml[w][g][1], c, ls);
+  for (int k = 0; k < (G * kD + kThreads - 1) / kThreads; k++) {
+    const int idx = threadIdx.x + k * kThreads;
+    if (idx < G * kD) {
+      const int g = idx / kD, d = idx % kD;
+      float mx = kNegBig;
+      for (int w = 0; w < kHW; w++) mx = fmaxf(mx, sh_ml[w][g][0]);
+      float a = 0.f, ls = 0.f;
+      for (int w = 0; w < kHW; w++) {
+        const float c = exp2f(sh_ml[w][g][0] - mx);
+        a = fmaf(sh_o[w][g][d], c, a);
+        ls = fmaf(sh_ml[w][g][1], c, ls);
+      }
+      res_o[k] = a; res_m[k] = mx; res_l[k] = ls;
     }
-    o[g] = a; lm[g] = mx; ll[g] = ls;
   }
-  if (p.splits == 1) {
+  if (S == 1) {
 #pragma unroll
-    for (int g = 0; g < G; g++)
-      p.out[size_t(qi) * p.ldo + (h * G + g) * kD + d] = __float2bfloat16_rn(ll[g] > 0.f ? o[g] / ll[g] : 0.f);
+    for (int k = 0; k < (G * kD + kThreads - 1) / kThreads; k++) {
+      const int idx = threadIdx.x + k * kThreads;
+      if (idx < G * kD)
+        p.out[size_t(qi) * p.ldo + h * G * kD + idx] = __float2bfloat16_rn(res_l[k] > 0.f ? res_o[k] / res_l[k] : 0.f);
+    }
     return;
   }
-  const size_t pbase = (size_t(qi) * p.nkv + h) * p.splits;
-#pragma unroll
-  for (int g = 0; g < G; g++) {
-    p.part_o[((pbase + sp) * G + g) * kD + d] = o[g];
-    if (d == 0) { p.part_ml[((pbase + sp) * G + g) * 2] = lm[g]; p.part_ml[((pbase + sp) * G + g) * 2 + 1] = ll[g]; }
-  }
-  __shared__ bool last;
-  __threadfence();
+  // publish this CTA's result in its own shared memory (slot [0] of the partial arrays)
   __syncthreads();
-  if (threadIdx.x == 0) last = atomicAdd(&p.tickets[size_t(qi) * p.nkv + h], 1u) == unsigned(p.splits - 1);
-  __syncthreads();
-  if (!last) return;
-  __threadfence();
 #pragma unroll
-  for (int g = 0; g < G; g++) {
-    float mx = kNegBig;
-    for (int s2 = 0; s2 < p.splits; s2++) mx = fmaxf(mx, *(volatile float*)&p.part_ml[((pbase + s2) * G + g) * 2]);
-    float a = 0.f, ls = 0.f;
-    for (int s2 = 0; s2 < p.splits; s2++) {
-      const float c = exp2f(*(volatile float*)&p.part_ml[((pbase + s2) * G + g) * 2] - mx);
-      a = fmaf(*(volatile float*)&p.part_o[((pbase + s2) * G + g) * kD + d], c, a);
-      ls = fmaf(*(volatile float*)&p.part_ml[((pbase + s2) * G + g) * 2 + 1], c, ls);
+  for (int k = 0; k < (G * kD + kThreads - 1) / kThreads; k++) {
+    const int idx = threadIdx.x + k * kThreads;
+    if (idx < G * kD) {
+      const int g = idx / kD, d = idx % kD;
+      sh_o[0][g][d] = res_o[k];
+      if (d == 0) { sh_ml[0][g][0] = res_m[k]; sh_ml[0][g][1] = res_l[k]; }
     }
-    p.out[size_t(qi) * p.ldo + (h * G + g) * kD + d] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
   }
-  if (threadIdx.x == 0) p.tickets[size_t(qi) * p.nkv + h] = 0;
+  cluster_sync();
+  // CTA `sp` merges outputs [sp * per, (sp + 1) * per) of the G * D values, in split order
+  const int per = (G * kD + S - 1) / S;
+  for (int i = threadIdx.x; i < per; i += kThreads) {
+    const int idx = sp * per + i;
+    if (idx < G * kD) {
+      const int g = idx / kD, d = idx % kD;
+      const uint32_t a_ml = smem_addr(&sh_ml[0][g][0]), a_o = smem_addr(&sh_o[0][g][d]);
+      float ms[kMaxSplits], mx = kNegBig;
+      for (int r = 0; r < S; r++) { ms[r] = ld_cluster_f32(a_ml, r); mx = fmaxf(mx, ms[r]); }
+      float a = 0.f, ls = 0.f;
+      for (int r = 0; r < S; r++) {
+        const float c = exp2f(ms[r] - mx);
+        a = fmaf(ld_cluster_f32(a_o, r), c, a);
+        ls = fmaf(ld_cluster_f32(a_ml + 4, r), c, ls);
+      }
+      p.out[size_t(qi) * p.ldo + h * G * kD + idx] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
+    }
+  }
+  cluster_sync();  // keep this CTA's shared memory alive until every peer has read it
 }
 
 }  // namespace
 
 extern "C" {
 
-// Scratch for kv splits: tickets (u32 per (query, kv head), must be zero before the first
-// launch; the kernel leaves them zero) followed by the fp32 partials.
+// kv splits merge through cluster shared memory: no scratch is needed.  Kept for callers
+// that size a workspace: returns a token amount.
 size_t tbv_op_attn_workspace(int nq_rows, int nq_heads, int nkv, int max_splits) {
-  const size_t tick = (size_t(nq_rows) * nkv * 4 + 255) & ~size_t(255);
-  return tick + size_t(nq_rows) * nq_heads * max_splits * (kD + 2) * 4;
+  (void)nq_rows; (void)nq_heads; (void)nkv; (void)max_splits;
+  return 256;
 }
 
+// splits: 1..8 CTAs (one thread-block cluster) per (query row, kv head).
 int tbv_op_paged_attention(const void* q, const void* k_cache, const void* v_cache, const void* block_tables,
                            const void* seq_of_query, const void* ctx_lens, void* out, void* workspace, int nq_rows, int nq_heads,
                            int nkv, int head_dim, int ldq, int ldo, int block_size, int max_blocks, int splits, float scale,
                            void* stream) {
+  (void)workspace;
   if (nq_rows <= 0) return 0;
   if (head_dim != kD || nq_heads % nkv || (ldq % 8) || block_size <= 0) return -2;
   const int G = nq_heads / nkv;
-  if (splits < 1) splits = 1;
-  if (splits > 1 && !workspace) return -2;
+  splits = splits < 1 ? 1 : (splits > kMaxSplits ? kMaxSplits : splits);
   AttnParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
@@ -218,21 +253,16 @@ int tbv_op_paged_attention(const void* q, const void* k_cache, const void* v_cac
   p.seq_of_query = static_cast<const int*>(seq_of_query);
   p.ctx_lens = static_cast<const int*>(ctx_lens);
   p.out = static_cast<__nv_bfloat16*>(out);
-  char* ws = static_cast<char*>(workspace);
-  const size_t tick = (size_t(nq_rows) * nkv * 4 + 255) & ~size_t(255);
-  p.tickets = reinterpret_cast<unsigned*>(ws);
-  p.part_o = reinterpret_cast<float*>(ws + tick);
-  p.part_ml = p.part_o + size_t(nq_rows) * nq_heads * splits * kD;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.ldq = ldq; p.ldo = ldo; p.nkv = nkv; p.block_size = block_size; p.max_blocks = max_blocks; p.splits = splits;
   dim3 grid(nq_rows, nkv, splits);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaSuccess;
   switch (G) {
-    case 1: e = pdl::launch(k_paged_attn<1>, grid, dim3(kThreads), 0, st, 1, p); break;
-    case 2: e = pdl::launch(k_paged_attn<2>, grid, dim3(kThreads), 0, st, 1, p); break;
-    case 4: e = pdl::launch(k_paged_attn<4>, grid, dim3(kThreads), 0, st, 1, p); break;
-    case 8: e = pdl::launch(k_paged_attn<8>, grid, dim3(kThreads), 0, st, 1, p); break;
+    case 1: e = pdl::launch(k_paged_attn<1, 256>, grid, dim3(256), 0, st, splits, p); break;
+    case 2: e = pdl::launch(k_paged_attn<2, 256>, grid, dim3(256), 0, st, splits, p); break;
+    case 4: e = pdl::launch(k_paged_attn<4, 256>, grid, dim3(256), 0, st, splits, p); break;
+    case 8: e = pdl::launch(k_paged_attn<8, 128>, grid, dim3(128), 0, st, splits, p); break;
     default: return -2;
   }
   return e == cudaSuccess ? 0 : -1;

@@ -109,9 +109,10 @@ class Engine:
 
     def attn_splits_for(self, B: int, max_ctx: int) -> int:
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        # enough CTAs to fill the GPU about four times over, but at least 64 cached tokens each
-        want = math.ceil(4 * sms / max(1, B * self.model.nkv))
-        return max(1, min(want, self.model.max_attn_splits, math.ceil(max_ctx / 64)))
+        # kv splits are the CTAs of one cluster (<= 8): enough CTAs for about two per SM, and at
+        # least 64 cached tokens each
+        want = math.ceil(2 * sms / max(1, B * self.model.nkv))
+        return max(1, min(want, 8, self.model.max_attn_splits, math.ceil(max_ctx / 64)))
 
     def capture(self, B: int, splits: int, advance: bool) -> torch.cuda.CUDAGraph:
         """Capture one decode step (all layers, both collectives per layer, sampling) as a graph."""
