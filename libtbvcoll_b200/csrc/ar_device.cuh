@@ -562,12 +562,13 @@ __device__ __forceinline__ float block_sum_fixed(float v, float* sh /* >= 32 flo
 
 // h: this thread's values of one row (units u = threadIdx.x + k*blockDim.x), already
 // rounded to bf16 precision.  Writes the normalised row.
+template <int MAXU = kNormMaxUnits>
 __device__ __forceinline__ void rmsnorm_row_store(const float (*h)[8], int nunits_row, int hidden,
                                                   float eps, const uint4* __restrict__ gamma,
                                                   uint4* y_row, float* sh) {
   float ss = 0.f;
 #pragma unroll
-  for (int k = 0; k < kNormMaxUnits; k++) {
+  for (int k = 0; k < MAXU; k++) {
     int u = threadIdx.x + k * blockDim.x;
     if (u < nunits_row) {
 #pragma unroll
@@ -577,7 +578,7 @@ __device__ __forceinline__ void rmsnorm_row_store(const float (*h)[8], int nunit
   float tot = block_sum_fixed(ss, sh);
   float rs = rsqrtf(tot / float(hidden) + eps);
 #pragma unroll
-  for (int k = 0; k < kNormMaxUnits; k++) {
+  for (int k = 0; k < MAXU; k++) {
     int u = threadIdx.x + k * blockDim.x;
     if (u < nunits_row) {
       float g[8], o[8];

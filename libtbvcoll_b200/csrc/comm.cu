@@ -475,6 +475,8 @@ static int gpu_init(tbv_comm* c) {
     g.ctx.flags[p] = reinterpret_cast<unsigned*>(c->peer_maps[p]);
     g.ctx.data[p] = static_cast<char*>(c->peer_maps[p]) + c->flag_bytes;
   }
+  CUDA_TRY(c, cudaMalloc(&c->ctxs_dev, sizeof(RankCtx)));
+  CUDA_TRY(c, cudaMemcpy(c->ctxs_dev, &g.ctx, sizeof(RankCtx), cudaMemcpyHostToDevice));
   // nobody may push before everybody has cleared its flags
   if (c->bs.barrier() != 0) { c->errmsg = c->bs.error(); return TBV_FAIL; }
   return TBV_OK;
@@ -673,7 +675,7 @@ static int gpu_ar_rmsnorm(tbv_comm* c, const void* const* xs, const void* const*
   const double t0 = now_us();
   if (check_err(c)) return TBV_FAIL;
   const size_t nbytes = size_t(tokens) * hidden * 2;
-  if (hidden % 8 || hidden > 8 * kNormMaxUnits * 1024 || nbytes > c->cap || tokens <= 0) { c->stats.fallbacks++; return TBV_FALLBACK; }
+  if (hidden % 8 || hidden > 8 * 4 * 1024 || nbytes > c->cap || tokens <= 0) { c->stats.fallbacks++; return TBV_FALLBACK; }
   const int nr = c->local ? c->world : 1;
   for (int r = 0; r < nr; r++)
     if (!aligned16(xs[r]) || !aligned16(residuals[r]) || !aligned16(residual_outs[r]) || !aligned16(ys[r]) || !aligned16(gamma))
@@ -900,10 +902,10 @@ int tbv_comm_set_wdog(tbv_comm* c, double seconds) {
   c->knobs.wdog_s = seconds;
   if (c->cpu) c->cpu->set_wdog(seconds);
   for (auto& g : c->ranks) g.ctx.wdog_ns = (unsigned long long)(seconds * 1e9);
-  if (c->local && c->ctxs_dev) {
-    std::vector<RankCtx> host(c->world);
-    for (int r = 0; r < c->world; r++) host[r] = c->ranks[r].ctx;
-    cudaMemcpy(c->ctxs_dev, host.data(), sizeof(RankCtx) * c->world, cudaMemcpyHostToDevice);
+  if (c->ctxs_dev) {
+    std::vector<RankCtx> host(c->ranks.size());
+    for (size_t r = 0; r < c->ranks.size(); r++) host[r] = c->ranks[r].ctx;
+    cudaMemcpy(c->ctxs_dev, host.data(), sizeof(RankCtx) * host.size(), cudaMemcpyHostToDevice);
   }
   return TBV_OK;
 }

@@ -1,0 +1,263 @@
+// gemm_ar.cu — row-parallel linear fused with its all-reduce, the residual add and the
+// RMSNorm that follows it, in ONE kernel over peer memory:
+//
+//   partial = X[T, K/tp] @ W[H, K/tp]^T            tcgen05 tiles, TMA-fed, TMEM accumulators
+//   every finished tile slice is rounded to bf16 and stored straight into the slot memory of
+//   every rank (plain 8-byte stores through the NVLink peer mappings — the epilogue IS the
+//   transfer), one sequence flag per M tile announces it;
+//   a few CTAs then wait for all tiles of all ranks, add the N copies in rank order in fp32,
+//   round, add the residual, and apply RMSNorm.
+//
+// This is what the reference's hook wraps as two separate steps (RowParallelLinear, then
+// GroupCoordinator.all_reduce: step3b/vllm_tp_bench.py:87-124) plus the norm it lists as future
+// work ("fuse k_acc + next RMSNorm", reports/12_references.md:136).  Semantics match the
+// unfused pipeline: the all-reduce operands are bf16, the sum is fp32 in rank order with one
+// rounding, so the residual stream has identical bits; the normalised output can differ in
+// the last bf16 digit because the variance is reduced by a 192-thread CTA here.
+//
+// Also here: the emulated-ranks form (blockIdx.y = rank, all ranks on one GPU) used to test
+// the protocol on a single GPU.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+
+#include "../comm.h"
+#include "gemm.cuh"
+#include "ops.h"
+
+using namespace sm100;
+using namespace tbv;
+
+namespace {
+
+struct Maps {
+  CUtensorMap a[TBV_MAXRANK];  // weights of (emulated) rank r
+  CUtensorMap b[TBV_MAXRANK];  // activations of rank r
+};
+struct FusedPtrs {
+  const __nv_bfloat16* residual[TBV_MAXRANK];
+  __nv_bfloat16* residual_out[TBV_MAXRANK];
+  __nv_bfloat16* y[TBV_MAXRANK];
+};
+constexpr int kMaxWaiters = 32;
+constexpr int kFusedMaxUnits = 6;  // 16-byte units per thread in the norm phase: hidden <= 8 * 6 * 192 = 9216
+
+__global__ void __launch_bounds__(gemm::kThreads, 1)
+k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const RankCtx* ctxs, const __grid_constant__ FusedPtrs fp,
+                  const __nv_bfloat16* gamma, float eps) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ gemm::Smem s;
+  __shared__ unsigned long long sh_seq;
+  __shared__ float sh_red[32];
+  const int er = blockIdx.y;  // (emulated) rank index into the per-rank arrays; 0 for a real rank
+  const RankCtx& c = ctxs[er];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tile = blockIdx.x, m0 = m_tile * gemm::kBM;
+  const int S = p.splits;
+  const int split = S > 1 ? int(cluster_ctarank()) : 0;
+  const int kb_per = (p.kb_total + S - 1) / S;
+  const int kb0 = split * kb_per;
+  int nkb = p.kb_total - kb0;
+  nkb = nkb < 0 ? 0 : (nkb > kb_per ? kb_per : nkb);
+  const int T = p.N, H = p.M;
+  const unsigned long long t_enter = (threadIdx.x == 0 && m_tile == 0 && split == 0) ? tbv::globaltimer() : 0;
+
+  uint8_t* sm = gemm::mainloop(&maps.a[er], &maps.b[er], p, s, smem_raw, m0, 0, kb0, nkb);
+  volatile int* abortp = &s.abort_flag;
+  float* stage_f = reinterpret_cast<float*>(sm);
+
+  if (warp >= 2) {
+    const int quarter = warp & 3, ml = quarter * 32 + lane;
+    bool ok = nkb > 0 ? mbar_wait(smem_u32(&s.accum), 0, abortp, p.limit_ns) : true;
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    // The accumulator is complete, so the producer has passed its dependency wait: the
+    // previous collective has finished and the device sequence number is stable.
+    if (threadIdx.x == 64) sh_seq = *(volatile unsigned long long*)&c.st->seq + 1ull;
+    for (int col = 0; col < p.bn; col += 16) {
+      uint32_t r[16];
+      if (ok && nkb > 0) {
+        tmem_ld16(s.tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(col), r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j++) r[j] = 0u;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; j++) stage_f[(col + j) * 128 + ml] = __uint_as_float(r[j]);
+    }
+  }
+  __syncwarp();
+  if (S > 1) cluster_sync_all(); else __syncthreads();
+  CallInfo ci;
+  ci.seq = S > 1 ? 0 : sh_seq;
+  if (S > 1) {
+    // every CTA of the cluster read the same device word; take this CTA's own copy
+    ci.seq = sh_seq;
+  }
+  ci.want = unsigned(ci.seq);
+  ci.slot = int(ci.seq % (unsigned long long)c.nslot);
+
+  if (warp >= 2) {
+    // deterministic split-K (CTA j reduces feature slice j over the cluster's K ranges), then the
+    // bf16 slice goes to EVERY rank's slot region [src = me], own rank included
+    const int te = threadIdx.x - 64;
+    const int fs = 128 / S, q4 = fs / 4;
+    const uint32_t stage_addr = smem_u32(sm);
+    for (int idx = te; idx < T * q4; idx += 128) {
+      const int t = idx / q4, f = split * fs + (idx % q4) * 4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (S > 1) {
+        for (int r = 0; r < S; r++) {
+          float4 v = ld_dsmem_f32x4(mapa_shared(stage_addr + uint32_t((t * 128 + f) * 4), uint32_t(r)));
+          if (r == 0) acc = v;
+          else { acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
+        }
+      } else {
+        acc = *reinterpret_cast<const float4*>(stage_f + t * 128 + f);
+      }
+      __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      const size_t off = (size_t(t) * H + m0 + f) * 2;
+      for (int d = 0; d < c.world; d++) {
+        const int peer = (c.rank + d) % c.world;
+        *reinterpret_cast<uint2*>(slot_region(c, peer, ci.slot, c.rank) + off) = pk;
+      }
+    }
+  }
+  __syncwarp();
+  if (S > 1) cluster_sync_all(); else __syncthreads();  // all slices of this M tile are stored; peers' shared memory no longer needed
+  gemm::teardown(p, s);                                   // TMEM back before the waiting phase
+  if (split == 0 && threadIdx.x == 0) {
+    fence_sys();
+    for (int peer = 0; peer < c.world; peer++)
+      st_relaxed_sys(c.flags[peer] + flag_index(c, ci.slot, 0, c.rank, m_tile), ci.want);
+    if (m_tile == 0) c.hm->bc[1] = ci.seq;
+  }
+
+  // ---- a few CTAs finish the job: wait for every tile of every rank, reduce, residual, norm ----
+  const int n_cta = gridDim.x * S, cta_id = m_tile * S + split;
+  int waiters = T < kMaxWaiters ? T : kMaxWaiters;
+  if (waiters > n_cta) waiters = n_cta;
+  unsigned long long t_ready = 0;
+  if (cta_id < waiters) {
+    const int n_tiles = gridDim.x;
+    for (int i = threadIdx.x; i < c.world * n_tiles; i += blockDim.x) {
+      const int src = i / n_tiles, ch = i % n_tiles;
+      wait_flag(c, c.flags[c.rank] + flag_index(c, ci.slot, 0, src, ch), ci.want, kWhereFused, src, ch, ci.seq);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && cta_id == 0) { t_ready = tbv::globaltimer(); c.hm->bc[2] = ci.seq; }
+    const int upr = H / 8;
+    for (int row = cta_id; row < T; row += waiters) {
+      float h[kFusedMaxUnits][8];
+#pragma unroll
+      for (int k = 0; k < kFusedMaxUnits; k++) {
+        const int u = threadIdx.x + k * blockDim.x;
+        if (u < upr) {
+          const size_t off = size_t(row) * upr + u;
+          float acc[8];
+          for (int r = 0; r < c.world; r++) {
+            uint4 v = ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, ci.slot, r)) + off);
+            float f[8];
+            Pack<__nv_bfloat16>::unpack(v, f);
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc[i] = (r == 0) ? f[i] : acc[i] + f[i];
+          }
+          float res[8];
+          Pack<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(fp.residual[er])[off], res);
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const float sum = __bfloat162float(__float2bfloat16_rn(acc[i]));
+            h[k][i] = __bfloat162float(__float2bfloat16_rn(sum + res[i]));
+          }
+          reinterpret_cast<uint4*>(fp.residual_out[er])[off] = Pack<__nv_bfloat16>::pack(h[k]);
+        }
+      }
+      rmsnorm_row_store<kFusedMaxUnits>(h, upr, H, eps, reinterpret_cast<const uint4*>(gamma),
+                                        reinterpret_cast<uint4*>(fp.y[er]) + size_t(row) * upr, sh_red);
+    }
+  }
+  call_end(c, ci, unsigned(n_cta), t_enter, t_ready, size_t(T) * H * 2, TBV_ALGO_ONESHOT);
+}
+
+bool g_attr_done = false;
+
+}  // namespace
+
+// w/x/residual/residual_out/y: one pointer per (emulated) rank; a real rank passes arrays of 1.
+static int launch_fused(tbv_comm* c, const void* const* ws, const void* const* xs, const void* const* residuals, const void* gamma,
+                        void* const* residual_outs, void* const* ys, int tokens, int hidden, int k_local, int ldx, float eps,
+                        void* stream) {
+  const int nr = c->local ? c->world : 1;
+  if (c->cpu || c->ranks.empty() || c->world < 2) return TBV_FALLBACK;
+  if (c->sticky_err.load()) return TBV_FAIL;
+  for (auto& g : c->ranks)
+    if (*(volatile unsigned*)&g.hm->err != 0) { c->sticky_err.store(1); return TBV_FAIL; }
+  if (tokens <= 0 || tokens > 256 || hidden % 128 || hidden / 128 > TBV_MAXCHAN || hidden > 8 * kFusedMaxUnits * gemm::kThreads ||
+      (k_local % 8) || (ldx % 8) || size_t(tokens) * hidden * 2 > c->cap)
+    return TBV_FALLBACK;
+  if (c->skip.load() > 0) { c->skip.fetch_sub(1); return TBV_OK; }
+  int bn, splits, stages;
+  tbvops::gemm_config(hidden, tokens, k_local, 0, &bn, &splits, &stages);
+  if ((tokens + bn - 1) / bn != 1) return TBV_FALLBACK;
+  if (c->local) {
+    // emulated ranks share one GPU without a cooperative launch: keep the whole grid resident
+    while (splits > 1 && (hidden / 128) * splits * nr > tbvops::sm_count()) splits /= 2;
+    if ((hidden / 128) * splits * nr > tbvops::sm_count()) return TBV_FALLBACK;
+    tbvops::gemm_config(hidden, tokens, k_local, splits, &bn, &splits, &stages);
+  }
+  while (stages * (gemm::kATileBytes + bn * 128) < bn * 512) stages++;  // fp32 staging reuses the ring
+  Maps maps;
+  FusedPtrs fp{};
+  for (int r = 0; r < nr; r++) {
+    if (tbvops::make_tensor_map_bf16(&maps.a[r], ws[r], hidden, k_local, k_local, 128) != 0) return TBV_FALLBACK;
+    if (tbvops::make_tensor_map_bf16(&maps.b[r], xs[r], tokens, k_local, ldx, bn) != 0) return TBV_FALLBACK;
+    fp.residual[r] = static_cast<const __nv_bfloat16*>(residuals[r]);
+    fp.residual_out[r] = static_cast<__nv_bfloat16*>(residual_outs[r]);
+    fp.y[r] = static_cast<__nv_bfloat16*>(ys[r]);
+  }
+  gemm::Params p{};
+  p.M = hidden; p.N = tokens; p.K = k_local; p.ldy = hidden; p.bn = bn; p.splits = splits; p.stages = stages;
+  p.kb_total = (k_local + 63) / 64;
+  p.limit_ns = 2000000000ull;
+  p.err = tbvops::gemm_err_flag();
+  const size_t smem = size_t(stages) * (gemm::kATileBytes + bn * 128) + 1024;
+  if (!g_attr_done) {
+    if (cudaFuncSetAttribute(k_gemm_ar_rmsnorm, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) return TBV_FAIL;
+    g_attr_done = true;
+  }
+  const RankCtx* ctxs = c->ctxs_dev;
+  cudaError_t e = pdl::launch(k_gemm_ar_rmsnorm, dim3(hidden / 128, nr, splits), dim3(gemm::kThreads), smem,
+                              static_cast<cudaStream_t>(stream), splits, maps, p, ctxs, fp, static_cast<const __nv_bfloat16*>(gamma), eps);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "[tbvcoll] fused gemm+all-reduce launch failed: %s\n", cudaGetErrorString(e));
+    c->sticky_err.store(1);
+    return TBV_FAIL;
+  }
+  c->host_seq++;
+  return TBV_OK;
+}
+
+extern "C" {
+
+// y = RMSNorm(h) * gamma with h = bf16(sum over ranks of bf16(x @ w^T)) + residual; residual_out = h.
+// x: [tokens, k_local] (row stride ldx), w: [hidden, k_local] — this rank's shard of a row-parallel layer.
+// tokens <= 256, hidden % 128 == 0.  TBV_FALLBACK (-2): compose gemm + all-reduce + add-norm instead.
+int tbv_comm_gemm_allreduce_rmsnorm(tbv_comm* c, const void* w, const void* x, const void* residual, const void* gamma,
+                                    void* residual_out, void* y, int tokens, int hidden, int k_local, int ldx, float eps,
+                                    void* stream) {
+  if (!c || c->local) return TBV_FAIL;
+  return launch_fused(c, &w, &x, &residual, gamma, &residual_out, &y, tokens, hidden, k_local, ldx, eps, stream);
+}
+
+int tbv_comm_gemm_allreduce_rmsnorm_local(tbv_comm* c, const void* const* ws, const void* const* xs, const void* const* residuals,
+                                          const void* gamma, void* const* residual_outs, void* const* ys, int tokens, int hidden,
+                                          int k_local, int ldx, float eps, void* stream) {
+  if (!c || !c->local) return TBV_FAIL;
+  return launch_fused(c, ws, xs, residuals, gamma, residual_outs, ys, tokens, hidden, k_local, ldx, eps, stream);
+}
+
+}  // extern "C"

@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(1024) k_rmsnorm(const __nv_bfloat16* __restric
 extern "C" {
 // y = RMSNorm(x) * gamma.  x, y: [tokens, hidden] bf16 contiguous; hidden % 8 == 0, hidden <= 32768.
 int tbv_op_rmsnorm(const void* x, const void* gamma, void* y, int tokens, int hidden, float eps, void* stream) {
-  if (hidden % 8 || hidden > 8 * kNormMaxUnits * 1024 || tokens <= 0) return -2;
+  if (hidden % 8 || hidden > 8 * 4 * 1024 || tokens <= 0) return -2;
   cudaError_t e = pdl::launch(k_rmsnorm<false>, dim3(tokens), dim3(tbvops::norm_threads(hidden)), 0, static_cast<cudaStream_t>(stream), 1,
                               static_cast<const __nv_bfloat16*>(x), nullptr, static_cast<const __nv_bfloat16*>(gamma), nullptr,
                               static_cast<__nv_bfloat16*>(y), hidden, eps);
@@ -58,7 +58,7 @@ int tbv_op_rmsnorm(const void* x, const void* gamma, void* y, int tokens, int hi
 // and y == x is allowed.
 int tbv_op_add_rmsnorm(const void* x, const void* residual, const void* gamma, void* residual_out, void* y, int tokens,
                        int hidden, float eps, void* stream) {
-  if (hidden % 8 || hidden > 8 * kNormMaxUnits * 1024 || tokens <= 0) return -2;
+  if (hidden % 8 || hidden > 8 * 4 * 1024 || tokens <= 0) return -2;
   cudaError_t e = pdl::launch(k_rmsnorm<true>, dim3(tokens), dim3(tbvops::norm_threads(hidden)), 0, static_cast<cudaStream_t>(stream), 1,
                               static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
                               static_cast<const __nv_bfloat16*>(gamma), static_cast<__nv_bfloat16*>(residual_out),

@@ -65,6 +65,17 @@ int tbv_comm_allreduce_rmsnorm_local(tbv_comm* c, const void* const* xs,
                                      const void* const* residuals, const void* gamma,
                                      void* const* residual_outs, void* const* ys,
                                      int tokens, int hidden, float eps, void* stream);
+// Row-parallel linear fused with its all-reduce, the residual add and RMSNorm in ONE kernel
+// (tcgen05 GEMM whose epilogue stores into every rank's slot memory):
+//   h = bf16(sum over ranks of bf16(x @ w^T)) + residual; residual_out = h; y = RMSNorm(h) * gamma.
+// x: [tokens, k_local] bf16 (row stride ldx), w: [hidden, k_local] bf16.  tokens <= 256.
+int tbv_comm_gemm_allreduce_rmsnorm(tbv_comm* c, const void* w, const void* x, const void* residual,
+                                    const void* gamma, void* residual_out, void* y, int tokens, int hidden,
+                                    int k_local, int ldx, float eps, void* stream);
+int tbv_comm_gemm_allreduce_rmsnorm_local(tbv_comm* c, const void* const* ws, const void* const* xs,
+                                          const void* const* residuals, const void* gamma,
+                                          void* const* residual_outs, void* const* ys, int tokens,
+                                          int hidden, int k_local, int ldx, float eps, void* stream);
 // reduce-scatter / all-gather over the same slot ring (rows of `row_bytes`).
 // reduce_scatter: in [world*rows_per_rank rows] -> out [rows_per_rank rows] (this rank's block).
 int tbv_comm_reduce_scatter(tbv_comm* c, const void* in, void* out, size_t out_bytes,

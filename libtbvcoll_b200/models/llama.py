@@ -9,8 +9,10 @@ the weight fusions it names (q/k/v -> qkv, gate/up -> gate_up, :38).  Per layer:
     -> all-reduce + residual + RMSNorm (ONE kernel)  -> gate_up GEMM with SiLU-mul epilogue
     -> down_proj GEMM (partial sums) -> all-reduce + residual + next RMSNorm (ONE kernel)
 
-i.e. 7 launches per layer and the two row-parallel all-reduces the reference's hook
-intercepts (2 per layer; step3b/vllm_tp_bench.py:87-124) never appear as separate kernels.
+With TP > 1 the o_proj / down_proj GEMM, its all-reduce, the residual add and the norm are ONE
+kernel each (the GEMM epilogue stores into the peers' memory), i.e. 5 launches per layer, and
+the two row-parallel all-reduces the reference's hook intercepts (2 per layer;
+step3b/vllm_tp_bench.py:87-124) never appear as separate kernels.
 All buffers are preallocated so a decode step can be captured in a CUDA graph.
 """
 from __future__ import annotations
@@ -80,12 +82,10 @@ class LlamaTP:
             ops.rope_kv(qkv, positions, self.cos_sin, slot_mapping, self.k_cache[l], self.v_cache[l], self.nq, self.nkv, self.D)
             ops.paged_attention(q_view, self.k_cache[l], self.v_cache[l], block_tables, ctx_lens, attn_view, self.scale,
                                 self.block_size, seq_of_query=seq_of_query, splits=attn_splits, workspace=self.attn_ws)
-            ops.gemm(attn, w[p + "o.weight"], out=part)
-            tp.all_reduce_add_rmsnorm(part, h, w[p + "post_norm"], cfg.rms_eps)        # part := norm(h), h += sum
+            tp.gemm_all_reduce_add_rmsnorm(attn, w[p + "o.weight"], h, w[p + "post_norm"], cfg.rms_eps, out=part)   # part := norm(h), h += sum
             ops.gemm(part, w[p + "gate_up.weight"], out=act, epi=ops.EPI_SILU_MUL)
-            ops.gemm(act, w[p + "down.weight"], out=xn)
             nxt = w[f"layers.{l + 1}.input_norm"] if l + 1 < cfg.num_layers else w["norm"]
-            tp.all_reduce_add_rmsnorm(xn, h, nxt, cfg.rms_eps)                          # xn := norm(h) for the next layer
+            tp.gemm_all_reduce_add_rmsnorm(act, w[p + "down.weight"], h, nxt, cfg.rms_eps, out=xn)                  # xn := norm(h) for the next layer
         if logit_rows is None:
             xl = xn
         else:

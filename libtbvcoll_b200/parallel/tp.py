@@ -8,6 +8,7 @@ vLLM hook does (step3b/vllm_tp_bench.py:108-124), and counts it.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -22,6 +23,7 @@ class TPGroup:
         self.rank, self.world, self.comm = rank, world, comm
         self.fallback_group = fallback_group
         self.fused_norm_max_bytes = fused_norm_max_bytes
+        self.fuse_gemm = os.environ.get("TBV_FUSE_GEMM_AR", "1") != "0"
         self.calls = 0
         self.fallbacks = 0
         self.launches = 0   # collective kernels launched (for the bench's gpu_launches claim)
@@ -67,6 +69,21 @@ class TPGroup:
         self.fallbacks += 1
         torch.distributed.reduce_scatter_tensor(out, x, group=self.fallback_group)
         return out
+
+    # -- fused: row-parallel GEMM + all-reduce + residual + RMSNorm in one kernel ---------------
+    def gemm_all_reduce_add_rmsnorm(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor, eps: float,
+                                    out: torch.Tensor):
+        """out := RMSNorm(h) * gamma, residual := h, with h = sum over ranks of (x @ w^T) + residual.
+        One kernel (tcgen05 GEMM whose epilogue stores into the peers' slot memory) when the
+        library takes the shape, else GEMM followed by ``all_reduce_add_rmsnorm``."""
+        if self.world > 1 and self.comm is not None and self.fuse_gemm:
+            self.calls += 1
+            if self.comm.gemm_all_reduce_rmsnorm(x, w, residual, gamma, eps, out):
+                self.launches += 1
+                return out, residual
+            self.calls -= 1
+        ops.gemm(x, w, out=out)
+        return self.all_reduce_add_rmsnorm(out, residual, gamma, eps)
 
     # -- fused: all-reduce + residual + RMSNorm ---------------------------------------------
     def all_reduce_add_rmsnorm(self, x: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor, eps: float):

@@ -70,6 +70,13 @@ def load_library(so: Optional[str] = None) -> ctypes.CDLL:
     l.tbv_comm_allreduce_rmsnorm.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, ctypes.c_int, ctypes.c_int, ctypes.c_float, c_vp]
     l.tbv_comm_allreduce_rmsnorm_local.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), c_vp, ctypes.POINTER(c_vp),
                                                    ctypes.POINTER(c_vp), ctypes.c_int, ctypes.c_int, ctypes.c_float, c_vp]
+    l.tbv_comm_gemm_allreduce_rmsnorm.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                  ctypes.c_int, ctypes.c_float, c_vp]
+    l.tbv_comm_gemm_allreduce_rmsnorm.restype = ctypes.c_int
+    l.tbv_comm_gemm_allreduce_rmsnorm_local.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), c_vp,
+                                                        ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), ctypes.c_int, ctypes.c_int,
+                                                        ctypes.c_int, ctypes.c_int, ctypes.c_float, c_vp]
+    l.tbv_comm_gemm_allreduce_rmsnorm_local.restype = ctypes.c_int
     l.tbv_comm_reduce_scatter.argtypes = [c_vp, c_vp, c_vp, ctypes.c_size_t, ctypes.c_int, c_vp]
     l.tbv_comm_all_gather.argtypes = [c_vp, c_vp, c_vp, ctypes.c_size_t, c_vp]
     l.tbv_comm_sync.argtypes = [c_vp]
@@ -210,6 +217,40 @@ class Comm:
             return False
         if rc != 0:
             raise RuntimeError(f"tbv_comm_allreduce_rmsnorm_local failed rc={rc}")
+        return True
+
+    def gemm_all_reduce_rmsnorm(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor, eps: float,
+                                y: torch.Tensor, residual_out: Optional[torch.Tensor] = None) -> bool:
+        """ONE kernel for a row-parallel layer and what follows it: h = bf16(sum over ranks of
+        bf16(x @ w^T)) + residual -> ``residual_out`` (default: in place over ``residual``),
+        RMSNorm(h) * gamma -> ``y``.  x: [T, K/tp] (rows may be strided), w: [H, K/tp].  False ->
+        compose gemm + all_reduce_rmsnorm instead (T > 256, shapes the kernel does not take, ...)."""
+        if x.dtype is not torch.bfloat16 or not x.is_cuda or x.stride(1) != 1 or not w.is_contiguous():
+            return False
+        residual_out = residual if residual_out is None else residual_out
+        T, K = x.shape
+        H = w.shape[0]
+        rc = self._l.tbv_comm_gemm_allreduce_rmsnorm(self._h, c_vp(w.data_ptr()), c_vp(x.data_ptr()), c_vp(residual.data_ptr()),
+                                                     c_vp(gamma.data_ptr()), c_vp(residual_out.data_ptr()), c_vp(y.data_ptr()), T, H, K,
+                                                     x.stride(0), eps, _stream_of(x))
+        if rc == -2:
+            return False
+        if rc != 0:
+            raise RuntimeError(f"tbv_comm_gemm_allreduce_rmsnorm failed rc={rc}")
+        return True
+
+    def gemm_all_reduce_rmsnorm_local(self, xs, ws, residuals, gamma, eps, ys, residual_outs=None) -> bool:
+        n = self.world
+        residual_outs = residuals if residual_outs is None else residual_outs
+        T, K = xs[0].shape
+        H = ws[0].shape[0]
+        arr = lambda ts: (c_vp * n)(*[t.data_ptr() for t in ts])
+        rc = self._l.tbv_comm_gemm_allreduce_rmsnorm_local(self._h, arr(ws), arr(xs), arr(residuals), c_vp(gamma.data_ptr()),
+                                                           arr(residual_outs), arr(ys), T, H, K, xs[0].stride(0), eps, _stream_of(xs[0]))
+        if rc == -2:
+            return False
+        if rc != 0:
+            raise RuntimeError(f"tbv_comm_gemm_allreduce_rmsnorm_local failed rc={rc}")
         return True
 
     def reduce_scatter(self, t: torch.Tensor, out: torch.Tensor) -> bool:

@@ -128,3 +128,34 @@ def test_fused_allreduce_residual_rmsnorm(world, T, H):
             assert (ys[r].float() - want_y.float()).abs().max().item() <= 2 ** -6 * want_y.float().abs().max().item()
     finally:
         c.destroy()
+
+
+@pytest.mark.parametrize("world,T,H,K", [(2, 8, 512, 256), (4, 5, 1024, 1024), (2, 64, 4096, 2048), (2, 130, 512, 512)])
+def test_fused_gemm_allreduce_residual_rmsnorm_emulated(world, T, H, K):
+    """Row-parallel GEMM whose epilogue stores into every rank's slot memory, then reduce +
+    residual + RMSNorm, all in one kernel; ranks emulated on one GPU."""
+    from libtbvcoll_b200.tbvcoll import Comm
+    from libtbvcoll_b200.ops import reference as ref
+    c = Comm.local(world, 0, cap_bytes=T * H * 2)
+    try:
+        g = torch.Generator().manual_seed(5)
+        xs = [(torch.randn(T, K, generator=g)).to(torch.bfloat16).to(DEV) for _ in range(world)]
+        ws = [(torch.randn(H, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV) for _ in range(world)]
+        res0 = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+        gamma = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).to(DEV)
+        for rep in range(3):      # several calls: slot ring and sequence numbers advance
+            res = [res0.clone() for _ in range(world)]
+            ys = [torch.zeros(T, H, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+            ok = c.gemm_all_reduce_rmsnorm_local(xs, ws, res, gamma, 1e-5, ys)
+            assert ok, "the fused kernel declined a shape it should take"
+            torch.cuda.synchronize()
+            assert not c.err()
+            partials = [ref.gemm(x, w).to(torch.bfloat16) for x, w in zip(xs, ws)]
+            want_y, want_h = ref.ar_residual_rmsnorm(partials, res0, gamma, 1e-5)
+            for r in range(world):
+                assert torch.equal(res[r], res[0]) and torch.equal(ys[r], ys[0])         # identical bits on every rank
+            tol_h = 2 ** -6 * want_h.float().abs().max().item()
+            assert (res[0].float() - want_h.float()).abs().max().item() <= tol_h
+            assert (ys[0].float() - want_y.float()).abs().max().item() <= 2 ** -5 * want_y.float().abs().max().item()
+    finally:
+        c.destroy()

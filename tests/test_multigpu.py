@@ -3,7 +3,7 @@ Run with 2 or more GPUs visible, e.g. ``pytest tests/test_multigpu.py -m gpu``."
 import pytest
 import torch
 
-from _workers import run_ranks, gpu_collectives, gpu_engine_tp, gpu_peer_skips
+from _workers import run_ranks, gpu_collectives, gpu_engine_tp, gpu_peer_skips, gpu_fused_gemm_ar
 from conftest import free_port
 
 pytestmark = pytest.mark.gpu
@@ -43,3 +43,11 @@ def test_peer_drops_a_call_device_watchdog():
     assert r0["first"] == 2.0 and r0["err"] and r0["refused"] and r0["alive"] == 16.0
     assert 0.4 < r0["elapsed"] < 10
     assert r0["last"]["code"] == 1 and r0["last"]["peer"] == 1
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs >= 2 GPUs")
+def test_fused_gemm_allreduce_rmsnorm_real_ranks():
+    for world in _worlds():
+        res = run_ranks(gpu_fused_gemm_ar, world, free_port(), timeout=300)
+        assert all(r["ok"] and not r["err"] for r in res)
+        assert all(r["hashes"] == res[0]["hashes"] for r in res)      # identical bits on every rank
