@@ -38,16 +38,26 @@ struct TraceRec {
   unsigned int algo, nchan;
 };
 
-// Host-mapped mirror written by kernels, read by the host without a sync.
+// Device-resident diagnostics written on every call: breadcrumbs and the timing ring.  They
+// live in device memory on purpose: a store to host memory ahead of a system-scope fence
+// would put a PCIe round trip on the critical path of every collective.  The host copies
+// them out in the statistics getters; on a watchdog expiry the kernel copies the breadcrumbs
+// into the host-mapped record below.
+struct DevMirror {
+  unsigned long long bc[8];  // breadcrumbs: 0 enter, 1 pushed, 2 wait-pass, 3 done (seq values)
+  unsigned long long tag_bad;
+  TraceRec ring[kTraceN];
+};
+
+// Host-mapped error record, written only when a wait gives up; the host reads it without a sync.
 struct HostMirror {
   unsigned int err;       // same code as DevState::err
   unsigned int where;     // wait site that gave up (kWhere*)
   unsigned int peer;      // rank that did not arrive
   unsigned int chan;
   unsigned long long err_seq;
-  unsigned long long bc[8];  // breadcrumbs: 0 enter, 1 pushed, 2 wait-pass, 3 done (seq values)
+  unsigned long long bc[8];  // copy of the breadcrumbs at the time of the error
   unsigned long long tag_bad;
-  TraceRec ring[kTraceN];
 };
 
 enum : unsigned { kErrNone = 0, kErrTimeout = 1, kErrTag = 2 };
@@ -63,6 +73,7 @@ struct RankCtx {
   unsigned int* flags[TBV_MAXRANK];
   char* mc_data;                   // multicast (NVLS) mapping of the slot memory, or null
   DevState* st;
+  DevMirror* dm;
   HostMirror* hm;
 };
 
@@ -102,6 +113,7 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
 __device__ __forceinline__ void report_error(const RankCtx& c, unsigned code, unsigned where,
                                              int peer, int chan, unsigned long long seq) {
   if (atomicCAS(&c.st->err, 0u, code) == 0u) {
+    for (int i = 0; i < 8; i++) c.hm->bc[i] = c.dm->bc[i];
     c.hm->where = where;
     c.hm->peer = unsigned(peer);
     c.hm->chan = unsigned(chan);
@@ -213,16 +225,18 @@ __device__ __forceinline__ void call_end(const RankCtx& c, const CallInfo& ci, u
                                          unsigned long long nbytes, unsigned algo) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
+    TraceRec* r = &c.dm->ring[ci.seq & (kTraceN - 1)];
+    if (t_enter) { r->t_enter = t_enter; r->nbytes = nbytes; r->algo = algo; r->nchan = nctas; }
+    if (t_ready) r->t_ready = t_ready;
+    // No fence: the next kernel on the stream starts after this grid has completed (or, with
+    // programmatic dependent launch, passes its dependency wait only then), which orders
+    // everything written here before it.
     unsigned old = atomicAdd(&c.st->arrive, 1u);
     if (old == nctas - 1) {
       c.st->arrive = 0;
-      TraceRec* r = &c.hm->ring[ci.seq & (kTraceN - 1)];
-      r->t_enter = t_enter; r->t_ready = t_ready; r->t_done = globaltimer();
-      r->nbytes = nbytes; r->algo = algo; r->nchan = nctas;
+      r->t_done = globaltimer();
       r->seq = ci.seq;
-      c.hm->bc[3] = ci.seq;
-      __threadfence();
+      c.dm->bc[3] = ci.seq;
       *(volatile unsigned long long*)&c.st->seq = ci.seq;
     }
   }
@@ -262,7 +276,7 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   const size_t per = (units + nchan - 1) / nchan;
   const size_t u0 = per * chan;
   const size_t u1 = (u0 + per < units) ? (u0 + per) : units;
-  if (chan == 0 && threadIdx.x == 0) c.hm->bc[0] = ci.seq;
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
 
   // push my range to every peer's [slot][src = me] region
   for (size_t u = u0 + threadIdx.x; u < u1; u += blockDim.x) {
@@ -284,17 +298,17 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   }
   __syncthreads();
   publish(c, ci, 0, chan);
-  if (chan == 0 && threadIdx.x == 0) c.hm->bc[1] = ci.seq;
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
   wait_all(c, ci, 0, chan, kWherePhase0);
   unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   if (chan == 0 && threadIdx.x == 0) {
-    c.hm->bc[2] = ci.seq;
+    c.dm->bc[2] = ci.seq;
     if (c.debug_tag) {
       for (int p = 0; p < c.world; p++) {
         if (p == c.rank) continue;
         unsigned long long tag = *reinterpret_cast<volatile unsigned long long*>(
             slot_region(c, c.rank, ci.slot, p) + c.cap - 8);
-        if (tag != ci.seq) { atomicAdd(&c.st->tag_bad, 1u); c.hm->tag_bad += 1; }
+        if (tag != ci.seq) { atomicAdd(&c.st->tag_bad, 1u); c.dm->tag_bad += 1; }
       }
     }
   }
@@ -347,7 +361,7 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   const size_t cu = (units + c.world - 1) / c.world;     // units per rank chunk
   const size_t per = (cu + nchan - 1) / nchan;           // units per channel inside a chunk
   const int W = c.world, me = c.rank;
-  if (chan == 0 && threadIdx.x == 0) c.hm->bc[0] = ci.seq;
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
   const int R = W;  // index of the result region inside a slot
   unsigned long long t_ready = 0;
 
@@ -371,9 +385,9 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
     }
     __syncthreads();
     publish(c, ci, 0, chan);
-    if (chan == 0 && threadIdx.x == 0) c.hm->bc[1] = ci.seq;
+    if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
     wait_all(c, ci, 0, chan, kWherePhase0);
-    if (threadIdx.x == 0 && chan == 0) { t_ready = globaltimer(); c.hm->bc[2] = ci.seq; }
+    if (threadIdx.x == 0 && chan == 0) { t_ready = globaltimer(); c.dm->bc[2] = ci.seq; }
   }
 
   {
@@ -498,7 +512,7 @@ __device__ void ar_nvls_body(const RankCtx& c, const T* __restrict__ in, T* out,
   const size_t per = (cu + nchan - 1) / nchan;
   const int W = c.world, me = c.rank;
   const int R = W;
-  if (chan == 0 && threadIdx.x == 0) c.hm->bc[0] = ci.seq;
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
   // stage: region 0 of my own slot memory; channel `chan` stages its sub-range of EVERY chunk
   uint4* stage = reinterpret_cast<uint4*>(slot_region(c, me, ci.slot, 0));
   for (int r = 0; r < W; r++) {
@@ -511,7 +525,7 @@ __device__ void ar_nvls_body(const RankCtx& c, const T* __restrict__ in, T* out,
   }
   __syncthreads();
   publish(c, ci, 0, chan);
-  if (chan == 0 && threadIdx.x == 0) c.hm->bc[1] = ci.seq;
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
   wait_all(c, ci, 0, chan, kWherePhase0);
   unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   {
@@ -606,7 +620,7 @@ __device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __
   unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   CallInfo ci = call_begin(c, sh_seq);
   const int upr = hidden / 8;  // 16-byte units per row
-  if (chan == 0 && threadIdx.x == 0) c.hm->bc[0] = ci.seq;
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
   for (int row = chan; row < tokens; row += nchan) {
     const uint4* src = reinterpret_cast<const uint4*>(x) + size_t(row) * upr;
     for (int u = threadIdx.x; u < upr; u += blockDim.x) {
@@ -618,7 +632,7 @@ __device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __
   }
   __syncthreads();
   publish(c, ci, 0, chan);
-  if (chan == 0 && threadIdx.x == 0) c.hm->bc[1] = ci.seq;
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
   wait_all(c, ci, 0, chan, kWhereFused);
   unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   for (int row = chan; row < tokens; row += nchan) {

@@ -253,6 +253,7 @@ static void fill_ctx(tbv_comm* c, GpuRank& g, int rank) {
   x.slot_stride = size_t(c->world + 1) * c->cap;
   x.wdog_ns = (unsigned long long)(c->knobs.wdog_s * 1e9);
   x.st = g.st;
+  x.dm = g.dm;
   x.hm = g.hm_dev;
   x.mc_data = c->mc_base ? c->mc_base + c->flag_bytes : nullptr;
 }
@@ -260,6 +261,8 @@ static void fill_ctx(tbv_comm* c, GpuRank& g, int rank) {
 static int alloc_rank_state(tbv_comm* c, GpuRank& g) {
   CUDA_TRY(c, cudaMalloc(&g.st, sizeof(DevState)));
   CUDA_TRY(c, cudaMemset(g.st, 0, sizeof(DevState)));
+  CUDA_TRY(c, cudaMalloc(&g.dm, sizeof(DevMirror)));
+  CUDA_TRY(c, cudaMemset(g.dm, 0, sizeof(DevMirror)));
   CUDA_TRY(c, cudaHostAlloc(&g.hm, sizeof(HostMirror), cudaHostAllocMapped | cudaHostAllocPortable));
   memset(g.hm, 0, sizeof(HostMirror));
   CUDA_TRY(c, cudaHostGetDevicePointer(&g.hm_dev, g.hm, 0));
@@ -541,12 +544,15 @@ static bool check_err(tbv_comm* c) {
 // Fold finished calls' device timestamps into the statistics (lazy: runs in the getters).
 static void harvest_trace(tbv_comm* c) {
   if (c->cpu || c->ranks.empty()) return;
-  HostMirror* hm = c->ranks[0].hm;
   unsigned long long upto = c->host_seq;
+  if (upto == c->trace_read) return;
+  c->trace_host.resize(kTraceN);
+  // device -> host copy of the ring (the getters are off the hot path)
+  if (cudaMemcpy(c->trace_host.data(), c->ranks[0].dm->ring, sizeof(TraceRec) * kTraceN, cudaMemcpyDeviceToHost) != cudaSuccess) return;
   if (upto - c->trace_read > kTraceN) c->trace_read = upto - kTraceN;
   for (unsigned long long s = c->trace_read + 1; s <= upto; s++) {
-    const TraceRec& r = hm->ring[s & (kTraceN - 1)];
-    if (*(volatile const unsigned long long*)&r.seq != s) break;  // not finished yet
+    const TraceRec& r = c->trace_host[s & (kTraceN - 1)];
+    if (r.seq != s) break;  // not finished yet
     double xfer = r.t_ready > r.t_enter ? (r.t_ready - r.t_enter) * 1e-3 : 0.0;
     double post = r.t_done > r.t_ready && r.t_ready ? (r.t_done - r.t_ready) * 1e-3 : 0.0;
     c->stats.add_xfer(size_t(r.nbytes), 0.0, xfer, post, 0.0, int(r.nchan), int(r.algo));
@@ -804,6 +810,7 @@ int tbv_comm_destroy(tbv_comm* c) {
     for (auto& g : c->ranks) {
       if (c->local && g.base) cudaFree(g.base);
       if (g.st) cudaFree(g.st);
+      if (g.dm) cudaFree(g.dm);
       if (g.hm) cudaFreeHost(g.hm);
     }
     if (c->ctxs_dev) cudaFree(c->ctxs_dev);
@@ -933,7 +940,10 @@ void tbv_comm_hist(tbv_comm* c) {
   if (!c) return;
   harvest_trace(c);
   unsigned long long bad = 0;
-  for (auto& g : c->ranks) bad += g.hm ? g.hm->tag_bad : 0;
+  for (auto& g : c->ranks) {
+    unsigned long long v = 0;
+    if (g.dm && cudaMemcpy(&v, &g.dm->tag_bad, sizeof(v), cudaMemcpyDeviceToHost) == cudaSuccess) bad += v;
+  }
   c->stats.dump_hist(c->rank, bad);
 }
 void tbv_comm_last_error(tbv_comm* c, unsigned long long out[4]) {

@@ -39,6 +39,7 @@ struct GpuRank {  // one (real or emulated) rank's device resources
   char* base = nullptr;        // flags + data, this rank's own allocation
   size_t alloc_bytes = 0;
   DevState* st = nullptr;
+  DevMirror* dm = nullptr;     // device memory: breadcrumbs + timing ring
   HostMirror* hm = nullptr;    // host pointer
   HostMirror* hm_dev = nullptr;
   RankCtx ctx{};
@@ -68,6 +69,7 @@ struct tbv_comm {
   std::atomic<int> skip{0};
   std::atomic<int> sticky_err{0};
   unsigned long long host_seq = 0, trace_read = 0;
+  std::vector<tbv::TraceRec> trace_host;   // staging for the timing ring
   void* last_stream = nullptr;
   std::vector<void*> streams_seen;
   std::string errmsg;

@@ -39,7 +39,7 @@ struct FusedPtrs {
   __nv_bfloat16* residual_out[TBV_MAXRANK];
   __nv_bfloat16* y[TBV_MAXRANK];
 };
-constexpr int kMaxWaiters = 32;
+constexpr int kMaxWaiters = 128;  // CTAs that stay for the reduce + norm phase (at most half the grid)
 constexpr int kFusedMaxUnits = 6;  // 16-byte units per thread in the norm phase: hidden <= 8 * 6 * 192 = 9216
 
 __global__ void __launch_bounds__(gemm::kThreads, 1)
@@ -127,6 +127,12 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
       }
     }
   }
+  // Every CTA makes its own remote stores visible at system scope before it joins the cluster
+  // barrier, so the one flag per M tile that follows covers all K-split slices.
+  if (warp >= 2) {
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (threadIdx.x == 64) fence_sys();
+  }
   __syncwarp();
   if (S > 1) cluster_sync_all(); else __syncthreads();  // all slices of this M tile are stored; peers' shared memory no longer needed
   gemm::teardown(p, s);                                   // TMEM back before the waiting phase
@@ -134,13 +140,13 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
     fence_sys();
     for (int peer = 0; peer < c.world; peer++)
       st_relaxed_sys(c.flags[peer] + flag_index(c, ci.slot, 0, c.rank, m_tile), ci.want);
-    if (m_tile == 0) c.hm->bc[1] = ci.seq;
+    if (m_tile == 0) c.dm->bc[1] = ci.seq;
   }
 
   // ---- a few CTAs finish the job: wait for every tile of every rank, reduce, residual, norm ----
   const int n_cta = gridDim.x * S, cta_id = m_tile * S + split;
   int waiters = T < kMaxWaiters ? T : kMaxWaiters;
-  if (waiters > n_cta) waiters = n_cta;
+  if (waiters > n_cta / 2) waiters = n_cta / 2 > 0 ? n_cta / 2 : 1;
   unsigned long long t_ready = 0;
   if (cta_id < waiters) {
     const int n_tiles = gridDim.x;
@@ -149,7 +155,7 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
       wait_flag(c, c.flags[c.rank] + flag_index(c, ci.slot, 0, src, ch), ci.want, kWhereFused, src, ch, ci.seq);
     }
     __syncthreads();
-    if (threadIdx.x == 0 && cta_id == 0) { t_ready = tbv::globaltimer(); c.hm->bc[2] = ci.seq; }
+    if (threadIdx.x == 0 && cta_id == 0) { t_ready = tbv::globaltimer(); c.dm->bc[2] = ci.seq; }
     const int upr = H / 8;
     for (int row = cta_id; row < T; row += waiters) {
       float h[kFusedMaxUnits][8];

@@ -333,8 +333,8 @@ class Comm:
 
     def ctx_blob(self) -> bytes:
         """The device-side context (peer pointers etc.) that fused kernels take by value."""
-        buf = ctypes.create_string_buffer(192)
-        if self._l.tbv_comm_ctx(self._h, buf, 192) != 0:
+        buf = ctypes.create_string_buffer(200)
+        if self._l.tbv_comm_ctx(self._h, buf, 200) != 0:
             raise RuntimeError("tbv_comm_ctx failed")
         return buf.raw
 
