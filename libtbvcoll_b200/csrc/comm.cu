@@ -946,6 +946,13 @@ void tbv_comm_hist(tbv_comm* c) {
   }
   c->stats.dump_hist(c->rank, bad);
 }
+// Device breadcrumbs of (emulated) rank r: bc[0..3] = sequence numbers at enter / pushed /
+// wait-pass / done; bc[4..7] = %globaltimer stamps of the last fused GEMM call (accumulator
+// ready, flag published, all tiles arrived, kernel entry).  Synchronous copy.
+int tbv_comm_breadcrumbs(tbv_comm* c, int r, unsigned long long out[8]) {
+  if (!c || c->cpu || r < 0 || r >= int(c->ranks.size())) return TBV_FAIL;
+  return cudaMemcpy(out, c->ranks[r].dm->bc, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? TBV_OK : TBV_FAIL;
+}
 void tbv_comm_last_error(tbv_comm* c, unsigned long long out[4]) {
   out[0] = out[1] = out[2] = out[3] = 0;
   if (!c) return;

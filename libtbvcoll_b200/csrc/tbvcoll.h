@@ -111,6 +111,8 @@ void tbv_comm_hist(tbv_comm* c);
 // Last device breadcrumbs / watchdog record, for tests: out[0]=err code, out[1]=seq,
 // out[2]=where, out[3]=peer.
 void tbv_comm_last_error(tbv_comm* c, unsigned long long out[4]);
+// Device breadcrumbs of (emulated) rank r (see comm.cu); synchronous device-to-host copy.
+int tbv_comm_breadcrumbs(tbv_comm* c, int r, unsigned long long out[8]);
 
 // ---- process-global API with the reference's names ------------------------------
 // devs: "cpu" selects the CPU backend, "cuda:N" / "N" a device; any other string

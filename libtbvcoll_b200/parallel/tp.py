@@ -23,7 +23,10 @@ class TPGroup:
         self.rank, self.world, self.comm = rank, world, comm
         self.fallback_group = fallback_group
         self.fused_norm_max_bytes = fused_norm_max_bytes
-        self.fuse_gemm = os.environ.get("TBV_FUSE_GEMM_AR", "1") != "0"
+        # One-kernel GEMM + all-reduce + norm.  Off by default: at decode sizes the two-kernel form
+        # (GEMM, then fused all-reduce + norm overlapped by programmatic dependent launch) measures
+        # faster; TBV_FUSE_GEMM_AR=1 selects the single kernel.
+        self.fuse_gemm = os.environ.get("TBV_FUSE_GEMM_AR", "0") == "1"
         self.calls = 0
         self.fallbacks = 0
         self.launches = 0   # collective kernels launched (for the bench's gpu_launches claim)

@@ -94,6 +94,8 @@ def load_library(so: Optional[str] = None) -> ctypes.CDLL:
     l.tbv_comm_rails.argtypes = [c_vp]
     l.tbv_comm_hist.argtypes = [c_vp]
     l.tbv_comm_last_error.argtypes = [c_vp, c_ullp]
+    l.tbv_comm_breadcrumbs.argtypes = [c_vp, ctypes.c_int, c_ullp]
+    l.tbv_comm_breadcrumbs.restype = ctypes.c_int
     for n in ("tbv_comm_create", "tbv_comm_create_local", "tbv_comm_destroy", "tbv_comm_allreduce", "tbv_comm_allreduce_local",
               "tbv_comm_allreduce_rmsnorm", "tbv_comm_allreduce_rmsnorm_local", "tbv_comm_reduce_scatter", "tbv_comm_all_gather",
               "tbv_comm_sync", "tbv_comm_set_algo", "tbv_comm_set_nchan", "tbv_comm_set_wdog", "tbv_comm_skip_next", "tbv_comm_ctx"):
@@ -318,6 +320,13 @@ class Comm:
         a = (ctypes.c_ulonglong * 4)()
         self._l.tbv_comm_last_error(self._h, a)
         return {"code": a[0], "seq": a[1], "where": a[2], "peer": a[3]}
+
+    def breadcrumbs(self, r: int = 0):
+        """Device breadcrumbs of (emulated) rank r: 8 integers (see tbv_comm_breadcrumbs)."""
+        a = (ctypes.c_ulonglong * 8)()
+        if self._l.tbv_comm_breadcrumbs(self._h, r, a) != 0:
+            raise RuntimeError("tbv_comm_breadcrumbs failed")
+        return list(a)
 
     def stats5(self):
         v = [ctypes.c_double() for _ in range(5)]
