@@ -64,7 +64,7 @@ Knobs Knobs::from_env() {
   k.nchan = int(env_long("TBV_NCHAN", 0));
   k.nvls = int(env_long("TBV_NVLS", 0));
   k.init_timeout_s = env_double("TBV_INIT_TIMEOUT", 60.0);
-  k.nvls_min = env_long("TBV_NVLS_MIN", 1 << 20);
+  k.nvls_min = env_long("TBV_NVLS_MIN", LONG_MAX);  // auto never picks the switch-reduced kernel unless asked
   const char* a = getenv("TBV_ALGO");
   if (a) {
     if (!strcmp(a, "oneshot")) k.algo = TBV_ALGO_ONESHOT;

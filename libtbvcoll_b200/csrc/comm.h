@@ -30,7 +30,7 @@ struct Knobs {
   int nvls = 0;           // TBV_NVLS: 1 = set up a multicast object and allow the NVLS kernels
   int mem = 0;            // TBV_MEM: 0 = VMM with IPC fallback, 1 = VMM only, 2 = cudaIpc only
   double init_timeout_s = 60.0;  // TBV_INIT_TIMEOUT
-  long nvls_min = 1 << 20;       // TBV_NVLS_MIN: smallest message for NVLS in auto mode
+  long nvls_min = 0x7fffffffffffffffl;  // TBV_NVLS_MIN: smallest message for the switch-reduced kernel in auto mode
   static Knobs from_env();
 };
 

@@ -76,6 +76,23 @@ int tbv_comm_gemm_allreduce_rmsnorm_local(tbv_comm* c, const void* const* ws, co
                                           const void* const* residuals, const void* gamma,
                                           void* const* residual_outs, void* const* ys, int tokens,
                                           int hidden, int k_local, int ldx, float eps, void* stream);
+// Sequence-parallel prefill pairs (tcgen05 GEMM fused with its collective; see ops/gemm_sp.cu).
+// GEMM -> reduce-scatter: x [tokens, k_local], w [hidden, k_local]; tokens % world == 0.  This rank
+// receives rows [rank*tokens/world, ...) of the rank-ordered sum.  mode 0: out = sum;
+// mode 1: h = sum + residual -> residual_out, y = RMSNorm(h) * gamma (all [tokens/world, hidden]).
+int tbv_comm_gemm_reduce_scatter(tbv_comm* c, const void* w, const void* x, void* out, const void* residual,
+                                 const void* gamma, void* residual_out, void* y, int tokens, int hidden,
+                                 int k_local, int ldx, float eps, int mode, void* stream);
+int tbv_comm_gemm_reduce_scatter_local(tbv_comm* c, const void* const* ws, const void* const* xs, void* const* outs,
+                                       const void* const* residuals, const void* gamma, void* const* residual_outs,
+                                       void* const* ys, int tokens, int hidden, int k_local, int ldx, float eps,
+                                       int mode, void* stream);
+// all-gather -> GEMM: x [rows_per_rank, K] (this rank's token rows), w [M, K]; y [world*rows_per_rank, M].
+// The first call for a shape allocates a small table of tensor maps: make it outside stream capture.
+int tbv_comm_allgather_gemm(tbv_comm* c, const void* w, const void* x, void* y, int rows_per_rank, int M, int K,
+                            int ldx, int ldy, void* stream);
+int tbv_comm_allgather_gemm_local(tbv_comm* c, const void* const* ws, const void* const* xs, void* const* ys,
+                                  int rows_per_rank, int M, int K, int ldx, int ldy, void* stream);
 // reduce-scatter / all-gather over the same slot ring (rows of `row_bytes`).
 // reduce_scatter: in [world*rows_per_rank rows] -> out [rows_per_rank rows] (this rank's block).
 int tbv_comm_reduce_scatter(tbv_comm* c, const void* in, void* out, size_t out_bytes,

@@ -77,6 +77,13 @@ def load_library(so: Optional[str] = None) -> ctypes.CDLL:
                                                         ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), ctypes.c_int, ctypes.c_int,
                                                         ctypes.c_int, ctypes.c_int, ctypes.c_float, c_vp]
     l.tbv_comm_gemm_allreduce_rmsnorm_local.restype = ctypes.c_int
+    PP, I, F = ctypes.POINTER(c_vp), ctypes.c_int, ctypes.c_float
+    l.tbv_comm_gemm_reduce_scatter.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, I, F, I, c_vp]
+    l.tbv_comm_gemm_reduce_scatter_local.argtypes = [c_vp, PP, PP, PP, PP, c_vp, PP, PP, I, I, I, I, F, I, c_vp]
+    l.tbv_comm_allgather_gemm.argtypes = [c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, c_vp]
+    l.tbv_comm_allgather_gemm_local.argtypes = [c_vp, PP, PP, PP, I, I, I, I, I, c_vp]
+    for n in ("tbv_comm_gemm_reduce_scatter", "tbv_comm_gemm_reduce_scatter_local", "tbv_comm_allgather_gemm", "tbv_comm_allgather_gemm_local"):
+        getattr(l, n).restype = I
     l.tbv_comm_reduce_scatter.argtypes = [c_vp, c_vp, c_vp, ctypes.c_size_t, ctypes.c_int, c_vp]
     l.tbv_comm_all_gather.argtypes = [c_vp, c_vp, c_vp, ctypes.c_size_t, c_vp]
     l.tbv_comm_sync.argtypes = [c_vp]
@@ -254,6 +261,54 @@ class Comm:
         if rc != 0:
             raise RuntimeError(f"tbv_comm_gemm_allreduce_rmsnorm_local failed rc={rc}")
         return True
+
+    @staticmethod
+    def _rc(rc: int, name: str) -> bool:
+        if rc == -2:
+            return False
+        if rc != 0:
+            raise RuntimeError(f"{name} failed rc={rc}")
+        return True
+
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+                            gamma: Optional[torch.Tensor] = None, eps: float = 1e-5, y: Optional[torch.Tensor] = None) -> bool:
+        """Row-parallel GEMM whose tile epilogues scatter over NVLink, then the owner of each token
+        row reduces it.  x: [T, K/tp], w: [H, K/tp].  With ``out`` [T/tp, H]: out = this rank's rows
+        of the sum.  With ``residual`` (updated in place), ``gamma`` and ``y``: residual += sum,
+        y = RMSNorm(residual) * gamma on the local T/tp rows (sequence-parallel prefill)."""
+        T, K = x.shape
+        mode = 0 if residual is None else 1
+        p = lambda t: c_vp(t.data_ptr()) if t is not None else None
+        rc = self._l.tbv_comm_gemm_reduce_scatter(self._h, p(w), p(x), p(out), p(residual), p(gamma), p(residual), p(y), T, w.shape[0], K,
+                                                  x.stride(0), eps, mode, _stream_of(x))
+        return self._rc(rc, "tbv_comm_gemm_reduce_scatter")
+
+    def gemm_reduce_scatter_local(self, xs, ws, outs=None, residuals=None, gamma=None, eps=1e-5, ys=None) -> bool:
+        n = self.world
+        T, K = xs[0].shape
+        mode = 0 if residuals is None else 1
+        arr = lambda ts: (c_vp * n)(*[t.data_ptr() for t in ts]) if ts is not None else (c_vp * n)()
+        rc = self._l.tbv_comm_gemm_reduce_scatter_local(self._h, arr(ws), arr(xs), arr(outs), arr(residuals),
+                                                        c_vp(gamma.data_ptr()) if gamma is not None else None, arr(residuals), arr(ys),
+                                                        T, ws[0].shape[0], K, xs[0].stride(0), eps, mode, _stream_of(xs[0]))
+        return self._rc(rc, "tbv_comm_gemm_reduce_scatter_local")
+
+    def allgather_gemm(self, x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> bool:
+        """y[world * rows, M] = all_gather(x)[world * rows, K] @ w[M, K]^T.  x: this rank's token rows.
+        Remote rows are staged in this GPU's memory and loaded by TMA from there as soon as their
+        chunk has arrived; tiles over local rows start immediately."""
+        rows, K = x.shape
+        rc = self._l.tbv_comm_allgather_gemm(self._h, c_vp(w.data_ptr()), c_vp(x.data_ptr()), c_vp(y.data_ptr()), rows, w.shape[0], K,
+                                             x.stride(0), y.stride(0), _stream_of(x))
+        return self._rc(rc, "tbv_comm_allgather_gemm")
+
+    def allgather_gemm_local(self, xs, ws, ys) -> bool:
+        n = self.world
+        rows, K = xs[0].shape
+        arr = lambda ts: (c_vp * n)(*[t.data_ptr() for t in ts])
+        rc = self._l.tbv_comm_allgather_gemm_local(self._h, arr(ws), arr(xs), arr(ys), rows, ws[0].shape[0], K, xs[0].stride(0),
+                                                   ys[0].stride(0), _stream_of(xs[0]))
+        return self._rc(rc, "tbv_comm_allgather_gemm_local")
 
     def reduce_scatter(self, t: torch.Tensor, out: torch.Tensor) -> bool:
         """out = block ``rank`` of the rank-ordered sum of t (t has world * out.numel() elements)."""

@@ -159,3 +159,63 @@ def test_fused_gemm_allreduce_residual_rmsnorm_emulated(world, T, H, K):
             assert (ys[0].float() - want_y.float()).abs().max().item() <= 2 ** -5 * want_y.float().abs().max().item()
     finally:
         c.destroy()
+
+
+@pytest.mark.parametrize("world,T,H,K", [(2, 64, 512, 256), (4, 128, 1024, 512), (2, 512, 4096, 1024), (8, 256, 256, 128)])
+def test_gemm_reduce_scatter_emulated(world, T, H, K):
+    """GEMM whose tile epilogues scatter into the owners' slot memory, then reduce (+ residual + norm)."""
+    from libtbvcoll_b200.tbvcoll import Comm
+    from libtbvcoll_b200 import ops
+    from libtbvcoll_b200.ops import reference as ref
+    rpr = T // world
+    c = Comm.local(world, 0, cap_bytes=rpr * H * 2)
+    try:
+        g = torch.Generator().manual_seed(6)
+        xs = [torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV) for _ in range(world)]
+        ws = [(torch.randn(H, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV) for _ in range(world)]
+        gamma = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).to(DEV)
+        res0 = [torch.randn(rpr, H, generator=g).to(torch.bfloat16).to(DEV) for _ in range(world)]
+        partials = [ops.gemm(x, w, splits=1) for x, w in zip(xs, ws)]          # same kernel arithmetic, no collective
+        torch.cuda.synchronize()
+        total = oracle(partials)
+        for rep in range(3):
+            outs = [torch.zeros(rpr, H, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+            assert c.gemm_reduce_scatter_local(xs, ws, outs=outs)
+            torch.cuda.synchronize()
+            for r in range(world):
+                assert torch.equal(outs[r], total[r * rpr:(r + 1) * rpr]), (rep, r)
+            res = [t.clone() for t in res0]
+            ys = [torch.zeros(rpr, H, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+            assert c.gemm_reduce_scatter_local(xs, ws, residuals=res, gamma=gamma, eps=1e-5, ys=ys)
+            torch.cuda.synchronize()
+            for r in range(world):
+                y2, h2 = ops.add_rmsnorm(total[r * rpr:(r + 1) * rpr].clone(), res0[r].clone(), gamma, 1e-5)
+                assert torch.equal(res[r], h2) and torch.equal(ys[r], y2)       # bit-identical to the unfused pipeline
+        assert not c.err()
+        want = ref.gemm(xs[0], ws[0])
+        assert (partials[0].float() - want).abs().max().item() <= 0.01 * want.abs().max().item() + 1e-3
+    finally:
+        c.destroy()
+
+
+@pytest.mark.parametrize("world,rows,M,K", [(2, 32, 256, 128), (4, 64, 384, 512), (2, 256, 1024, 2048), (8, 16, 128, 64)])
+def test_allgather_gemm_emulated(world, rows, M, K):
+    from libtbvcoll_b200.tbvcoll import Comm
+    from libtbvcoll_b200 import ops
+    c = Comm.local(world, 0, cap_bytes=rows * K * 2)
+    try:
+        g = torch.Generator().manual_seed(8)
+        xs = [torch.randn(rows, K, generator=g).to(torch.bfloat16).to(DEV) for _ in range(world)]
+        ws = [(torch.randn(M, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV) for _ in range(world)]
+        full = torch.cat(xs, 0)
+        for rep in range(3):
+            ys = [torch.zeros(world * rows, M, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+            assert c.allgather_gemm_local(xs, ws, ys)
+            torch.cuda.synchronize()
+            for r in range(world):
+                want = ops.gemm(full, ws[r], splits=1)
+                torch.cuda.synchronize()
+                assert torch.equal(ys[r], want), (rep, r)
+        assert not c.err()
+    finally:
+        c.destroy()
