@@ -79,6 +79,28 @@ __global__ void k_silu_mul(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* _
   *reinterpret_cast<uint4*>(out + t * I + i8) = o4;
 }
 
+// same, for row-interleaved gate/up columns: x[t, 2i] = gate_i, x[t, 2i+1] = up_i
+__global__ void k_silu_mul_interleaved(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int I) {
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
+  const size_t t = blockIdx.y;
+  const int i8 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i8 >= I) return;
+  const uint4 a4 = *reinterpret_cast<const uint4*>(x + t * 2 * I + 2 * i8);
+  const uint4 b4 = *reinterpret_cast<const uint4*>(x + t * 2 * I + 2 * i8 + 8);
+  const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(&a4);
+  const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&b4);
+  uint4 o4;
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&o4);
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    const __nv_bfloat16* src = k < 4 ? a : b;
+    const float gf = __bfloat162float(src[(2 * k) & 7]), uf = __bfloat162float(src[(2 * k + 1) & 7]);
+    o[k] = __float2bfloat16_rn(bfr(gf / (1.0f + __expf(-gf))) * uf);
+  }
+  *reinterpret_cast<uint4*>(out + t * I + i8) = o4;
+}
+
 // out[t] = table[ids[t] - vocab_start] if in [vocab_start, vocab_end) else 0  (vocab-parallel shard)
 __global__ void k_embedding(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                             __nv_bfloat16* __restrict__ out, int hidden, long long vocab_start, long long vocab_end) {
@@ -219,6 +241,15 @@ int tbv_op_silu_mul(const void* x, void* out, int tokens, int inter, void* strea
   if (inter % 8) return -2;
   dim3 grid((inter / 8 + 255) / 256, tokens);
   cudaError_t e = pdl::launch(k_silu_mul, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), 1,
+                              static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), inter);
+  return e == cudaSuccess ? 0 : -1;
+}
+
+int tbv_op_silu_mul_interleaved(const void* x, void* out, int tokens, int inter, void* stream) {
+  if (tokens <= 0) return 0;
+  if (inter % 8) return -2;
+  dim3 grid((inter / 8 + 255) / 256, tokens);
+  cudaError_t e = pdl::launch(k_silu_mul_interleaved, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), 1,
                               static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), inter);
   return e == cudaSuccess ? 0 : -1;
 }

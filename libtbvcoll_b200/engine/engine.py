@@ -18,6 +18,7 @@ Two decode loops over the same captured step:
 from __future__ import annotations
 
 import math
+import os
 import time
 from typing import Dict, List, Optional, Sequence
 
@@ -60,6 +61,10 @@ class Engine:
         pin = lambda n, dt: torch.zeros(n, dtype=dt).pin_memory()
         self.ids_h, self.pos_h = pin(B, torch.int64), pin(B, torch.int32)
         self.slots_h, self.ctx_h, self.out_h = pin(B, torch.int64), pin(B, torch.int32), pin(B, torch.int64)
+        # sequence-parallel prefill (GEMM->reduce-scatter, all-gather->GEMM) for chunks whose row count
+        # divides evenly; TBV_SP_PREFILL=0 keeps the all-reduce path
+        self.sp_prefill = os.environ.get("TBV_SP_PREFILL", "1") != "0"
+        self.sp_chunks = 0
         self.graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
         self.launches_per_step = 0
         self.last_stats: Dict[str, float] = {}
@@ -91,8 +96,13 @@ class Engine:
             n_log = len(last_rows)
             out = torch.zeros(max(n_log, 1), dtype=torch.int64, device=dev)
             logit_rows = torch.tensor([r for r, _ in last_rows] or [0], dtype=torch.int64).to(dev)
-            self.model.forward(T, ids.to(dev), pos.to(dev), slots.to(dev), self.bm.tables, (pos + 1).to(dev), seqof.to(dev),
-                               logit_rows, max(n_log, 1), out, attn_splits=1)
+            if self.sp_prefill and self.model.sp_ok(T):
+                self.model.forward_sp(T, ids.to(dev), pos.to(dev), slots.to(dev), self.bm.tables, (pos + 1).to(dev), seqof.to(dev),
+                                      logit_rows, max(n_log, 1), out)
+                self.sp_chunks += 1
+            else:
+                self.model.forward(T, ids.to(dev), pos.to(dev), slots.to(dev), self.bm.tables, (pos + 1).to(dev), seqof.to(dev),
+                                   logit_rows, max(n_log, 1), out, attn_splits=1)
             if n_log:
                 toks = out[:n_log].tolist()
                 for (r, b), t in zip(last_rows, toks):

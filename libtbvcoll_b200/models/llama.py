@@ -48,6 +48,7 @@ class LlamaTP:
         self.qkv = torch.zeros(max_tokens, qkv_dim, dtype=bf, device=dev)
         self.attn = torch.zeros(max_tokens, self.nq * self.D, dtype=bf, device=dev)
         self.act = torch.zeros(max_tokens, self.ipr, dtype=bf, device=dev)
+        self.gu = None   # [max_tokens, 2 * ipr], allocated on first sequence-parallel prefill
         self.xl = torch.zeros(max_batch, H, dtype=bf, device=dev)        # rows that get logits
         self.logits = torch.zeros(max_batch, self.vpr, dtype=bf, device=dev)
         self.argmax_ws = ops.argmax_workspace(max_batch, dev)
@@ -91,6 +92,60 @@ class LlamaTP:
         else:
             xl = self.xl[:n_logits]
             torch.index_select(xn, 0, logit_rows, out=xl)
+        logits = self.logits[:n_logits]
+        ops.gemm(xl, w["lm_head"], out=logits)
+        return self.sample_greedy(logits, n_logits, out_tokens)
+
+    # -- sequence-parallel prefill --------------------------------------------------------------
+    def sp_ok(self, T: int) -> bool:
+        """Whether a chunk of T token rows can take the sequence-parallel path."""
+        tp, cfg = self.tp, self.cfg
+        if tp.world < 2 or tp.comm is None or cfg.qkv_bias or T % (tp.world * 16):
+            return False
+        rpr, H = T // tp.world, cfg.hidden_size
+        bn = next((b for b in (256, 128, 64, 32, 16) if rpr % b == 0), 0)
+        return bool(bn) and T * H * 2 <= tp.comm.cap and (rpr // bn) * (H // 128) <= 128
+
+    def forward_sp(self, T: int, ids, positions, slot_mapping, block_tables, ctx_lens, seq_of_query, logit_rows, n_logits, out_tokens):
+        """Prefill with the token dimension sharded between the collectives (Megatron-style
+        sequence parallelism): residual stream and norms live on T/tp rows; each column-parallel GEMM
+        is all-gather -> GEMM, each row-parallel GEMM is GEMM -> reduce-scatter (+ residual + RMSNorm
+        on the local rows), both as fused tcgen05 kernels over peer memory."""
+        cfg, w, tp, comm = self.cfg, self.w, self.tp, self.tp.comm
+        rpr = T // tp.world
+        if self.gu is None:
+            self.gu = torch.zeros(self.max_tokens, 2 * self.ipr, dtype=torch.bfloat16, device=self.device)
+        h, xn, part = self.h[:rpr], self.xn[:rpr], self.part[:rpr]
+        qkv, attn, act, gu = self.qkv[:T], self.attn[:T], self.act[:T], self.gu[:T]
+        q_view = qkv.view(T, self.nq + 2 * self.nkv, self.D)[:, : self.nq]
+        attn_view = attn.view(T, self.nq, self.D)
+
+        def must(ok, what):
+            if not ok:
+                raise RuntimeError(f"sequence-parallel prefill: the library declined {what}")
+            tp.calls += 1
+            tp.launches += 2
+
+        ops.embedding(ids, w["embed"], vocab_start=tp.rank * self.vpr, out=self.part[:T])
+        must(comm.reduce_scatter(self.part[:T], h), "reduce_scatter(embedding)")
+        ops.rmsnorm(h, w["layers.0.input_norm"], cfg.rms_eps, out=xn)
+        for l in range(cfg.num_layers):
+            p = f"layers.{l}."
+            must(comm.allgather_gemm(xn, w[p + "qkv.weight"], qkv), "allgather_gemm(qkv)")
+            ops.rope_kv(qkv, positions, self.cos_sin, slot_mapping, self.k_cache[l], self.v_cache[l], self.nq, self.nkv, self.D)
+            ops.paged_attention(q_view, self.k_cache[l], self.v_cache[l], block_tables, ctx_lens, attn_view, self.scale,
+                                self.block_size, seq_of_query=seq_of_query, splits=1)
+            must(comm.gemm_reduce_scatter(attn, w[p + "o.weight"], residual=h, gamma=w[p + "post_norm"], eps=cfg.rms_eps, y=part),
+                 "gemm_reduce_scatter(o_proj)")
+            must(comm.allgather_gemm(part, w[p + "gate_up.weight"], gu), "allgather_gemm(gate_up)")
+            ops.silu_mul(gu, out=act, interleaved=True)
+            nxt = w[f"layers.{l + 1}.input_norm"] if l + 1 < cfg.num_layers else w["norm"]
+            must(comm.gemm_reduce_scatter(act, w[p + "down.weight"], residual=h, gamma=nxt, eps=cfg.rms_eps, y=xn),
+                 "gemm_reduce_scatter(down_proj)")
+        # the rows that get logits may live on any rank: gather the final normalised rows
+        must(comm.all_gather(xn, self.part[:T]), "all_gather(final)")
+        xl = self.xl[:n_logits]
+        torch.index_select(self.part[:T], 0, logit_rows if logit_rows is not None else torch.arange(T, device=self.device), out=xl)
         logits = self.logits[:n_logits]
         ops.gemm(xl, w["lm_head"], out=logits)
         return self.sample_greedy(logits, n_logits, out_tokens)

@@ -38,6 +38,8 @@ def lib():
     l.tbv_op_add_rmsnorm.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, I, I, F, c_vp]
     l.tbv_op_rope_kv.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, c_vp]
     l.tbv_op_silu_mul.argtypes = [c_vp, c_vp, I, I, c_vp]
+    l.tbv_op_silu_mul_interleaved.argtypes = [c_vp, c_vp, I, I, c_vp]
+    l.tbv_op_silu_mul_interleaved.restype = I
     l.tbv_op_embedding.argtypes = [c_vp, c_vp, c_vp, I, I, LL, LL, c_vp]
     l.tbv_op_argmax_workspace.argtypes = [I]
     l.tbv_op_argmax_workspace.restype = SZ
@@ -165,11 +167,12 @@ def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, s
     _count()
 
 
-def silu_mul(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x: [T, 2I] = [gate | up] -> silu(gate) * up, [T, I]."""
+def silu_mul(x: torch.Tensor, out: Optional[torch.Tensor] = None, interleaved: bool = False) -> torch.Tensor:
+    """x: [T, 2I] = [gate | up] (or, ``interleaved``, columns g0 u0 g1 u1 ...) -> silu(gate) * up, [T, I]."""
     T, I2 = x.shape
     out = torch.empty((T, I2 // 2), dtype=x.dtype, device=x.device) if out is None else out
-    _chk(lib().tbv_op_silu_mul(_p(x), _p(out), T, I2 // 2, _st()), "tbv_op_silu_mul")
+    fn = lib().tbv_op_silu_mul_interleaved if interleaved else lib().tbv_op_silu_mul
+    _chk(fn(_p(x), _p(out), T, I2 // 2, _st()), "tbv_op_silu_mul")
     _count()
     return out
 

@@ -328,8 +328,19 @@ def gpu_engine_tp(rank, world, port):
     vpr = cfg.vocab_size // world
     err = (got - want[:, rank * vpr:(rank + 1) * vpr]).abs().max().item()
     h = lambda o: hashlib.sha256(repr(o).encode()).hexdigest()
+    # the same prompts with sequence-parallel prefill switched off: identical tokens expected
+    eng2 = Engine(cfg, tp, device=dev, source=src, max_batch=4, max_seq_len=128, prefill_chunk=64)
+    eng2.sp_prefill = False
+    d = eng2.generate(prompts, 10, loop="host")
+    # and with the single-kernel GEMM + all-reduce + norm in the decode step
+    tp.fuse_gemm = True
+    eng3 = Engine(cfg, tp, device=dev, source=src, max_batch=4, max_seq_len=128, prefill_chunk=64)
+    e = eng3.generate(prompts, 10, loop="host")
+    tp.fuse_gemm = False
+    agree = sum(int(x == y) for xs_, ys_ in zip(a, e) for x, y in zip(xs_, ys_)) / sum(len(x) for x in a)
     out = {"hash": h(a), "loops_equal": h(a) == h(b) == h(cc), "logit_err": err, "logit_scale": want.abs().max().item(),
-           "fallbacks": tp.fallbacks, "launches_per_step": eng.launches_per_step}
+           "fallbacks": tp.fallbacks, "launches_per_step": eng.launches_per_step, "sp_chunks": eng.sp_chunks,
+           "sp_equals_allreduce_path": h(a) == h(d), "fused_gemm_token_agreement": agree}
     c.destroy()
     return out
 
@@ -409,3 +420,46 @@ def gpu_fused_gemm_ar(rank, world, port):
     out["err"] = c.err()
     c.destroy()
     return out
+
+
+def gpu_sp_kernels(rank, world, port):
+    """GEMM->reduce-scatter and all-gather->GEMM on real ranks, bit-exact against compositions of the
+    plain GEMM kernel and the fixed-order oracle."""
+    import torch
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from libtbvcoll_b200 import ops
+    from libtbvcoll_b200.tbvcoll import Comm
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    ok = True
+    c = Comm(rank, world, rank, "127.0.0.1", port, cap_bytes=1024 * 4096 * 2)
+    for T, H, K in ((world * 64, 512, 256), (2048, 4096, 1024 // 1)):
+        g = torch.Generator().manual_seed(T + H)
+        xs = [torch.randn(T, K, generator=g).to(torch.bfloat16).to(dev) for _ in range(world)]
+        ws = [(torch.randn(H, K, generator=g) * 0.05).to(torch.bfloat16).to(dev) for _ in range(world)]
+        gamma = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).to(dev)
+        rpr = T // world
+        res0 = torch.randn(rpr, H, generator=g).to(torch.bfloat16).to(dev)
+        total = oracle_sum([ops.gemm(x, w, splits=1) for x, w in zip(xs, ws)])
+        for rep in range(3):
+            out = torch.zeros(rpr, H, dtype=torch.bfloat16, device=dev)
+            assert c.gemm_reduce_scatter(xs[rank], ws[rank], out=out)
+            res, y = res0.clone(), torch.zeros(rpr, H, dtype=torch.bfloat16, device=dev)
+            assert c.gemm_reduce_scatter(xs[rank], ws[rank], residual=res, gamma=gamma, eps=1e-5, y=y)
+            torch.cuda.synchronize()
+            y2, h2 = ops.add_rmsnorm(total[rank * rpr:(rank + 1) * rpr].clone(), res0.clone(), gamma, 1e-5)
+            torch.cuda.synchronize()
+            ok &= bool(torch.equal(out, total[rank * rpr:(rank + 1) * rpr]) and torch.equal(res, h2) and torch.equal(y, y2))
+        # all-gather -> GEMM: rank r contributes rows [r*rows, (r+1)*rows) of X
+        rows, M = rpr, 384
+        xr = [torch.randn(rows, K, generator=g).to(torch.bfloat16).to(dev) for _ in range(world)]
+        wm = [(torch.randn(M, K, generator=g) * 0.05).to(torch.bfloat16).to(dev) for _ in range(world)]
+        want = ops.gemm(torch.cat(xr, 0), wm[rank], splits=1)
+        for rep in range(3):
+            yy = torch.zeros(world * rows, M, dtype=torch.bfloat16, device=dev)
+            assert c.allgather_gemm(xr[rank], wm[rank], yy)
+            torch.cuda.synchronize()
+            ok &= bool(torch.equal(yy, want))
+    err = c.err()
+    c.destroy()
+    return {"ok": ok, "err": err}

@@ -3,7 +3,7 @@ Run with 2 or more GPUs visible, e.g. ``pytest tests/test_multigpu.py -m gpu``."
 import pytest
 import torch
 
-from _workers import run_ranks, gpu_collectives, gpu_engine_tp, gpu_peer_skips, gpu_fused_gemm_ar
+from _workers import run_ranks, gpu_collectives, gpu_engine_tp, gpu_peer_skips, gpu_fused_gemm_ar, gpu_sp_kernels
 from conftest import free_port
 
 pytestmark = pytest.mark.gpu
@@ -33,6 +33,8 @@ def test_engine_tensor_parallel():
         assert len({r["hash"] for r in res}) == 1
         for r in res:
             assert r["loops_equal"] and r["fallbacks"] == 0
+            assert r["sp_chunks"] > 0 and r["sp_equals_allreduce_path"]
+            assert r["fused_gemm_token_agreement"] > 0.7
             assert r["logit_err"] < 0.05 * r["logit_scale"] + 0.02
 
 
@@ -51,3 +53,10 @@ def test_fused_gemm_allreduce_rmsnorm_real_ranks():
         res = run_ranks(gpu_fused_gemm_ar, world, free_port(), timeout=300)
         assert all(r["ok"] and not r["err"] for r in res)
         assert all(r["hashes"] == res[0]["hashes"] for r in res)      # identical bits on every rank
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs >= 2 GPUs")
+def test_sequence_parallel_kernel_pairs_real_ranks():
+    for world in _worlds():
+        res = run_ranks(gpu_sp_kernels, world, free_port(), timeout=300)
+        assert all(r["ok"] and not r["err"] for r in res)
