@@ -227,7 +227,8 @@ static int pick_algo(const tbv_comm* c, size_t nbytes, bool vec) {
   if (a != TBV_ALGO_AUTO) return a;
   if (c->nvls && vec && long(nbytes) >= c->knobs.nvls_min) return TBV_ALGO_NVLS;
   long lim = c->knobs.oneshot_max;
-  if (lim < 0) lim = c->world <= 2 ? LONG_MAX : (c->world <= 4 ? (512l << 10) : (256l << 10));
+  // measured crossovers (graph-timed, B200 NVSwitch): N=2 one-shot wins up to ~2-4 MiB, N=4 up to ~2 MiB
+  if (lim < 0) lim = c->world <= 2 ? (2l << 20) : (c->world <= 4 ? (2l << 20) : (512l << 10));
   return long(nbytes) <= lim ? TBV_ALGO_ONESHOT : TBV_ALGO_TWOSHOT;
 }
 // Channels (CTAs).  The rule must be a pure function of (bytes, world, knobs): every
