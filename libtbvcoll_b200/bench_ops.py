@@ -65,6 +65,8 @@ def main():
     ap.add_argument("--ctx", type=int, default=640)
     ap.add_argument("--json", default="")
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--only", default="", help="comma list of op names to run (default: all)")
+    ap.add_argument("--nbuf", type=int, default=0, help="weight buffers to cycle (default: enough to exceed 512 MB)")
     args = ap.parse_args()
     from libtbvcoll_b200 import ops
     from libtbvcoll_b200.models.config import get_config
@@ -77,9 +79,12 @@ def main():
               ("gate_up+silu", 2 * cfg.intermediate_size // tp, cfg.hidden_size, 1), ("down_proj", cfg.hidden_size, cfg.intermediate_size // tp, 0),
               ("lm_head", cfg.vocab_size // tp, cfg.hidden_size, 0)]
     rows = []
+    only = set(filter(None, args.only.split(",")))
     for name, M, K, epi in shapes:
+        if only and name not in only:
+            continue
         wbytes = M * K * 2
-        nbuf = max(2, min(64, math.ceil((512 << 20) / wbytes)))
+        nbuf = args.nbuf or max(2, min(64, math.ceil((512 << 20) / wbytes)))
         ws = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(nbuf)]
         x = torch.randn(B, K, device=dev, dtype=torch.bfloat16)
         out = torch.empty(B, M // 2 if epi else M, device=dev, dtype=torch.bfloat16)
@@ -93,6 +98,8 @@ def main():
         rows.append(row)
         print(json.dumps(row), flush=True)
         del ws
+    if only and "paged_attention" not in only:
+        return
     # attention at decode shape
     bs = 16
     nblk = B * math.ceil(args.ctx / bs) + 1

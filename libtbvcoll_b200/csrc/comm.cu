@@ -237,7 +237,7 @@ static int pick_nchan(const tbv_comm* c, int algo, size_t units_per_rankchunk, i
   int maxchan = c->local ? std::max(1, std::min(TBV_MAXCHAN, c->sm_count / c->world)) : TBV_MAXCHAN;
   if (c->knobs.nchan > 0) return std::min(c->knobs.nchan, maxchan);
   size_t per_chan_units = c->knobs.chunk > 0 ? std::max<size_t>(1, size_t(c->knobs.chunk) / 16)
-                                             : size_t(threads) * (algo == TBV_ALGO_ONESHOT ? 1 : 4);
+                                             : size_t(threads);  // one 16-byte unit per thread and pass (measured: fatter channels leave two-shot latency-bound at 8 ranks)
   size_t n = (units_per_rankchunk + per_chan_units - 1) / per_chan_units;
   int cap = algo == TBV_ALGO_ONESHOT ? 32 : 64;
   return int(std::max<size_t>(1, std::min<size_t>(n, size_t(std::min(cap, maxchan)))));
