@@ -74,7 +74,7 @@ def main():
     ap.add_argument("--max-tokens", type=int, default=8192)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--json", default="")
-    ap.add_argument("--algos", default="auto,oneshot,twoshot,nvls")
+    ap.add_argument("--algos", default="auto,ll,oneshot,twoshot,nvls")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", os.environ["RANK"]))
     torch.cuda.set_device(local)

@@ -71,6 +71,8 @@ struct RankCtx {
   unsigned long long wdog_ns;      // bound on every device-side wait
   char* data[TBV_MAXRANK];         // data[p]: rank p's slot memory as mapped here
   unsigned int* flags[TBV_MAXRANK];
+  char* ll[TBV_MAXRANK];           // ll[p]: rank p's LL packet area (only ever holds LL packets)
+  unsigned long long ll_cap;       // bytes per (slot, source-rank) LL region
   char* mc_data;                   // multicast (NVLS) mapping of the slot memory, or null
   DevState* st;
   DevMirror* dm;
@@ -83,6 +85,12 @@ __device__ __forceinline__ size_t flag_index(const RankCtx& c, int slot, int pha
 }
 __device__ __forceinline__ char* slot_region(const RankCtx& c, int peer, int slot, int region) {
   return c.data[peer] + size_t(slot) * c.slot_stride + size_t(region) * c.cap;
+}
+
+// LL packets live in an area of their own: a region that only ever holds (payload, sequence)
+// packets can never show a stale word that equals a future sequence number.
+__device__ __forceinline__ char* ll_region(const RankCtx& c, int peer, int slot, int src) {
+  return c.ll[peer] + (size_t(slot) * c.world + src) * c.ll_cap;
 }
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
@@ -342,6 +350,90 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
     }
   }
   call_end(c, ci, nchan, t_enter, t_ready, nbytes, TBV_ALGO_ONESHOT);
+}
+
+// ---- LL ("low latency") one-shot all-reduce ---------------------------------------------
+// Every 8-byte store carries 4 bytes of payload and the 4-byte sequence number of the call, so
+// the data announces itself: no fence, no separate flag, no second round trip.  The receiver
+// polls the packet until both of its flags show this call's sequence number.  Costs twice the
+// bytes, so it is used for small messages only (nbytes * 2 <= slot capacity and <= TBV_LL_MAX).
+// 8-byte stores are single transactions on NVLink; a 16-byte store is two self-describing halves.
+__device__ __forceinline__ void st_v4(void* p, unsigned a, unsigned b, unsigned c2, unsigned d) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c2), "r"(d) : "memory");
+}
+// Poll one 16-byte LL line (two packets) until both flags equal `want`; bounded like wait_flag.
+__device__ __forceinline__ uint2 ll_wait_load(const RankCtx& c, const void* p, unsigned want, int peer, int chan,
+                                              unsigned long long seq) {
+  uint4 v = ld_volatile_v4(p);
+  unsigned spins = 0;
+  unsigned long long t0 = 0;
+  while (v.y != want || v.w != want) {
+    if (++spins > 4096u) {
+      unsigned long long now = globaltimer();
+      if (t0 == 0) {
+        t0 = now;
+        if (*(volatile unsigned*)&c.st->err != 0u) break;
+      } else if (now - t0 > c.wdog_ns) {
+        report_error(c, kErrTimeout, kWherePhase0, peer, chan, seq);
+        break;
+      }
+      __nanosleep(64);
+    }
+    v = ld_volatile_v4(p);
+  }
+  return make_uint2(v.x, v.z);
+}
+// push one 16-byte input unit `v` as two LL lines (32 bytes) at line index u of every peer's region
+__device__ __forceinline__ void ll_push_unit(const RankCtx& c, int slot, size_t u, const uint4& v, unsigned want) {
+  for (int d = 1; d < c.world; d++) {
+    const int p = (c.rank + d) % c.world;
+    char* dst = ll_region(c, p, slot, c.rank) + u * 32;
+    st_v4(dst, v.x, want, v.y, want);
+    st_v4(dst + 16, v.z, want, v.w, want);
+  }
+}
+__device__ __forceinline__ uint4 ll_pull_unit(const RankCtx& c, int slot, int src, size_t u, unsigned want, int chan,
+                                              unsigned long long seq) {
+  const char* p = ll_region(c, c.rank, slot, src) + u * 32;
+  const uint2 a = ll_wait_load(c, p, want, src, chan, seq), b = ll_wait_load(c, p + 16, want, src, chan, seq);
+  return make_uint4(a.x, a.y, b.x, b.y);
+}
+
+template <typename T>
+__device__ void ar_oneshot_ll_body(const RankCtx& c, const T* __restrict__ in, T* out, size_t nbytes, int nchan, int chan,
+                                   unsigned long long* sh_seq) {
+  unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
+  const size_t units = nbytes / 16;
+  const size_t per = (units + nchan - 1) / nchan;
+  const size_t u0 = per * chan;
+  const size_t u1 = (u0 + per < units) ? (u0 + per) : units;
+  // the first unit's load is issued before the sequence number is known (they do not depend on each other)
+  const size_t uf = u0 + threadIdx.x;
+  uint4 first = make_uint4(0, 0, 0, 0);
+  if (uf < u1) first = reinterpret_cast<const uint4*>(in)[uf];
+  CallInfo ci = call_begin(c, sh_seq);
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
+  for (size_t u = uf; u < u1; u += blockDim.x) {
+    const uint4 v = (u == uf) ? first : reinterpret_cast<const uint4*>(in)[u];
+    ll_push_unit(c, ci.slot, u, v, ci.want);
+  }
+  unsigned long long t_ready = 0;
+  for (size_t u = uf; u < u1; u += blockDim.x) {
+    const uint4 mine = (u == uf) ? first : reinterpret_cast<const uint4*>(in)[u];
+    float acc[Pack<T>::N];
+#pragma unroll
+    for (int i = 0; i < Pack<T>::N; i++) acc[i] = 0.f;
+    for (int r = 0; r < c.world; r++) {
+      const uint4 v = (r == c.rank) ? mine : ll_pull_unit(c, ci.slot, r, u, ci.want, chan, ci.seq);
+      float f[Pack<T>::N];
+      Pack<T>::unpack(v, f);
+#pragma unroll
+      for (int i = 0; i < Pack<T>::N; i++) acc[i] = (r == 0) ? f[i] : acc[i] + f[i];
+    }
+    reinterpret_cast<uint4*>(out)[u] = Pack<T>::pack(acc);
+  }
+  if (threadIdx.x == 0 && chan == 0) { t_ready = globaltimer(); c.dm->bc[2] = ci.seq; }
+  call_end(c, ci, nchan, t_enter, t_ready, nbytes, TBV_ALGO_LL);
 }
 
 __device__ __forceinline__ void multimem_st_v4(void* p, const uint4& v) {
@@ -627,24 +719,33 @@ __device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __
                                        const __nv_bfloat16* __restrict__ gamma,
                                        __nv_bfloat16* residual_out, __nv_bfloat16* y, int tokens,
                                        int hidden, float eps, int nchan, int chan,
-                                       unsigned long long* sh_seq, float* sh_red) {
+                                       unsigned long long* sh_seq, float* sh_red, bool ll) {
   unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
-  CallInfo ci = call_begin(c, sh_seq);
   const int upr = hidden / 8;  // 16-byte units per row
+  // first row's first unit: loaded before the sequence number is known
+  uint4 first = make_uint4(0, 0, 0, 0);
+  if (chan < tokens && int(threadIdx.x) < upr) first = reinterpret_cast<const uint4*>(x)[size_t(chan) * upr + threadIdx.x];
+  CallInfo ci = call_begin(c, sh_seq);
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
   for (int row = chan; row < tokens; row += nchan) {
     const uint4* src = reinterpret_cast<const uint4*>(x) + size_t(row) * upr;
     for (int u = threadIdx.x; u < upr; u += blockDim.x) {
-      uint4 v = src[u];
-      for (int p = 0; p < c.world; p++)
-        if (p != c.rank)
-          reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, c.rank))[size_t(row) * upr + u] = v;
+      uint4 v = (row == chan && u == int(threadIdx.x)) ? first : src[u];
+      if (ll) {
+        ll_push_unit(c, ci.slot, size_t(row) * upr + u, v, ci.want);
+      } else {
+        for (int p = 0; p < c.world; p++)
+          if (p != c.rank)
+            reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, c.rank))[size_t(row) * upr + u] = v;
+      }
     }
   }
-  __syncthreads();
-  publish(c, ci, 0, chan);
-  if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
-  wait_all(c, ci, 0, chan, kWhereFused);
+  if (!ll) {
+    __syncthreads();
+    publish(c, ci, 0, chan);
+    if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
+    wait_all(c, ci, 0, chan, kWhereFused);
+  }
   unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   for (int row = chan; row < tokens; row += nchan) {
     float h[kNormMaxUnits][8];
@@ -657,7 +758,8 @@ __device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __
         uint4 mine = reinterpret_cast<const uint4*>(x)[off];
         for (int r = 0; r < c.world; r++) {
           uint4 v = (r == c.rank) ? mine
-                                  : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, ci.slot, r)) + off);
+                    : (ll ? ll_pull_unit(c, ci.slot, r, off, ci.want, chan, ci.seq)
+                          : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, ci.slot, r)) + off));
           float f[8];
           Pack<__nv_bfloat16>::unpack(v, f);
 #pragma unroll

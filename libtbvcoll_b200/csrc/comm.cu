@@ -64,12 +64,14 @@ Knobs Knobs::from_env() {
   k.nchan = int(env_long("TBV_NCHAN", 0));
   k.nvls = int(env_long("TBV_NVLS", 0));
   k.init_timeout_s = env_double("TBV_INIT_TIMEOUT", 60.0);
+  k.ll_max = env_long("TBV_LL_MAX", 256 << 10);
   k.nvls_min = env_long("TBV_NVLS_MIN", LONG_MAX);  // auto never picks the switch-reduced kernel unless asked
   const char* a = getenv("TBV_ALGO");
   if (a) {
     if (!strcmp(a, "oneshot")) k.algo = TBV_ALGO_ONESHOT;
     else if (!strcmp(a, "twoshot")) k.algo = TBV_ALGO_TWOSHOT;
     else if (!strcmp(a, "nvls")) k.algo = TBV_ALGO_NVLS;
+    else if (!strcmp(a, "ll")) k.algo = TBV_ALGO_LL;
   }
   const char* m = getenv("TBV_MEM");
   if (m) k.mem = !strcmp(m, "vmm") ? 1 : (!strcmp(m, "ipc") ? 2 : 0);
@@ -190,6 +192,19 @@ __global__ void __launch_bounds__(512) k_ar_twoshot_local(const RankCtx* ctxs, c
                           nbytes, gridDim.x, blockIdx.x, mode, &sh_seq);
 }
 template <typename T>
+__global__ void __launch_bounds__(512) k_ar_ll(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
+  __shared__ unsigned long long sh_seq;
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
+  ar_oneshot_ll_body<T>(c, in, out, nbytes, gridDim.x, blockIdx.x, &sh_seq);
+}
+template <typename T>
+__global__ void __launch_bounds__(512) k_ar_ll_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p, size_t nbytes) {
+  __shared__ unsigned long long sh_seq;
+  ar_oneshot_ll_body<T>(ctxs[blockIdx.y], static_cast<const T*>(p.in[blockIdx.y]), static_cast<T*>(p.out[blockIdx.y]), nbytes,
+                        gridDim.x, blockIdx.x, &sh_seq);
+}
+template <typename T>
 __global__ void __launch_bounds__(512) k_ar_nvls(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
@@ -199,15 +214,15 @@ __global__ void __launch_bounds__(512) k_ar_nvls(const __grid_constant__ RankCtx
 __global__ void __launch_bounds__(1024) k_ar_rmsnorm(const __grid_constant__ RankCtx c, const __nv_bfloat16* x,
                                                      const __nv_bfloat16* residual, const __nv_bfloat16* gamma,
                                                      __nv_bfloat16* residual_out, __nv_bfloat16* y, int tokens, int hidden,
-                                                     float eps) {
+                                                     float eps, bool ll) {
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
   __shared__ float sh_red[32];
-  ar_rmsnorm_body(c, x, residual, gamma, residual_out, y, tokens, hidden, eps, gridDim.x, blockIdx.x, &sh_seq, sh_red);
+  ar_rmsnorm_body(c, x, residual, gamma, residual_out, y, tokens, hidden, eps, gridDim.x, blockIdx.x, &sh_seq, sh_red, ll);
 }
 __global__ void __launch_bounds__(1024) k_ar_rmsnorm_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p,
-                                                           const __nv_bfloat16* gamma, int tokens, int hidden, float eps) {
+                                                           const __nv_bfloat16* gamma, int tokens, int hidden, float eps, bool ll) {
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
@@ -215,7 +230,7 @@ __global__ void __launch_bounds__(1024) k_ar_rmsnorm_local(const RankCtx* ctxs, 
   const int r = blockIdx.y;
   ar_rmsnorm_body(ctxs[r], static_cast<const __nv_bfloat16*>(p.in[r]), static_cast<const __nv_bfloat16*>(p.aux[r]), gamma,
                   static_cast<__nv_bfloat16*>(p.aux_out[r]), static_cast<__nv_bfloat16*>(p.out[r]), tokens, hidden, eps,
-                  gridDim.x, blockIdx.x, &sh_seq, sh_red);
+                  gridDim.x, blockIdx.x, &sh_seq, sh_red, ll);
 }
 
 // ---- sizing tables --------------------------------------------------------------------------
@@ -224,7 +239,10 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 static int pick_algo(const tbv_comm* c, size_t nbytes, bool vec) {
   int a = c->knobs.algo;
   if (a == TBV_ALGO_NVLS && !(c->nvls && vec)) a = TBV_ALGO_AUTO;
+  const bool ll_ok = vec && nbytes * 2 <= c->ll_cap;
+  if (a == TBV_ALGO_LL && !ll_ok) a = TBV_ALGO_AUTO;
   if (a != TBV_ALGO_AUTO) return a;
+  if (ll_ok && long(nbytes) <= c->knobs.ll_max) return TBV_ALGO_LL;
   if (c->nvls && vec && long(nbytes) >= c->knobs.nvls_min) return TBV_ALGO_NVLS;
   long lim = c->knobs.oneshot_max;
   // measured crossovers (graph-timed, B200 NVSwitch): N=2 one-shot wins up to ~2-4 MiB, N=4 up to ~2 MiB
@@ -239,7 +257,7 @@ static int pick_nchan(const tbv_comm* c, int algo, size_t units_per_rankchunk, i
   size_t per_chan_units = c->knobs.chunk > 0 ? std::max<size_t>(1, size_t(c->knobs.chunk) / 16)
                                              : size_t(threads);  // one 16-byte unit per thread and pass (measured: fatter channels leave two-shot latency-bound at 8 ranks)
   size_t n = (units_per_rankchunk + per_chan_units - 1) / per_chan_units;
-  int cap = algo == TBV_ALGO_ONESHOT ? 32 : 64;
+  int cap = (algo == TBV_ALGO_ONESHOT || algo == TBV_ALGO_LL) ? 32 : 64;
   return int(std::max<size_t>(1, std::min<size_t>(n, size_t(std::min(cap, maxchan)))));
 }
 
@@ -252,6 +270,7 @@ static void fill_ctx(tbv_comm* c, GpuRank& g, int rank) {
   x.debug_tag = c->knobs.tag;
   x.cap = c->cap;
   x.slot_stride = size_t(c->world + 1) * c->cap;
+  x.ll_cap = c->ll_cap;
   x.wdog_ns = (unsigned long long)(c->knobs.wdog_s * 1e9);
   x.st = g.st;
   x.dm = g.dm;
@@ -273,6 +292,9 @@ static int alloc_rank_state(tbv_comm* c, GpuRank& g) {
 static void compute_sizes(tbv_comm* c) {
   c->flag_bytes = (size_t(c->knobs.nslot) * 2 * c->world * TBV_MAXCHAN * sizeof(unsigned) + 4095) & ~size_t(4095);
   c->data_bytes = size_t(c->knobs.nslot) * size_t(c->world + 1) * c->cap;
+  // LL area: two bytes on the wire per payload byte, one region per (slot, source)
+  c->ll_cap = (size_t(std::max(0l, c->knobs.ll_max)) * 2 + 4095) & ~size_t(4095);
+  c->ll_bytes = size_t(c->knobs.nslot) * c->world * c->ll_cap;
 }
 
 // VMM path: returns TBV_OK, or TBV_FALLBACK if VMM cannot be used here (caller tries IPC).
@@ -295,7 +317,7 @@ static int setup_vmm(tbv_comm* c) {
     d.DeviceGetAttribute(&sup, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, c->device);
     if (!sup) want_mc = false;
   }
-  size_t total = c->flag_bytes + c->data_bytes;
+  size_t total = c->flag_bytes + c->data_bytes + c->ll_bytes;
   if (want_mc) {
     mprop.numDevices = unsigned(c->world);
     mprop.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
@@ -414,7 +436,7 @@ static int setup_vmm(tbv_comm* c) {
 
 static int setup_ipc(tbv_comm* c) {
   GpuRank& g = c->ranks[0];
-  size_t total = c->flag_bytes + c->data_bytes;
+  size_t total = c->flag_bytes + c->data_bytes + c->ll_bytes;
   g.alloc_bytes = total;
   CUDA_TRY(c, cudaMalloc(&g.base, total));
   cudaIpcMemHandle_t mine;
@@ -461,7 +483,7 @@ static int gpu_init(tbv_comm* c) {
 
   int rc = TBV_FALLBACK;
   if (c->world == 1) {
-    CUDA_TRY(c, cudaMalloc(&g.base, c->flag_bytes + c->data_bytes));
+    CUDA_TRY(c, cudaMalloc(&g.base, c->flag_bytes + c->data_bytes + c->ll_bytes));
     c->peer_maps.assign(1, g.base);
     rc = TBV_OK;
   } else {
@@ -473,11 +495,13 @@ static int gpu_init(tbv_comm* c) {
   }
   if (rc != TBV_OK) return TBV_FAIL;
   CUDA_TRY(c, cudaMemset(g.base, 0, c->flag_bytes));
+  CUDA_TRY(c, cudaMemset(g.base + c->flag_bytes + c->data_bytes, 0, c->ll_bytes));  // no stale word may look like a packet
   CUDA_TRY(c, cudaDeviceSynchronize());
   fill_ctx(c, g, c->rank);
   for (int p = 0; p < c->world; p++) {
     g.ctx.flags[p] = reinterpret_cast<unsigned*>(c->peer_maps[p]);
     g.ctx.data[p] = static_cast<char*>(c->peer_maps[p]) + c->flag_bytes;
+    g.ctx.ll[p] = static_cast<char*>(c->peer_maps[p]) + c->flag_bytes + c->data_bytes;
   }
   CUDA_TRY(c, cudaMalloc(&c->ctxs_dev, sizeof(RankCtx)));
   CUDA_TRY(c, cudaMemcpy(c->ctxs_dev, &g.ctx, sizeof(RankCtx), cudaMemcpyHostToDevice));
@@ -497,9 +521,10 @@ static int gpu_init_local(tbv_comm* c) {
     GpuRank& g = c->ranks[r];
     g.device = c->device;
     if (alloc_rank_state(c, g) != TBV_OK) return TBV_FAIL;
-    g.alloc_bytes = c->flag_bytes + c->data_bytes;
+    g.alloc_bytes = c->flag_bytes + c->data_bytes + c->ll_bytes;
     CUDA_TRY(c, cudaMalloc(&g.base, g.alloc_bytes));
     CUDA_TRY(c, cudaMemset(g.base, 0, c->flag_bytes));
+    CUDA_TRY(c, cudaMemset(g.base + c->flag_bytes + c->data_bytes, 0, c->ll_bytes));
   }
   std::vector<RankCtx> host(c->world);
   for (int r = 0; r < c->world; r++) {
@@ -508,6 +533,7 @@ static int gpu_init_local(tbv_comm* c) {
     for (int p = 0; p < c->world; p++) {
       g.ctx.flags[p] = reinterpret_cast<unsigned*>(c->ranks[p].base);
       g.ctx.data[p] = c->ranks[p].base + c->flag_bytes;
+      g.ctx.ll[p] = c->ranks[p].base + c->flag_bytes + c->data_bytes;
     }
     host[r] = g.ctx;
   }
@@ -585,6 +611,7 @@ static cudaError_t launch_ar_t(tbv_comm* c, int algo, bool vec, int nchan, int t
   T* o = static_cast<T*>(out);
   const dim3 g(nchan), b(threads);
   if (algo == TBV_ALGO_NVLS) return pdl::launch(k_ar_nvls<T>, g, b, 0, st, 1, x, i, o, nbytes);
+  if (algo == TBV_ALGO_LL) return pdl::launch(k_ar_ll<T>, g, b, 0, st, 1, x, i, o, nbytes);
   if (algo == TBV_ALGO_ONESHOT)
     return vec ? pdl::launch(k_ar_oneshot<T, true>, g, b, 0, st, 1, x, i, o, nbytes)
                : pdl::launch(k_ar_oneshot<T, false>, g, b, 0, st, 1, x, i, o, nbytes);
@@ -598,6 +625,11 @@ static cudaError_t launch_ar_local_t(tbv_comm* c, int algo, bool vec, int nchan,
   dim3 grid(nchan, c->world);
   const RankCtx* ctxs = c->ctxs_dev;
   void* fn;
+  if (algo == TBV_ALGO_LL) {
+    fn = (void*)k_ar_ll_local<T>;
+    void* args[] = {(void*)&ctxs, (void*)&p, (void*)&nbytes};
+    return cudaLaunchCooperativeKernel(fn, grid, dim3(threads), args, 0, st);
+  }
   if (algo == TBV_ALGO_ONESHOT) {
     fn = vec ? (void*)k_ar_oneshot_local<T, true> : (void*)k_ar_oneshot_local<T, false>;
     void* args[] = {(void*)&ctxs, (void*)&p, (void*)&nbytes};
@@ -635,7 +667,8 @@ static int gpu_collective(tbv_comm* c, const void* const* ins, void* const* outs
   const size_t unit = vec ? 16 : dtype_size(dtype);
   size_t units = full / unit;
   if (mode != 0 && (nbytes % unit)) return TBV_FALLBACK;
-  size_t per_rank_units = algo == TBV_ALGO_ONESHOT ? units : (units + c->world - 1) / c->world;
+  const bool oneshot_like = algo == TBV_ALGO_ONESHOT || algo == TBV_ALGO_LL;
+  size_t per_rank_units = oneshot_like ? units : (units + c->world - 1) / c->world;
   if (mode != 0 && per_rank_units * unit != nbytes) return TBV_FALLBACK;  // chunks must be exactly the blocks
   int threads = 512;
   if (per_rank_units < 512) threads = int(std::max<size_t>(32, (per_rank_units + 31) / 32 * 32));
@@ -695,12 +728,13 @@ static int gpu_ar_rmsnorm(tbv_comm* c, const void* const* xs, const void* const*
   int maxchan = c->local ? std::max(1, std::min(TBV_MAXCHAN, c->sm_count / c->world)) : TBV_MAXCHAN;
   int nchan = std::min(tokens, c->knobs.nchan > 0 ? std::min(c->knobs.nchan, maxchan) : maxchan);
   cudaError_t e;
+  bool ll = (c->knobs.algo == TBV_ALGO_AUTO || c->knobs.algo == TBV_ALGO_LL) && nbytes * 2 <= c->ll_cap && long(nbytes) <= c->knobs.ll_max;
   if (c->local) {
     LocalPtrs p{};
     for (int r = 0; r < nr; r++) { p.in[r] = xs[r]; p.out[r] = ys[r]; p.aux[r] = residuals[r]; p.aux_out[r] = residual_outs[r]; }
     const RankCtx* ctxs = c->ctxs_dev;
     const __nv_bfloat16* g = static_cast<const __nv_bfloat16*>(gamma);
-    void* args[] = {(void*)&ctxs, (void*)&p, (void*)&g, (void*)&tokens, (void*)&hidden, (void*)&eps};
+    void* args[] = {(void*)&ctxs, (void*)&p, (void*)&g, (void*)&tokens, (void*)&hidden, (void*)&eps, (void*)&ll};
     e = cudaLaunchCooperativeKernel((void*)k_ar_rmsnorm_local, dim3(nchan, c->world), dim3(threads), args, 0, st);
   } else if (c->world == 1) {
     return TBV_FALLBACK;  // nothing to reduce: the caller uses the plain fused add+norm op
@@ -708,7 +742,7 @@ static int gpu_ar_rmsnorm(tbv_comm* c, const void* const* xs, const void* const*
     e = pdl::launch(k_ar_rmsnorm, dim3(nchan), dim3(threads), 0, st, 1, c->ranks[0].ctx,
                     static_cast<const __nv_bfloat16*>(xs[0]), static_cast<const __nv_bfloat16*>(residuals[0]),
                     static_cast<const __nv_bfloat16*>(gamma), static_cast<__nv_bfloat16*>(residual_outs[0]),
-                    static_cast<__nv_bfloat16*>(ys[0]), tokens, hidden, eps);
+                    static_cast<__nv_bfloat16*>(ys[0]), tokens, hidden, eps, ll);
   }
   if (e != cudaSuccess) {
     c->errmsg = std::string("kernel launch: ") + cudaGetErrorString(e);
@@ -896,7 +930,7 @@ int tbv_comm_is_async(tbv_comm* c) { return c ? c->knobs.async : 0; }
 int tbv_comm_err(tbv_comm* c) { return c ? int(check_err(c)) : 1; }
 int tbv_comm_has_nvls(tbv_comm* c) { return c ? int(c->nvls) : 0; }
 int tbv_comm_set_algo(tbv_comm* c, int algo) {
-  if (!c || algo < 0 || algo > 3) return TBV_FAIL;
+  if (!c || algo < 0 || algo > 4) return TBV_FAIL;
   c->knobs.algo = algo;
   return TBV_OK;
 }
@@ -923,7 +957,7 @@ int tbv_comm_skip_next(tbv_comm* c, int n) {
   return TBV_OK;
 }
 int tbv_comm_ctx(tbv_comm* c, void* ctx_out, size_t ctx_bytes) {
-  if (!c || c->cpu || c->ranks.empty() || ctx_bytes != sizeof(RankCtx)) return TBV_FAIL;
+  if (!c || c->cpu || c->ranks.empty() || ctx_bytes < sizeof(RankCtx)) return TBV_FAIL;
   memcpy(ctx_out, &c->ranks[0].ctx, sizeof(RankCtx));
   return TBV_OK;
 }

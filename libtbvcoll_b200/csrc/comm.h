@@ -30,6 +30,7 @@ struct Knobs {
   int nvls = 0;           // TBV_NVLS: 1 = set up a multicast object and allow the NVLS kernels
   int mem = 0;            // TBV_MEM: 0 = VMM with IPC fallback, 1 = VMM only, 2 = cudaIpc only
   double init_timeout_s = 60.0;  // TBV_INIT_TIMEOUT
+  long ll_max = 256 << 10;       // TBV_LL_MAX: largest message that uses flag-in-payload (LL) packets
   long nvls_min = 0x7fffffffffffffffl;  // TBV_NVLS_MIN: smallest message for the switch-reduced kernel in auto mode
   static Knobs from_env();
 };
@@ -58,7 +59,7 @@ struct tbv_comm {
   // GPU backend
   std::vector<tbv::GpuRank> ranks;       // size 1 (real) or world (emulated)
   tbv::RankCtx* ctxs_dev = nullptr;      // emulated: device array of contexts
-  size_t flag_bytes = 0, data_bytes = 0;
+  size_t flag_bytes = 0, data_bytes = 0, ll_bytes = 0, ll_cap = 0;
   bool vmm = false, nvls = false;
   std::vector<void*> peer_maps;          // mapped peer bases (to unmap at teardown)
   std::vector<unsigned long long> vmm_handles;  // CUmemGenericAllocationHandle per rank (imported + own)

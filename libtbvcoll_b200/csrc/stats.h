@@ -26,7 +26,7 @@ struct Stats {
   unsigned long long n_acc = 0, n_enq = 0;
   double hb_us[32] = {0}, hb_chan[32] = {0};
   unsigned long long hb_n[32] = {0};
-  unsigned long long hb_algo[32][4] = {{0}};
+  unsigned long long hb_algo[32][8] = {{0}};
   double peer_wait_us[8] = {0};
   unsigned long long peer_n[8] = {0};
   unsigned long long stream_switches = 0, streams_seen = 0, fallbacks = 0;
@@ -42,7 +42,7 @@ struct Stats {
     t_pre += pre; t_acc += xfer; t_post += post; t_drain += drain; n_acc++;
     int b = bucket(nbytes);
     hb_us[b] += xfer; hb_chan[b] += nchan; hb_n[b]++;
-    hb_algo[b][algo & 3]++;
+    hb_algo[b][algo & 7]++;
   }
   // averages, then reset (reference: libtbvcoll.cpp:522-536)
   void read5(double* pre, double* xfer, double* post, double* enq, double* drain, unsigned long long* n) {
@@ -59,13 +59,13 @@ struct Stats {
   }
   void dump_hist(int rank, unsigned long long tag_bad) {
     std::lock_guard<std::mutex> g(mu);
-    static const char* an[4] = {"auto", "oneshot", "twoshot", "nvls"};
+    static const char* an[8] = {"auto", "oneshot", "twoshot", "nvls", "ll", "?", "?", "?"};
     fprintf(stderr, "[tbvcoll] rank %d hist: streams=%llu switches=%llu fallbacks=%llu tag_bad=%llu\n", rank,
             streams_seen, stream_switches, fallbacks, tag_bad);
     for (int b = 0; b < 32; b++) {
       if (!hb_n[b]) continue;
       int best = 1;
-      for (int a = 1; a < 4; a++) if (hb_algo[b][a] > hb_algo[b][best]) best = a;
+      for (int a = 1; a < 8; a++) if (hb_algo[b][a] > hb_algo[b][best]) best = a;
       fprintf(stderr, "[tbvcoll]   2^%-2d B  n=%-8llu xfer=%8.2f us  chan=%5.1f  algo=%s\n", b, hb_n[b],
               hb_us[b] / hb_n[b], hb_chan[b] / hb_n[b], an[best]);
     }

@@ -30,6 +30,7 @@ extern "C" {
 #define TBV_ALGO_ONESHOT 1
 #define TBV_ALGO_TWOSHOT 2
 #define TBV_ALGO_NVLS 3
+#define TBV_ALGO_LL 4   // one-shot with flag-in-payload packets (small messages)
 
 #define TBV_MAXRANK 8
 #define TBV_MAXSLOT 32

@@ -116,7 +116,7 @@ def _stream_of(t: torch.Tensor):
     return c_vp(torch.cuda.current_stream(t.device).cuda_stream) if t.is_cuda else None
 
 
-ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3}
+ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "ll": 4}
 
 
 class Comm:
@@ -397,8 +397,8 @@ class Comm:
 
     def ctx_blob(self) -> bytes:
         """The device-side context (peer pointers etc.) that fused kernels take by value."""
-        buf = ctypes.create_string_buffer(200)
-        if self._l.tbv_comm_ctx(self._h, buf, 200) != 0:
+        buf = ctypes.create_string_buffer(1024)
+        if self._l.tbv_comm_ctx(self._h, buf, 1024) != 0:
             raise RuntimeError("tbv_comm_ctx failed")
         return buf.raw
 

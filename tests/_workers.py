@@ -222,7 +222,7 @@ def gpu_collectives(rank, world, port, mem):
     dev = f"cuda:{rank}"
     c = Comm(rank, world, rank, "127.0.0.1", port, cap_bytes=1 << 20)
     res = {"bad": []}
-    for algo in ("oneshot", "twoshot"):
+    for algo in ("oneshot", "twoshot", "ll"):
         c.set_algo(algo)
         for dtype in (torch.float32, torch.float16, torch.bfloat16):
             es = torch.tensor([], dtype=dtype).element_size()

@@ -23,7 +23,7 @@ def oracle(ts):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("algo", ["oneshot", "twoshot"])
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "ll"])
 def test_exact_all_dtypes_sizes(world, algo):
     from libtbvcoll_b200.tbvcoll import Comm
     c = Comm.local(world, 0, cap_bytes=1 << 20)
@@ -45,7 +45,7 @@ def test_exact_all_dtypes_sizes(world, algo):
         c.destroy()
 
 
-@pytest.mark.parametrize("world,algo", [(2, "oneshot"), (8, "oneshot"), (4, "twoshot")])
+@pytest.mark.parametrize("world,algo", [(2, "oneshot"), (8, "oneshot"), (4, "twoshot"), (2, "ll"), (8, "ll")])
 def test_stress_back_to_back_no_sync_4_slots(world, algo):
     """Counterpart of step4/test_stress.py:23-42: many calls with no synchronisation in
     between (slot reuse), every output checked afterwards."""
