@@ -111,7 +111,9 @@ def main():
     q = torch.randn(B, nq, D, device=dev, dtype=torch.bfloat16)
     o = torch.empty_like(q)
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    splits = max(1, min(math.ceil(2 * sms / (B * nkv)), 8, math.ceil(args.ctx / 64)))
+    splits = 1
+    while splits < 8 and B * nkv * splits * 2 <= 2 * sms and args.ctx // (splits * 2) >= 64:
+        splits *= 2
     ws_a = ops.attn_workspace(B, nq, nkv, splits, dev)
     us = time_graph([(lambda l=l: ops.paged_attention(q, kcs[l], vcs[l], bt, ctx, o, 0.088, bs, splits=splits, workspace=ws_a)) for l in range(L)])
     byts = B * args.ctx * nkv * D * 2 * 2

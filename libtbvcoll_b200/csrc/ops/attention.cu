@@ -12,6 +12,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "../pdl.cuh"
 
@@ -224,6 +226,238 @@ __global__ void __launch_bounds__(kThreads) k_paged_attn(const AttnParams p) {
   cluster_sync();  // keep this CTA's shared memory alive until every peer has read it
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-core form: S = Q K^T and O = P V as m16n8k16 bf16 MMAs (the G query heads of one kv
+// head are the rows of a 16-row tile, zero padded), K/V tiles of 16 cached tokens staged in
+// shared memory by cp.async (3 stages per warp, XOR-swizzled 16-byte chunks) and fed with
+// ldmatrix.  ~7 warp instructions per cached token instead of ~78 in the CUDA-core kernel, which
+// is what makes the kernel memory-bound instead of issue-bound.  Same grid, cluster merge and
+// numerics contract (fp32 softmax, base-2 exponent) as k_paged_attn.
+constexpr int kMW = 4;            // warps per CTA
+constexpr int kTile = 16;         // cached tokens per MMA tile
+constexpr int kStages = 3;
+constexpr int kTileBytes = kTile * kD * 2;            // 4 KB for K, 4 KB for V
+constexpr int kMmaSmem = kMW * kStages * 2 * kTileBytes;  // 96 KB
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int G>
+__global__ void __launch_bounds__(kMW * 32) k_paged_attn_mma(const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t dsm[];
+  __shared__ float sh_o[kMW][G][kD];
+  __shared__ float sh_ml[kMW][G][2];
+  __shared__ int sh_bt[kMaxBlocksPerCta];
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
+  const int qi = blockIdx.x, h = blockIdx.y, sp = blockIdx.z, S = p.splits;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = lane >> 2, quad = lane & 3;       // MMA row (query head) and column pair of this lane
+  const int ctx = p.ctx_lens[qi];
+  const int seq = p.seq_of_query ? p.seq_of_query[qi] : qi;
+  const int* bt = p.block_tables + size_t(seq) * p.max_blocks;
+  int chunk = (ctx + S - 1) / S;
+  chunk = (chunk + p.block_size - 1) / p.block_size * p.block_size;
+  const int t0 = sp * chunk, t1 = min(ctx, t0 + chunk);
+
+  // Q fragments (A operand): rows >= G are zero
+  uint32_t qa0[kD / 16], qa2[kD / 16];
+#pragma unroll
+  for (int ks = 0; ks < kD / 16; ks++) {
+    qa0[ks] = qa2[ks] = 0u;
+    if (row < G) {
+      const __nv_bfloat16* qp = p.q + size_t(qi) * p.ldq + (h * G + row) * kD + ks * 16 + quad * 2;
+      qa0[ks] = *reinterpret_cast<const uint32_t*>(qp);
+      qa2[ks] = *reinterpret_cast<const uint32_t*>(qp + 8);
+    }
+  }
+  float o[kD / 8][4];
+#pragma unroll
+  for (int dn = 0; dn < kD / 8; dn++) o[dn][0] = o[dn][1] = o[dn][2] = o[dn][3] = 0.f;
+  float m_run = kNegBig, l_run = 0.f;   // of row `row` (partial over this lane's columns for l)
+
+  const uint32_t wbase = static_cast<uint32_t>(__cvta_generic_to_shared(dsm)) + warp * (kStages * 2 * kTileBytes);
+  const int span = kMaxBlocksPerCta * p.block_size;
+  for (int pass0 = t0; pass0 < t1; pass0 += span) {
+    const int pass1 = min(t1, pass0 + span);
+    const int b0 = pass0 / p.block_size, nb = (pass1 - pass0 + p.block_size - 1) / p.block_size;
+    __syncthreads();
+    if (threadIdx.x < nb) sh_bt[threadIdx.x] = bt[b0 + threadIdx.x];
+    __syncthreads();
+    const int ntiles = (pass1 - pass0 + kTile - 1) / kTile;
+    const int my_tiles = ntiles > warp ? (ntiles - warp + kMW - 1) / kMW : 0;
+
+    auto issue = [&](int i) {   // stage tile i of this warp (tokens tok0 .. tok0+15)
+      if (i < my_tiles) {
+        const int tok0 = pass0 + (warp + i * kMW) * kTile;
+        const uint32_t sk = wbase + (i % kStages) * 2 * kTileBytes, sv = sk + kTileBytes;
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+          const int id = lane + 32 * c, r = id >> 4, ch = id & 15;
+          const int tok = tok0 + r;
+          const uint32_t off = uint32_t(r * 256 + ((ch ^ (r & 7)) << 4));
+          if (tok < pass1) {
+            const long long slot = (long long)sh_bt[tok / p.block_size - b0] * p.block_size + tok % p.block_size;
+            const size_t g = (size_t(slot) * p.nkv + h) * kD + ch * 8;
+            cp_async16(sk + off, p.k_cache + g);
+            cp_async16(sv + off, p.v_cache + g);
+          } else {  // masked tokens: zero V so that 0 * garbage cannot make a NaN
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(sv + off), "r"(0u) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(sk + off), "r"(0u) : "memory");
+          }
+        }
+      }
+      cp_async_commit();
+    };
+    issue(0);
+    issue(1);
+    for (int i = 0; i < my_tiles; i++) {
+      issue(i + 2);
+      cp_async_wait<2>();
+      __syncwarp();
+      const int tok0 = pass0 + (warp + i * kMW) * kTile;
+      const uint32_t sk = wbase + (i % kStages) * 2 * kTileBytes, sv = sk + kTileBytes;
+      // ---- S = Q K^T for 16 tokens (two n tiles of 8)
+      float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int ks = 0; ks < kD / 16; ks++) {
+        uint32_t b[4];
+        const int mi = lane >> 3, r = ((mi >> 1) << 3) + (lane & 7), ch = ks * 2 + (mi & 1);
+        ldmatrix_x4(sk + uint32_t(r * 256 + ((ch ^ (r & 7)) << 4)), b);
+        mma_bf16(sc[0], qa0[ks], 0u, qa2[ks], 0u, b[0], b[1]);
+        mma_bf16(sc[1], qa0[ks], 0u, qa2[ks], 0u, b[2], b[3]);
+      }
+      // ---- online softmax on this lane's 4 columns of row `row`
+      float mx = m_run;
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          const int tok = tok0 + nt * 8 + quad * 2 + j;
+          sc[nt][j] = tok < pass1 ? sc[nt][j] * p.scale_log2 : kNegBig;
+          mx = fmaxf(mx, sc[nt][j]);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float corr = exp2f(m_run - mx);
+      m_run = mx;
+      float pr[2][2];
+      float ps = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          const int tok = tok0 + nt * 8 + quad * 2 + j;
+          pr[nt][j] = tok < pass1 ? exp2f(sc[nt][j] - mx) : 0.f;
+          ps += pr[nt][j];
+        }
+      l_run = l_run * corr + ps;
+#pragma unroll
+      for (int dn = 0; dn < kD / 8; dn++) { o[dn][0] *= corr; o[dn][1] *= corr; }
+      // ---- O += P V  (P: 16 heads x 16 tokens from the score registers; rows >= 8 are zero)
+      const uint32_t pa0 = pack_bf16(pr[0][0], pr[0][1]), pa2 = pack_bf16(pr[1][0], pr[1][1]);
+#pragma unroll
+      for (int dp = 0; dp < kD / 16; dp++) {   // two 8-dim n tiles per ldmatrix
+        uint32_t b[4];
+        const int mi = lane >> 3, r = ((mi & 1) << 3) + (lane & 7), ch = dp * 2 + (mi >> 1);
+        ldmatrix_x4_trans(sv + uint32_t(r * 256 + ((ch ^ (r & 7)) << 4)), b);
+        mma_bf16(o[dp * 2], pa0, 0u, pa2, 0u, b[0], b[1]);
+        mma_bf16(o[dp * 2 + 1], pa0, 0u, pa2, 0u, b[2], b[3]);
+      }
+      __syncwarp();
+    }
+    cp_async_wait<0>();
+  }
+  // row sums: add the 4 lanes of a row
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (row < G) {
+#pragma unroll
+    for (int dn = 0; dn < kD / 8; dn++) {
+      sh_o[warp][row][dn * 8 + quad * 2] = o[dn][0];
+      sh_o[warp][row][dn * 8 + quad * 2 + 1] = o[dn][1];
+    }
+    if (quad == 0) { sh_ml[warp][row][0] = m_run; sh_ml[warp][row][1] = l_run; }
+  }
+  __syncthreads();
+  // ---- combine the warps, then the CTAs of the cluster (same as the CUDA-core kernel)
+  constexpr int kThreads = kMW * 32;
+  constexpr int kPer = (G * kD + kThreads - 1) / kThreads;
+  float res_o[kPer], res_m[kPer], res_l[kPer];
+#pragma unroll
+  for (int k = 0; k < kPer; k++) {
+    const int idx = threadIdx.x + k * kThreads;
+    if (idx < G * kD) {
+      const int g = idx / kD, d = idx % kD;
+      float mx = kNegBig;
+      for (int w = 0; w < kMW; w++) mx = fmaxf(mx, sh_ml[w][g][0]);
+      float a = 0.f, ls = 0.f;
+      for (int w = 0; w < kMW; w++) {
+        const float c = exp2f(sh_ml[w][g][0] - mx);
+        a = fmaf(sh_o[w][g][d], c, a);
+        ls = fmaf(sh_ml[w][g][1], c, ls);
+      }
+      res_o[k] = a; res_m[k] = mx; res_l[k] = ls;
+    }
+  }
+  if (S == 1) {
+#pragma unroll
+    for (int k = 0; k < kPer; k++) {
+      const int idx = threadIdx.x + k * kThreads;
+      if (idx < G * kD) p.out[size_t(qi) * p.ldo + h * G * kD + idx] = __float2bfloat16_rn(res_l[k] > 0.f ? res_o[k] / res_l[k] : 0.f);
+    }
+    return;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < kPer; k++) {
+    const int idx = threadIdx.x + k * kThreads;
+    if (idx < G * kD) {
+      const int g = idx / kD, d = idx % kD;
+      sh_o[0][g][d] = res_o[k];
+      if (d == 0) { sh_ml[0][g][0] = res_m[k]; sh_ml[0][g][1] = res_l[k]; }
+    }
+  }
+  cluster_sync();
+  const int per = (G * kD + S - 1) / S;
+  for (int i = threadIdx.x; i < per; i += kThreads) {
+    const int idx = sp * per + i;
+    if (idx < G * kD) {
+      const int g = idx / kD, d = idx % kD;
+      const uint32_t a_ml = smem_addr(&sh_ml[0][g][0]), a_o = smem_addr(&sh_o[0][g][d]);
+      float ms[kMaxSplits], mx = kNegBig;
+      for (int r = 0; r < S; r++) { ms[r] = ld_cluster_f32(a_ml, r); mx = fmaxf(mx, ms[r]); }
+      float a = 0.f, ls = 0.f;
+      for (int r = 0; r < S; r++) {
+        const float c = exp2f(ms[r] - mx);
+        a = fmaf(ld_cluster_f32(a_o, r), c, a);
+        ls = fmaf(ld_cluster_f32(a_ml + 4, r), c, ls);
+      }
+      p.out[size_t(qi) * p.ldo + h * G * kD + idx] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
+    }
+  }
+  cluster_sync();
+}
+
 }  // namespace
 
 extern "C" {
@@ -258,6 +492,26 @@ int tbv_op_paged_attention(const void* q, const void* k_cache, const void* v_cac
   dim3 grid(nq_rows, nkv, splits);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaSuccess;
+  static int impl = -1;  // TBV_ATTN=simt selects the CUDA-core kernel (kept for comparison)
+  if (impl < 0) {
+    const char* ev = getenv("TBV_ATTN");
+    impl = (ev && !strcmp(ev, "simt")) ? 0 : 1;
+    cudaFuncSetAttribute(k_paged_attn_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem);
+    cudaFuncSetAttribute(k_paged_attn_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem);
+    cudaFuncSetAttribute(k_paged_attn_mma<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem);
+    cudaFuncSetAttribute(k_paged_attn_mma<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem);
+  }
+  if (impl == 1) {
+    const dim3 blk(kMW * 32);
+    switch (G) {
+      case 1: e = pdl::launch(k_paged_attn_mma<1>, grid, blk, kMmaSmem, st, splits, p); break;
+      case 2: e = pdl::launch(k_paged_attn_mma<2>, grid, blk, kMmaSmem, st, splits, p); break;
+      case 4: e = pdl::launch(k_paged_attn_mma<4>, grid, blk, kMmaSmem, st, splits, p); break;
+      case 8: e = pdl::launch(k_paged_attn_mma<8>, grid, blk, kMmaSmem, st, splits, p); break;
+      default: return -2;
+    }
+    return e == cudaSuccess ? 0 : -1;
+  }
   switch (G) {
     case 1: e = pdl::launch(k_paged_attn<1, 256>, grid, dim3(256), 0, st, splits, p); break;
     case 2: e = pdl::launch(k_paged_attn<2, 256>, grid, dim3(256), 0, st, splits, p); break;

@@ -119,10 +119,12 @@ class Engine:
 
     def attn_splits_for(self, B: int, max_ctx: int) -> int:
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        # kv splits are the CTAs of one cluster (<= 8): enough CTAs for about two per SM, and at
-        # least 64 cached tokens each
-        want = math.ceil(2 * sms / max(1, B * self.model.nkv))
-        return max(1, min(want, 8, self.model.max_attn_splits, math.ceil(max_ctx / 64)))
+        # kv splits are the CTAs of one cluster: the largest power of two (<= 8) that keeps the whole
+        # grid in one wave (two CTAs per SM) and leaves at least 64 cached tokens per CTA
+        s = 1
+        while s < 8 and B * self.model.nkv * s * 2 <= 2 * sms and max_ctx // (s * 2) >= 64:
+            s *= 2
+        return min(s, self.model.max_attn_splits)
 
     def capture(self, B: int, splits: int, advance: bool) -> torch.cuda.CUDAGraph:
         """Capture one decode step (all layers, both collectives per layer, sampling) as a graph."""
