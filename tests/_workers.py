@@ -463,3 +463,26 @@ def gpu_sp_kernels(rank, world, port):
     err = c.err()
     c.destroy()
     return {"ok": ok, "err": err}
+
+
+def cpu_torch_baseline_tp(rank, world, port):
+    """stock-PyTorch TP model over gloo: every rank produces the same logits, equal (fp32) to TP=1"""
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from libtbvcoll_b200.models.config import get_config
+    from libtbvcoll_b200.models.torch_baseline import TorchLlamaTP
+    from libtbvcoll_b200.utils.weights import RandomSource, shard_for_rank
+    cfg = get_config("tiny-bias")
+    src = RandomSource(cfg, seed=11, dtype=torch.float32)
+    ids = torch.tensor([[5, 9, 100, 7, 1999, 3]])
+    pos = torch.arange(6, dtype=torch.int32)[None]
+    m = TorchLlamaTP(cfg, rank, world, shard_for_rank(cfg, src, rank, world, "cpu", interleave_gate_up=False), "cpu", 1, 32)
+    with torch.no_grad():
+        tp_logits = m.forward(ids, pos, 0)
+        one = TorchLlamaTP(cfg, 0, 1, shard_for_rank(cfg, src, 0, 1, "cpu", interleave_gate_up=False), "cpu", 1, 32)
+        ref = one.forward(ids, pos, 0)
+        toks = m.generate([[5, 9, 100, 7]], 4)
+    dist.destroy_process_group()
+    return {"err": (tp_logits - ref).abs().max().item(), "scale": ref.abs().max().item(), "toks": toks, "ars": m.all_reduces}
