@@ -44,7 +44,7 @@ constexpr int kFusedMaxUnits = 6;  // 16-byte units per thread in the norm phase
 
 __global__ void __launch_bounds__(gemm::kThreads, 1)
 k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const RankCtx* ctxs, const __grid_constant__ FusedPtrs fp,
-                  const __nv_bfloat16* gamma, float eps) {
+                  const __nv_bfloat16* gamma, float eps, bool ll) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ gemm::Smem s;
   __shared__ unsigned long long sh_seq;
@@ -126,7 +126,10 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
       const size_t off = (size_t(t) * H + m0 + f) * 2;
       for (int d = 0; d < c.world; d++) {
         const int peer = (c.rank + d) % c.world;
-        *reinterpret_cast<uint2*>(slot_region(c, peer, ci.slot, c.rank) + off) = pk;
+        if (ll)  // two self-announcing packets: no fence and no flag are needed afterwards
+          st_v4(ll_region(c, peer, ci.slot, c.rank) + off * 2, pk.x, ci.want, pk.y, ci.want);
+        else
+          *reinterpret_cast<uint2*>(slot_region(c, peer, ci.slot, c.rank) + off) = pk;
       }
     }
   }
@@ -136,7 +139,7 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
   __syncwarp();
   if (S > 1) cluster_sync_all(); else __syncthreads();  // all slices of this M tile are stored; peers' shared memory no longer needed
   gemm::teardown(p, s);                                   // TMEM back before the waiting phase
-  if (split == 0 && threadIdx.x == 0) {
+  if (!ll && split == 0 && threadIdx.x == 0) {
     fence_sys();
     for (int peer = 0; peer < c.world; peer++)
       st_relaxed_sys(c.flags[peer] + flag_index(c, ci.slot, 0, c.rank, m_tile), ci.want);
@@ -150,11 +153,13 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
   unsigned long long t_ready = 0;
   if (cta_id < waiters) {
     const int n_tiles = gridDim.x;
-    for (int i = threadIdx.x; i < c.world * n_tiles; i += blockDim.x) {
-      const int src = i / n_tiles, ch = i % n_tiles;
-      wait_flag(c, c.flags[c.rank] + flag_index(c, ci.slot, 0, src, ch), ci.want, kWhereFused, src, ch, ci.seq);
+    if (!ll) {
+      for (int i = threadIdx.x; i < c.world * n_tiles; i += blockDim.x) {
+        const int src = i / n_tiles, ch = i % n_tiles;
+        wait_flag(c, c.flags[c.rank] + flag_index(c, ci.slot, 0, src, ch), ci.want, kWhereFused, src, ch, ci.seq);
+      }
+      __syncthreads();
     }
-    __syncthreads();
     if (threadIdx.x == 0 && cta_id == 0) { t_ready = tbv::globaltimer(); c.dm->bc[2] = ci.seq; c.dm->bc[6] = t_ready; }
     const int upr = H / 8;
     for (int row = cta_id; row < T; row += waiters) {
@@ -166,7 +171,8 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
           const size_t off = size_t(row) * upr + u;
           float acc[8];
           for (int r = 0; r < c.world; r++) {
-            uint4 v = ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, ci.slot, r)) + off);
+            uint4 v = ll ? ll_pull_unit(c, ci.slot, r, off, ci.want, m_tile, ci.seq)
+                         : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, ci.slot, r)) + off);
             float f[8];
             Pack<__nv_bfloat16>::unpack(v, f);
 #pragma unroll
@@ -237,8 +243,10 @@ static int launch_fused(tbv_comm* c, const void* const* ws, const void* const* x
     g_attr_done = true;
   }
   const RankCtx* ctxs = c->ctxs_dev;
+  const size_t nbytes = size_t(tokens) * hidden * 2;
+  const bool ll = (c->knobs.algo == TBV_ALGO_AUTO || c->knobs.algo == TBV_ALGO_LL) && nbytes * 2 <= c->ll_cap && long(nbytes) <= c->knobs.ll_max;
   cudaError_t e = pdl::launch(k_gemm_ar_rmsnorm, dim3(hidden / 128, nr, splits), dim3(gemm::kThreads), smem,
-                              static_cast<cudaStream_t>(stream), splits, maps, p, ctxs, fp, static_cast<const __nv_bfloat16*>(gamma), eps);
+                              static_cast<cudaStream_t>(stream), splits, maps, p, ctxs, fp, static_cast<const __nv_bfloat16*>(gamma), eps, ll);
   if (e != cudaSuccess) {
     fprintf(stderr, "[tbvcoll] fused gemm+all-reduce launch failed: %s\n", cudaGetErrorString(e));
     c->sticky_err.store(1);

@@ -5,7 +5,7 @@ This is the model layer the reference documents but does not ship ("TP=1/2 decod
 weight TP sharding, RoPE, GQA, KV cache, greedy", reports/11_custom_engine.md:10-20), with
 the weight fusions it names (q/k/v -> qkv, gate/up -> gate_up, :38).  Per layer:
 
-    qkv GEMM -> RoPE + KV-cache write -> paged attention -> o_proj GEMM (partial sums)
+    qkv GEMM (RoPE + KV-cache write in its epilogue) -> paged attention -> o_proj GEMM (partial sums)
     -> all-reduce + residual + RMSNorm (ONE kernel)  -> gate_up GEMM with SiLU-mul epilogue
     -> down_proj GEMM (partial sums) -> all-reduce + residual + next RMSNorm (ONE kernel)
 
@@ -79,8 +79,9 @@ class LlamaTP:
         ops.rmsnorm(h, w["layers.0.input_norm"], cfg.rms_eps, out=xn)
         for l in range(cfg.num_layers):
             p = f"layers.{l}."
-            ops.gemm(xn, w[p + "qkv.weight"], out=qkv, bias=w.get(p + "qkv.bias"))
-            ops.rope_kv(qkv, positions, self.cos_sin, slot_mapping, self.k_cache[l], self.v_cache[l], self.nq, self.nkv, self.D)
+            # qkv projection; RoPE and the KV-cache write happen in its epilogue
+            ops.gemm_qkv_rope(xn, w[p + "qkv.weight"], qkv, positions, self.cos_sin, slot_mapping, self.k_cache[l], self.v_cache[l],
+                              self.nq, self.nkv, bias=w.get(p + "qkv.bias"))
             ops.paged_attention(q_view, self.k_cache[l], self.v_cache[l], block_tables, ctx_lens, attn_view, self.scale,
                                 self.block_size, seq_of_query=seq_of_query, splits=attn_splits, workspace=self.attn_ws)
             tp.gemm_all_reduce_add_rmsnorm(attn, w[p + "o.weight"], h, w[p + "post_norm"], cfg.rms_eps, out=part)   # part := norm(h), h += sum

@@ -33,6 +33,8 @@ def lib():
     I, F, LL, SZ = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_size_t
     l.tbv_op_gemm.argtypes = [c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, I, I, c_vp]
     l.tbv_op_gemm_error.restype = I
+    l.tbv_op_gemm_qkv_rope.argtypes = [c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, I, c_vp]
+    l.tbv_op_gemm_qkv_rope.restype = I
     l.tbv_op_gemm_config.argtypes = [I, I, I, I, ctypes.POINTER(I), ctypes.POINTER(I), ctypes.POINTER(I)]
     l.tbv_op_rmsnorm.argtypes = [c_vp, c_vp, c_vp, I, I, F, c_vp]
     l.tbv_op_add_rmsnorm.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, I, I, F, c_vp]
@@ -97,6 +99,22 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, b
     _chk(lib().tbv_op_gemm(_p(w), _p(x), _p(out), _p(bias), M, N, K, x.stride(0), out.stride(0), epi, splits, _st()), "tbv_op_gemm")
     _count()
     return out
+
+
+def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
+                  slot_mapping: Optional[torch.Tensor], k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], nq: int, nkv: int,
+                  bias: Optional[torch.Tensor] = None, splits: int = 0) -> torch.Tensor:
+    """qkv[N, (nq+2nkv)*128] = x @ w^T (+ bias) with RoPE applied to the q and k heads and the k, v
+    heads written to the paged cache, all in the GEMM epilogue (head_dim 128).  Same bits as
+    ``gemm`` followed by ``rope_kv``."""
+    N, K = x.shape
+    M = w.shape[0]
+    assert M == (nq + 2 * nkv) * 128 and qkv.shape == (N, M) and positions.dtype is torch.int32 and cos_sin.shape[1] == 128
+    _chk(lib().tbv_op_gemm_qkv_rope(_p(w), _p(x), _p(qkv), _p(bias), M, N, K, x.stride(0), qkv.stride(0), _p(positions), _p(cos_sin),
+                                    _p(slot_mapping), _p(k_cache), _p(v_cache), nq, nkv, cos_sin.shape[0], splits, _st()),
+         "tbv_op_gemm_qkv_rope")
+    _count()
+    return qkv
 
 
 def gemm_config(M: int, N: int, K: int, splits: int = 0):

@@ -164,3 +164,26 @@ def test_paged_attention_as_causal_prefill(ops):
     rows = torch.cat([torch.arange(bs) + int(b) * bs for b in bt[0]])[:T].to(DEV)
     want = ref.attention(q, kc[rows], vc[rows], 0.1, causal_offset=0)
     assert (out.float() - want).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("T,nq,nkv,K,splits,bias", [(8, 8, 2, 512, 1, False), (5, 4, 4, 4096, 0, True), (70, 8, 2, 1024, 2, False),
+                                                     (300, 2, 1, 256, 1, True), (16, 16, 4, 4096, 8, False)])
+def test_qkv_gemm_with_rope_epilogue_equals_gemm_then_rope(ops, T, nq, nkv, K, splits, bias):
+    D, bs = 128, 16
+    M = (nq + 2 * nkv) * D
+    x, w = rnd(T, K, seed=31), rnd(M, K, scale=0.05, seed=32)
+    b = rnd(M, seed=33) if bias else None
+    pos = (torch.arange(T, dtype=torch.int32) * 3 % 200).to(DEV)
+    cs = ops.rope_cos_sin(D, 256, 5e5, DEV)
+    nslots = bs * ((T + bs - 1) // bs + 2)
+    slots = torch.randperm(nslots, generator=torch.Generator().manual_seed(2))[:T].to(DEV)
+    slots[T // 2] = -1
+    kc1, vc1 = torch.zeros(nslots, nkv, D, dtype=torch.bfloat16, device=DEV), torch.zeros(nslots, nkv, D, dtype=torch.bfloat16, device=DEV)
+    kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(vc1)
+    ref_qkv = ops.gemm(x, w, bias=b, splits=splits)
+    ops.rope_kv(ref_qkv, pos, cs, slots, kc1, vc1, nq, nkv, D)
+    got = torch.zeros(T, M, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_qkv_rope(x, w, got, pos, cs, slots, kc2, vc2, nq, nkv, bias=b, splits=splits)
+    torch.cuda.synchronize()
+    assert not ops.gemm_error()
+    assert torch.equal(got, ref_qkv) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
