@@ -64,7 +64,7 @@ Knobs Knobs::from_env() {
   k.nchan = int(env_long("TBV_NCHAN", 0));
   k.nvls = int(env_long("TBV_NVLS", 0));
   k.init_timeout_s = env_double("TBV_INIT_TIMEOUT", 60.0);
-  k.ll_max = env_long("TBV_LL_MAX", 256 << 10);
+  k.ll_max = env_long("TBV_LL_MAX", -1);  // -1: chosen from the world size when the communicator is created
   k.nvls_min = env_long("TBV_NVLS_MIN", LONG_MAX);  // auto never picks the switch-reduced kernel unless asked
   const char* a = getenv("TBV_ALGO");
   if (a) {
@@ -290,6 +290,10 @@ static int alloc_rank_state(tbv_comm* c, GpuRank& g) {
 }
 
 static void compute_sizes(tbv_comm* c) {
+  // LL packets double the bytes and every rank writes to every peer, so the size up to which they win
+  // shrinks with the world (measured, graph-timed: 2 ranks 4.6 vs 6.3 us at 8 KB and ahead up to 256 KB;
+  // 8 ranks 11.2 vs 9.8 us at 8 KB — plain one-shot is better there).
+  if (c->knobs.ll_max < 0) c->knobs.ll_max = c->world <= 2 ? (256 << 10) : (c->world <= 4 ? (64 << 10) : 0);
   c->flag_bytes = (size_t(c->knobs.nslot) * 2 * c->world * TBV_MAXCHAN * sizeof(unsigned) + 4095) & ~size_t(4095);
   c->data_bytes = size_t(c->knobs.nslot) * size_t(c->world + 1) * c->cap;
   // LL area: two bytes on the wire per payload byte, one region per (slot, source)

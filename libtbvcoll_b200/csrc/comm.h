@@ -30,7 +30,7 @@ struct Knobs {
   int nvls = 0;           // TBV_NVLS: 1 = set up a multicast object and allow the NVLS kernels
   int mem = 0;            // TBV_MEM: 0 = VMM with IPC fallback, 1 = VMM only, 2 = cudaIpc only
   double init_timeout_s = 60.0;  // TBV_INIT_TIMEOUT
-  long ll_max = 256 << 10;       // TBV_LL_MAX: largest message that uses flag-in-payload (LL) packets
+  long ll_max = -1;              // TBV_LL_MAX: largest message that uses flag-in-payload (LL) packets (-1: by world size)
   long nvls_min = 0x7fffffffffffffffl;  // TBV_NVLS_MIN: smallest message for the switch-reduced kernel in auto mode
   static Knobs from_env();
 };
