@@ -34,7 +34,7 @@ extern "C" {
 
 #define TBV_MAXRANK 8
 #define TBV_MAXSLOT 32
-#define TBV_MAXCHAN 128
+#define TBV_MAXCHAN 256
 
 typedef struct tbv_comm tbv_comm;
 

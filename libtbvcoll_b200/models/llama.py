@@ -105,7 +105,7 @@ class LlamaTP:
             return False
         rpr, H = T // tp.world, cfg.hidden_size
         bn = next((b for b in (256, 128, 64, 32, 16) if rpr % b == 0), 0)
-        return bool(bn) and T * H * 2 <= tp.comm.cap and (rpr // bn) * (H // 128) <= 128
+        return bool(bn) and T * H * 2 <= tp.comm.cap and (rpr // bn) * (H // 128) <= 256
 
     def forward_sp(self, T: int, ids, positions, slot_mapping, block_tables, ctx_lens, seq_of_query, logit_rows, n_logits, out_tokens):
         """Prefill with the token dimension sharded between the collectives (Megatron-style
