@@ -458,6 +458,168 @@ __global__ void __launch_bounds__(kMW * 32) k_paged_attn_mma(const AttnParams p)
   cluster_sync();
 }
 
+// ---------------------------------------------------------------------------------------------
+// Prefill form: a CTA owns up to QT = 64 / G consecutive query tokens of ONE sequence for one kv
+// head — 64 MMA rows (token, query head) on 4 warps — and all four warps consume the same K/V
+// tiles from shared memory, so a cached token is read once per 64 rows instead of once per query
+// row.  Causal: row (t, g) sees keys [0, ctx_lens[t]).  Tiles never straddle sequences: the
+// host passes a list of (first row, row count) segments.
+constexpr int kPfWarps = 4;
+constexpr int kPfStages = 4;
+constexpr int kPfSmem = kPfStages * 2 * kTileBytes;   // 32 KB
+
+struct PrefillParams {
+  AttnParams a;
+  const int* tiles;   // [ntiles, 2]: first query row, number of rows (<= 64 / G)
+};
+
+template <int G>
+__global__ void __launch_bounds__(kPfWarps * 32) k_prefill_attn_mma(const PrefillParams pp) {
+  extern __shared__ __align__(1024) uint8_t dsm[];
+  __shared__ int sh_bt[kMaxBlocksPerCta];
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();
+  const AttnParams& p = pp.a;
+  constexpr int QT = 64 / G;
+  const int row0 = pp.tiles[2 * blockIdx.x], nrows = pp.tiles[2 * blockIdx.x + 1], h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rlo = warp * 16 + (lane >> 2), rhi = rlo + 8;      // CTA-level MMA rows of this lane
+  const int quad = lane & 3;
+  const int tlo = rlo / G, glo = rlo % G, thi = rhi / G, ghi = rhi % G;   // (token in tile, query head)
+  const bool vlo = tlo < nrows, vhi = thi < nrows;
+  const int seq = p.seq_of_query ? p.seq_of_query[row0] : row0;
+  const int* bt = p.block_tables + size_t(seq) * p.max_blocks;
+  const int ctx_lo = vlo ? p.ctx_lens[row0 + tlo] : 0, ctx_hi = vhi ? p.ctx_lens[row0 + thi] : 0;
+  const int ctx_max = p.ctx_lens[row0 + nrows - 1];             // rows are in position order
+  (void)QT;
+
+  uint32_t qa[kD / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < kD / 16; ks++) {
+    qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
+    if (vlo) {
+      const __nv_bfloat16* qp = p.q + size_t(row0 + tlo) * p.ldq + (h * G + glo) * kD + ks * 16 + quad * 2;
+      qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
+      qa[ks][2] = *reinterpret_cast<const uint32_t*>(qp + 8);
+    }
+    if (vhi) {
+      const __nv_bfloat16* qp = p.q + size_t(row0 + thi) * p.ldq + (h * G + ghi) * kD + ks * 16 + quad * 2;
+      qa[ks][1] = *reinterpret_cast<const uint32_t*>(qp);
+      qa[ks][3] = *reinterpret_cast<const uint32_t*>(qp + 8);
+    }
+  }
+  float o[kD / 8][4];
+#pragma unroll
+  for (int dn = 0; dn < kD / 8; dn++) o[dn][0] = o[dn][1] = o[dn][2] = o[dn][3] = 0.f;
+  float m_lo = kNegBig, m_hi = kNegBig, l_lo = 0.f, l_hi = 0.f;
+
+  const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(dsm));
+  const int span = kMaxBlocksPerCta * p.block_size;
+  for (int pass0 = 0; pass0 < ctx_max; pass0 += span) {
+    const int pass1 = min(ctx_max, pass0 + span);
+    const int b0 = pass0 / p.block_size, nb = (pass1 - pass0 + p.block_size - 1) / p.block_size;
+    __syncthreads();
+    if (threadIdx.x < nb) sh_bt[threadIdx.x] = bt[b0 + threadIdx.x];
+    __syncthreads();
+    const int ntiles = (pass1 - pass0 + kTile - 1) / kTile;
+    auto issue = [&](int i) {   // all 128 threads stage tile i: 256 K chunks + 256 V chunks
+      if (i < ntiles) {
+        const int tok0 = pass0 + i * kTile;
+        const uint32_t sk = sbase + (i % kPfStages) * 2 * kTileBytes, sv = sk + kTileBytes;
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          const int id = threadIdx.x + 128 * c, r = id >> 4, ch = id & 15;
+          const int tok = tok0 + r;
+          const uint32_t off = uint32_t(r * 256 + ((ch ^ (r & 7)) << 4));
+          if (tok < pass1) {
+            const long long slot = (long long)sh_bt[tok / p.block_size - b0] * p.block_size + tok % p.block_size;
+            const size_t g = (size_t(slot) * p.nkv + h) * kD + ch * 8;
+            cp_async16(sk + off, p.k_cache + g);
+            cp_async16(sv + off, p.v_cache + g);
+          } else {
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(sv + off), "r"(0u) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(sk + off), "r"(0u) : "memory");
+          }
+        }
+      }
+      cp_async_commit();
+    };
+    issue(0); issue(1); issue(2);
+    for (int i = 0; i < ntiles; i++) {
+      issue(i + 3);
+      cp_async_wait<3>();
+      __syncthreads();
+      const int tok0 = pass0 + i * kTile;
+      const uint32_t sk = sbase + (i % kPfStages) * 2 * kTileBytes, sv = sk + kTileBytes;
+      float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int ks = 0; ks < kD / 16; ks++) {
+        uint32_t b[4];
+        const int mi = lane >> 3, r = ((mi >> 1) << 3) + (lane & 7), ch = ks * 2 + (mi & 1);
+        ldmatrix_x4(sk + uint32_t(r * 256 + ((ch ^ (r & 7)) << 4)), b);
+        mma_bf16(sc[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[0], b[1]);
+        mma_bf16(sc[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[2], b[3]);
+      }
+      float mx_lo = m_lo, mx_hi = m_hi;
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          const int tok = tok0 + nt * 8 + quad * 2 + j;
+          sc[nt][j] = tok < ctx_lo ? sc[nt][j] * p.scale_log2 : kNegBig;
+          sc[nt][2 + j] = tok < ctx_hi ? sc[nt][2 + j] * p.scale_log2 : kNegBig;
+          mx_lo = fmaxf(mx_lo, sc[nt][j]);
+          mx_hi = fmaxf(mx_hi, sc[nt][2 + j]);
+        }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float c_lo = exp2f(m_lo - mx_lo), c_hi = exp2f(m_hi - mx_hi);
+      m_lo = mx_lo; m_hi = mx_hi;
+      float pr[2][4], s_lo = 0.f, s_hi = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          const int tok = tok0 + nt * 8 + quad * 2 + j;
+          pr[nt][j] = tok < ctx_lo ? exp2f(sc[nt][j] - mx_lo) : 0.f;
+          pr[nt][2 + j] = tok < ctx_hi ? exp2f(sc[nt][2 + j] - mx_hi) : 0.f;
+          s_lo += pr[nt][j];
+          s_hi += pr[nt][2 + j];
+        }
+      l_lo = l_lo * c_lo + s_lo;
+      l_hi = l_hi * c_hi + s_hi;
+#pragma unroll
+      for (int dn = 0; dn < kD / 8; dn++) { o[dn][0] *= c_lo; o[dn][1] *= c_lo; o[dn][2] *= c_hi; o[dn][3] *= c_hi; }
+      const uint32_t pa0 = pack_bf16(pr[0][0], pr[0][1]), pa1 = pack_bf16(pr[0][2], pr[0][3]);
+      const uint32_t pa2 = pack_bf16(pr[1][0], pr[1][1]), pa3 = pack_bf16(pr[1][2], pr[1][3]);
+#pragma unroll
+      for (int dp = 0; dp < kD / 16; dp++) {
+        uint32_t b[4];
+        const int mi = lane >> 3, r = ((mi & 1) << 3) + (lane & 7), ch = dp * 2 + (mi >> 1);
+        ldmatrix_x4_trans(sv + uint32_t(r * 256 + ((ch ^ (r & 7)) << 4)), b);
+        mma_bf16(o[dp * 2], pa0, pa1, pa2, pa3, b[0], b[1]);
+        mma_bf16(o[dp * 2 + 1], pa0, pa1, pa2, pa3, b[2], b[3]);
+      }
+      __syncthreads();   // everyone is done with this stage before it is refilled
+    }
+    cp_async_wait<0>();
+  }
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+#pragma unroll
+  for (int dn = 0; dn < kD / 8; dn++) {
+    if (vlo) *reinterpret_cast<__nv_bfloat162*>(p.out + size_t(row0 + tlo) * p.ldo + (h * G + glo) * kD + dn * 8 + quad * 2) =
+        __floats2bfloat162_rn(o[dn][0] * inv_lo, o[dn][1] * inv_lo);
+    if (vhi) *reinterpret_cast<__nv_bfloat162*>(p.out + size_t(row0 + thi) * p.ldo + (h * G + ghi) * kD + dn * 8 + quad * 2) =
+        __floats2bfloat162_rn(o[dn][2] * inv_hi, o[dn][3] * inv_hi);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -517,6 +679,41 @@ int tbv_op_paged_attention(const void* q, const void* k_cache, const void* v_cac
     case 2: e = pdl::launch(k_paged_attn<2, 256>, grid, dim3(256), 0, st, splits, p); break;
     case 4: e = pdl::launch(k_paged_attn<4, 256>, grid, dim3(256), 0, st, splits, p); break;
     case 8: e = pdl::launch(k_paged_attn<8, 128>, grid, dim3(128), 0, st, splits, p); break;
+    default: return -2;
+  }
+  return e == cudaSuccess ? 0 : -1;
+}
+
+
+// Causal prefill over the paged cache.  tiles: int32 [ntiles, 2] = (first query row, rows <= 64 / G) with all
+// rows of a tile belonging to one sequence in position order; ctx_lens[row] = keys visible to that row.
+int tbv_op_prefill_attention(const void* q, const void* k_cache, const void* v_cache, const void* block_tables,
+                             const void* seq_of_query, const void* ctx_lens, const void* tiles, void* out, int ntiles,
+                             int nq_heads, int nkv, int head_dim, int ldq, int ldo, int block_size, int max_blocks, float scale,
+                             void* stream) {
+  if (ntiles <= 0) return 0;
+  if (head_dim != kD || nq_heads % nkv || (ldq % 8) || block_size <= 0) return -2;
+  const int G = nq_heads / nkv;
+  PrefillParams pp{};
+  AttnParams& p = pp.a;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+  p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+  p.block_tables = static_cast<const int*>(block_tables);
+  p.seq_of_query = static_cast<const int*>(seq_of_query);
+  p.ctx_lens = static_cast<const int*>(ctx_lens);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.ldq = ldq; p.ldo = ldo; p.nkv = nkv; p.block_size = block_size; p.max_blocks = max_blocks; p.splits = 1;
+  pp.tiles = static_cast<const int*>(tiles);
+  const dim3 grid(ntiles, nkv), blk(kPfWarps * 32);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  switch (G) {
+    case 1: e = pdl::launch(k_prefill_attn_mma<1>, grid, blk, kPfSmem, st, 1, pp); break;
+    case 2: e = pdl::launch(k_prefill_attn_mma<2>, grid, blk, kPfSmem, st, 1, pp); break;
+    case 4: e = pdl::launch(k_prefill_attn_mma<4>, grid, blk, kPfSmem, st, 1, pp); break;
+    case 8: e = pdl::launch(k_prefill_attn_mma<8>, grid, blk, kPfSmem, st, 1, pp); break;
     default: return -2;
   }
   return e == cudaSuccess ? 0 : -1;

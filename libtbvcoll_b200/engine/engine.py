@@ -65,6 +65,11 @@ class Engine:
         # divides evenly; TBV_SP_PREFILL=0 keeps the all-reduce path
         self.sp_prefill = os.environ.get("TBV_SP_PREFILL", "1") != "0"
         self.sp_chunks = 0
+        # query-tiled tensor-core attention for prompt rows (TBV_PREFILL_ATTN=rows: one CTA per query row)
+        self.tiled_prefill_attention = os.environ.get("TBV_PREFILL_ATTN", "tiled") != "rows"
+        self._ids_np, self._pos_np = self.ids_h.numpy(), self.pos_h.numpy()
+        self._slots_np, self._ctx_np, self._out_np = self.slots_h.numpy(), self.ctx_h.numpy(), self.out_h.numpy()
+        self._tables_np = self.bm.tables_host.numpy()
         self.graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
         self.launches_per_step = 0
         self.last_stats: Dict[str, float] = {}
@@ -96,13 +101,14 @@ class Engine:
             n_log = len(last_rows)
             out = torch.zeros(max(n_log, 1), dtype=torch.int64, device=dev)
             logit_rows = torch.tensor([r for r, _ in last_rows] or [0], dtype=torch.int64).to(dev)
+            tiles = ops.prefill_tiles(seqof, self.model.nq // self.model.nkv).to(dev) if self.tiled_prefill_attention else None
             if self.sp_prefill and self.model.sp_ok(T):
                 self.model.forward_sp(T, ids.to(dev), pos.to(dev), slots.to(dev), self.bm.tables, (pos + 1).to(dev), seqof.to(dev),
-                                      logit_rows, max(n_log, 1), out)
+                                      logit_rows, max(n_log, 1), out, prefill_tiles=tiles)
                 self.sp_chunks += 1
             else:
                 self.model.forward(T, ids.to(dev), pos.to(dev), slots.to(dev), self.bm.tables, (pos + 1).to(dev), seqof.to(dev),
-                                   logit_rows, max(n_log, 1), out, attn_splits=1)
+                                   logit_rows, max(n_log, 1), out, attn_splits=1, prefill_tiles=tiles)
             if n_log:
                 toks = out[:n_log].tolist()
                 for (r, b), t in zip(last_rows, toks):
@@ -145,12 +151,16 @@ class Engine:
         self.graphs[key] = g
         return g
 
-    def _load_decode_inputs(self, B: int, tokens: Sequence[int], lens: Sequence[int]) -> None:
-        """positions = index of the token being fed (= tokens so far - 1 + ... ) for every row."""
-        for b in range(B):
-            pos = lens[b]                     # the fed token sits at position `lens[b]`
-            self.ids_h[b], self.pos_h[b] = tokens[b], pos
-            self.slots_h[b], self.ctx_h[b] = self.bm.slot(b, pos), pos + 1
+    def _load_decode_inputs(self, B: int, tokens, lens) -> None:
+        """Stage one step's inputs in pinned memory (vectorised on the numpy views of the pinned
+        tensors) and copy them to the device: the fed token of row b sits at position lens[b]."""
+        import numpy as np
+        pos = np.asarray(lens, dtype=np.int64)[:B]
+        self._ids_np[:B] = np.asarray(tokens, dtype=np.int64)[:B]
+        self._pos_np[:B] = pos
+        self._ctx_np[:B] = pos + 1
+        bs = self.block_size
+        self._slots_np[:B] = self._tables_np[np.arange(B), pos // bs].astype(np.int64) * bs + pos % bs
         self.ids[:B].copy_(self.ids_h[:B], non_blocking=True)
         self.positions[:B].copy_(self.pos_h[:B], non_blocking=True)
         self.slots[:B].copy_(self.slots_h[:B], non_blocking=True)
@@ -187,25 +197,31 @@ class Engine:
                 outs[b].extend(hist[:, b].tolist())
         else:
             g = self.capture(B, splits, False) if use_graph else None
-            cur = list(first)
-            done = [False] * B
+            import numpy as np
+            cur = np.asarray(first, dtype=np.int64)
+            lens_np = np.asarray(lens, dtype=np.int64)
+            done = np.zeros(B, dtype=bool)
+            trace = []
+            stream = torch.cuda.current_stream(self.device)
             for _ in range(steps):
-                self._load_decode_inputs(B, cur, lens)
+                self._load_decode_inputs(B, cur, lens_np)
                 if g is not None:
                     g.replay()
                 else:
                     self._decode_step(B, splits, False)
                 self.out_h[:B].copy_(self.out_tokens[:B], non_blocking=True)
-                torch.cuda.current_stream(self.device).synchronize()
-                cur = self.out_h[:B].tolist()
+                stream.synchronize()
+                cur = self._out_np[:B].copy()
+                lens_np += 1
+                trace.append((cur, done.copy()))
+                if eos_id is not None:
+                    done |= cur == eos_id
+                    if done.all():
+                        break
+            for tok, was_done in trace:
                 for b in range(B):
-                    lens[b] += 1
-                    if not done[b]:
-                        outs[b].append(cur[b])
-                        if eos_id is not None and cur[b] == eos_id:
-                            done[b] = True
-                if eos_id is not None and all(done):
-                    break
+                    if not was_done[b]:
+                        outs[b].append(int(tok[b]))
         t2 = time.perf_counter()
         self.last_stats = {"prefill_s": t1 - t0, "decode_s": t2 - t1, "decode_steps": steps, "batch": B,
                            "decode_tok_s": B * steps / max(t2 - t1, 1e-9), "attn_splits": splits,

@@ -65,7 +65,7 @@ class LlamaTP:
     # -- one forward pass over T token rows ----------------------------------------------------
     def forward(self, T: int, ids: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor, block_tables: torch.Tensor,
                 ctx_lens: torch.Tensor, seq_of_query: Optional[torch.Tensor], logit_rows: Optional[torch.Tensor], n_logits: int,
-                out_tokens: torch.Tensor, attn_splits: int = 1) -> torch.Tensor:
+                out_tokens: torch.Tensor, attn_splits: int = 1, prefill_tiles: Optional[torch.Tensor] = None) -> torch.Tensor:
         """ids/positions/slot_mapping/ctx_lens: [T]; logit_rows: int64 [n_logits] rows whose next
         token is wanted (None = all T rows, decode).  Writes greedy tokens to out_tokens[:n_logits]."""
         cfg, w, tp = self.cfg, self.w, self.tp
@@ -82,8 +82,12 @@ class LlamaTP:
             # qkv projection; RoPE and the KV-cache write happen in its epilogue
             ops.gemm_qkv_rope(xn, w[p + "qkv.weight"], qkv, positions, self.cos_sin, slot_mapping, self.k_cache[l], self.v_cache[l],
                               self.nq, self.nkv, bias=w.get(p + "qkv.bias"))
-            ops.paged_attention(q_view, self.k_cache[l], self.v_cache[l], block_tables, ctx_lens, attn_view, self.scale,
-                                self.block_size, seq_of_query=seq_of_query, splits=attn_splits, workspace=self.attn_ws)
+            if prefill_tiles is not None:
+                ops.prefill_attention(q_view, self.k_cache[l], self.v_cache[l], block_tables, ctx_lens, seq_of_query, prefill_tiles,
+                                      attn_view, self.scale, self.block_size)
+            else:
+                ops.paged_attention(q_view, self.k_cache[l], self.v_cache[l], block_tables, ctx_lens, attn_view, self.scale,
+                                    self.block_size, seq_of_query=seq_of_query, splits=attn_splits, workspace=self.attn_ws)
             tp.gemm_all_reduce_add_rmsnorm(attn, w[p + "o.weight"], h, w[p + "post_norm"], cfg.rms_eps, out=part)   # part := norm(h), h += sum
             ops.gemm(part, w[p + "gate_up.weight"], out=act, epi=ops.EPI_SILU_MUL)
             nxt = w[f"layers.{l + 1}.input_norm"] if l + 1 < cfg.num_layers else w["norm"]
@@ -107,7 +111,8 @@ class LlamaTP:
         bn = next((b for b in (256, 128, 64, 32, 16) if rpr % b == 0), 0)
         return bool(bn) and T * H * 2 <= tp.comm.cap and (rpr // bn) * (H // 128) <= 256
 
-    def forward_sp(self, T: int, ids, positions, slot_mapping, block_tables, ctx_lens, seq_of_query, logit_rows, n_logits, out_tokens):
+    def forward_sp(self, T: int, ids, positions, slot_mapping, block_tables, ctx_lens, seq_of_query, logit_rows, n_logits, out_tokens,
+                   prefill_tiles=None):
         """Prefill with the token dimension sharded between the collectives (Megatron-style
         sequence parallelism): residual stream and norms live on T/tp rows; each column-parallel GEMM
         is all-gather -> GEMM, each row-parallel GEMM is GEMM -> reduce-scatter (+ residual + RMSNorm
@@ -134,8 +139,12 @@ class LlamaTP:
             p = f"layers.{l}."
             must(comm.allgather_gemm(xn, w[p + "qkv.weight"], qkv), "allgather_gemm(qkv)")
             ops.rope_kv(qkv, positions, self.cos_sin, slot_mapping, self.k_cache[l], self.v_cache[l], self.nq, self.nkv, self.D)
-            ops.paged_attention(q_view, self.k_cache[l], self.v_cache[l], block_tables, ctx_lens, attn_view, self.scale,
-                                self.block_size, seq_of_query=seq_of_query, splits=1)
+            if prefill_tiles is not None:
+                ops.prefill_attention(q_view, self.k_cache[l], self.v_cache[l], block_tables, ctx_lens, seq_of_query, prefill_tiles,
+                                      attn_view, self.scale, self.block_size)
+            else:
+                ops.paged_attention(q_view, self.k_cache[l], self.v_cache[l], block_tables, ctx_lens, attn_view, self.scale,
+                                    self.block_size, seq_of_query=seq_of_query, splits=1)
             must(comm.gemm_reduce_scatter(attn, w[p + "o.weight"], residual=h, gamma=w[p + "post_norm"], eps=cfg.rms_eps, y=part),
                  "gemm_reduce_scatter(o_proj)")
             must(comm.allgather_gemm(part, w[p + "gate_up.weight"], gu), "allgather_gemm(gate_up)")

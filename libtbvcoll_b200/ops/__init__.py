@@ -49,6 +49,8 @@ def lib():
     l.tbv_op_argmax_merge.argtypes = [c_vp, c_vp, I, I, LL, c_vp, c_vp]
     l.tbv_op_decode_advance.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, c_vp, c_vp, I, c_vp]
     l.tbv_op_decode_advance.restype = I
+    l.tbv_op_prefill_attention.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, I, I, I, F, c_vp]
+    l.tbv_op_prefill_attention.restype = I
     l.tbv_op_attn_workspace.argtypes = [I, I, I, I]
     l.tbv_op_attn_workspace.restype = SZ
     l.tbv_op_paged_attention.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, I, I, I, I, F, c_vp]
@@ -263,5 +265,37 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     _chk(lib().tbv_op_paged_attention(_p(q), _p(k_cache), _p(v_cache), _p(block_tables), _p(seq_of_query), _p(ctx_lens), _p(out),
                                       _p(workspace), Nq, nq, nkv, D, q.stride(0), out.stride(0), block_size, block_tables.shape[1],
                                       splits, scale, _st()), "tbv_op_paged_attention")
+    _count()
+    return out
+
+
+def prefill_tiles(seq_of_row, group: int) -> torch.Tensor:
+    """Segments of at most 64 // group consecutive query rows that belong to one sequence, as the
+    int32 [ntiles, 2] (first row, count) list ``prefill_attention`` takes.  ``seq_of_row``: host
+    sequence (list / CPU tensor) giving the sequence of every query row, rows grouped by sequence
+    in position order."""
+    qt = max(1, 64 // group)
+    seqs = seq_of_row.tolist() if hasattr(seq_of_row, "tolist") else list(seq_of_row)
+    tiles, i, n = [], 0, len(seqs)
+    while i < n:
+        j = i
+        while j < n and j - i < qt and seqs[j] == seqs[i]:
+            j += 1
+        tiles.append((i, j - i))
+        i = j
+    return torch.tensor(tiles, dtype=torch.int32)
+
+
+def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor, ctx_lens: torch.Tensor,
+                      seq_of_query: torch.Tensor, tiles: torch.Tensor, out: torch.Tensor, scale: float, block_size: int) -> torch.Tensor:
+    """Causal attention of prompt rows over the paged cache with query tiling on tensor cores: up to
+    64 (token, head) rows share every K/V tile.  Same arguments as ``paged_attention`` plus ``tiles``
+    (device int32 [ntiles, 2] from ``prefill_tiles``)."""
+    Nq, nq, D = q.shape
+    nkv = k_cache.shape[-2]
+    assert q.stride(2) == 1 and q.stride(1) == D and out.stride(2) == 1 and out.stride(1) == D and tiles.dtype is torch.int32
+    _chk(lib().tbv_op_prefill_attention(_p(q), _p(k_cache), _p(v_cache), _p(block_tables), _p(seq_of_query), _p(ctx_lens), _p(tiles),
+                                        _p(out), tiles.shape[0], nq, nkv, D, q.stride(0), out.stride(0), block_size,
+                                        block_tables.shape[1], scale, _st()), "tbv_op_prefill_attention")
     _count()
     return out

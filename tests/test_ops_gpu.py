@@ -187,3 +187,32 @@ def test_qkv_gemm_with_rope_epilogue_equals_gemm_then_rope(ops, T, nq, nkv, K, s
     torch.cuda.synchronize()
     assert not ops.gemm_error()
     assert torch.equal(got, ref_qkv) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+
+
+@pytest.mark.parametrize("nq,nkv", [(8, 2), (8, 1), (4, 4), (4, 2)])
+def test_prefill_attention_query_tiled(ops, nq, nkv):
+    """Several sequences of different lengths in one batch of prompt rows, second chunk semantics
+    included (rows whose context starts beyond 0 because earlier tokens are already cached)."""
+    D, bs = 128, 16
+    lens, starts = [70, 5, 33], [0, 40, 16]            # rows per sequence, tokens already in the cache
+    nblocks = 40
+    kc, vc = rnd(nblocks * bs, nkv, D, seed=41), rnd(nblocks * bs, nkv, D, seed=42)
+    bt = torch.randperm(nblocks, generator=torch.Generator().manual_seed(3))[:27].view(3, 9).to(torch.int32)
+    seqof = torch.tensor(sum(([s] * n for s, n in enumerate(lens)), []), dtype=torch.int32)
+    ctx = torch.tensor(sum(([starts[s] + i + 1 for i in range(n)] for s, n in enumerate(lens)), []), dtype=torch.int32)
+    T = int(seqof.numel())
+    q = rnd(T, nq, D, seed=43)
+    tiles = ops.prefill_tiles(seqof, nq // nkv)
+    assert int(tiles[:, 1].sum()) == T and int(tiles[:, 1].max()) <= 64 // (nq // nkv)
+    out = torch.zeros_like(q)
+    ops.prefill_attention(q, kc, vc, bt.to(DEV), ctx.to(DEV), seqof.to(DEV), tiles.to(DEV), out, 0.09, bs)
+    torch.cuda.synchronize()
+    want = torch.zeros_like(out)
+    ops.paged_attention(q, kc, vc, bt.to(DEV), ctx.to(DEV), want, 0.09, bs, seq_of_query=seqof.to(DEV))   # one CTA per row
+    r0 = 0
+    for s, n in enumerate(lens):
+        rows = torch.cat([torch.arange(bs) + int(b) * bs for b in bt[s]])[: starts[s] + n].to(DEV)
+        ref_o = ref.attention(q[r0:r0 + n], kc[rows], vc[rows], 0.09, causal_offset=starts[s])
+        assert (out[r0:r0 + n].float() - ref_o).abs().max().item() < 2e-2
+        r0 += n
+    assert (out.float() - want.float()).abs().max().item() < 2e-2
