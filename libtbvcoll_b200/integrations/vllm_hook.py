@@ -86,6 +86,10 @@ def _make_patched(orig: Callable) -> Callable:
     def patched(self, input_: torch.Tensor) -> torch.Tensor:
         if self.world_size == 1:
             return input_
+        if torch.compiler.is_compiling():
+            # Under torch.compile vLLM routes through the opaque custom op torch.ops.vllm.all_reduce,
+            # which lands in _all_reduce_out_place (wrapped below); nothing here may be traced.
+            return orig(self, input_)
         t0 = time.perf_counter()
         out = _try_tbv(self, input_)
         stats["calls"] += 1
