@@ -862,6 +862,7 @@ int tbv_comm_destroy(tbv_comm* c) {
 
 int tbv_comm_allreduce(tbv_comm* c, const void* in, void* out, size_t nbytes, int dtype, void* stream) {
   if (!c) return TBV_FAIL;
+  if (!in && nbytes) return TBV_FALLBACK;  // not a materialised tensor (e.g. a tracing placeholder): never launch on it
   if (!out) out = const_cast<void*>(in);
   if (c->cpu) {
     const double t0 = now_us();

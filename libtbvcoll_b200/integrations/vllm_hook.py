@@ -62,6 +62,11 @@ def _is_tp_group(self) -> bool:
 
 
 def _try_tbv(self, input_: torch.Tensor) -> Optional[torch.Tensor]:
+    # Only real, materialised CUDA tensors may reach the native call.  vLLM's compilation passes trace
+    # all_reduce patterns with FakeTensor / proxy tensors (tensor subclasses whose data_ptr is not a
+    # device address); handing such a pointer to a kernel is an illegal memory access.
+    if type(input_) is not torch.Tensor or torch.compiler.is_compiling():
+        return None
     if not _is_tp_group(self):
         return None
     if _state["raw"] is None:
@@ -72,6 +77,8 @@ def _try_tbv(self, input_: torch.Tensor) -> Optional[torch.Tensor]:
         return None
     if nb == 0:
         return input_
+    if input_.data_ptr() == 0:
+        return None
     out = torch.empty_like(input_)
     st = torch.cuda.current_stream().cuda_stream             # never cached: vLLM switches streams
     rc = _state["raw"](ctypes.c_void_p(input_.data_ptr()), ctypes.c_void_p(out.data_ptr()), nb, dt, ctypes.c_void_p(st))

@@ -153,8 +153,8 @@ class Comm:
 
     # -- collectives -------------------------------------------------------------------
     def _check(self, t: torch.Tensor, out: Optional[torch.Tensor]) -> Optional[int]:
-        if not t.is_contiguous() or (self.device >= 0) != t.is_cuda:
-            return None
+        if type(t) is not torch.Tensor or not t.is_contiguous() or (self.device >= 0) != t.is_cuda:
+            return None   # tensor subclasses (fake / proxy tensors of a tracer) have no device address
         if out is not None and (not out.is_contiguous() or out.dtype is not t.dtype or out.device != t.device):
             return None
         return _DT.get(t.dtype)
@@ -452,8 +452,8 @@ def comm() -> Comm:
 
 def all_reduce(t: torch.Tensor, out: Optional[torch.Tensor] = None) -> bool:
     """SUM over ranks; in place when ``out`` is None.  False = unsupported here, fall back."""
-    if not _ready or not t.is_contiguous() or (t.is_cuda != (_device >= 0)):
-        return False
+    if not _ready or type(t) is not torch.Tensor or not t.is_contiguous() or (t.is_cuda != (_device >= 0)):
+        return False    # tensor subclasses (fake / proxy tensors of a tracer) have no device address
     if out is not None and (not out.is_contiguous() or out.dtype is not t.dtype or out.numel() != t.numel()):
         return False
     dt = _DT.get(t.dtype)

@@ -36,7 +36,16 @@ def test_hook_falls_back_and_counts():
         assert torch.equal(tp.all_reduce(x), x + 100)                          # CPU tensor -> fallback
         assert torch.equal(tp._all_reduce_out_place(x), x + 200)               # the compiled-graph door is wrapped too
         assert torch.equal(tp.all_reduce(torch.ones(4, dtype=torch.int32)), torch.ones(4, dtype=torch.int32) + 100)
-        assert vllm_hook.stats["calls"] == 3 and vllm_hook.stats["fallbacks"] == 3
+        # tracing placeholders (FakeTensor): must never reach the native call, whatever the library says
+        from torch._subclasses.fake_tensor import FakeTensorMode
+        called = []
+        vllm_hook._state["raw"] = lambda *a: called.append(a) or 0
+        with FakeTensorMode():
+            fake = torch.empty(8, dtype=torch.bfloat16)
+            tp.all_reduce(fake)
+        assert called == []
+        vllm_hook._state["raw"] = (lambda *a: -2)
+        assert vllm_hook.stats["calls"] == 4 and vllm_hook.stats["fallbacks"] == 4
         assert "fallbacks" in vllm_hook.summary()
     finally:
         vllm_hook.uninstall()
