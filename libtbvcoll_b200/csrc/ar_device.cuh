@@ -46,6 +46,8 @@ struct TraceRec {
 struct DevMirror {
   unsigned long long bc[8];  // breadcrumbs: 0 enter, 1 pushed, 2 wait-pass, 3 done (seq values)
   unsigned long long tag_bad;
+  unsigned long long peer_wait_ns[TBV_MAXRANK];  // channel 0: time spent waiting for each source rank's flag
+  unsigned long long peer_n[TBV_MAXRANK];
   TraceRec ring[kTraceN];
 };
 
@@ -265,8 +267,13 @@ __device__ __forceinline__ void publish(const RankCtx& c, const CallInfo& ci, in
 __device__ __forceinline__ void wait_all(const RankCtx& c, const CallInfo& ci, int phase, int chan,
                                          unsigned where) {
   if (threadIdx.x < unsigned(c.world) && int(threadIdx.x) != c.rank) {
+    const unsigned long long t0 = chan == 0 ? globaltimer() : 0;
     wait_flag(c, c.flags[c.rank] + flag_index(c, ci.slot, phase, threadIdx.x, chan), ci.want,
               where, threadIdx.x, chan, ci.seq);
+    if (chan == 0) {  // arrival skew per peer, for the `rails` dump (one writer per entry: no atomics needed)
+      c.dm->peer_wait_ns[threadIdx.x] += globaltimer() - t0;
+      c.dm->peer_n[threadIdx.x] += 1;
+    }
   }
   __syncthreads();
 }

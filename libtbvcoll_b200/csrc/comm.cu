@@ -974,6 +974,16 @@ void tbv_comm_stats5(tbv_comm* c, double* pre, double* xfer, double* post, doubl
 void tbv_comm_rails(tbv_comm* c) {
   if (!c) return;
   harvest_trace(c);
+  if (!c->cpu && !c->ranks.empty() && c->ranks[0].dm) {
+    // per-peer flag-wait times accumulated on the device (channel 0); read and reset
+    unsigned long long buf[2 * TBV_MAXRANK] = {0};
+    DevMirror* dm = c->ranks[0].dm;
+    if (cudaMemcpy(buf, dm->peer_wait_ns, sizeof(buf), cudaMemcpyDeviceToHost) == cudaSuccess) {
+      std::lock_guard<std::mutex> g(c->stats.mu);
+      for (int p = 0; p < c->world; p++) { c->stats.peer_wait_us[p] += buf[p] * 1e-3; c->stats.peer_n[p] += buf[TBV_MAXRANK + p]; }
+      cudaMemset(dm->peer_wait_ns, 0, sizeof(buf));
+    }
+  }
   c->stats.dump_rails(c->rank, c->world);
 }
 void tbv_comm_hist(tbv_comm* c) {

@@ -7,7 +7,9 @@
 // bandwidth, and verify=OK/BAD on the first 1024 floats.
 //
 //   tbv_arbench <rank> <world> <cuda-dev> <bytes> <iters> [peer_ip=127.0.0.1] [port=18990]
-//   env: TBV_ALGO, TBV_NCHAN, TBV_NSLOT, TBV_WDOG ... as for the library
+//   env: TBV_ALGO, TBV_NCHAN, TBV_NSLOT, TBV_WDOG ... as for the library;
+//        HOSTBUF=1 puts the user buffers in pinned, device-mapped HOST memory — the control experiment of
+//        step4/allreduce_mr.cpp:81-93,113-116 (how much of the latency is where the payload lives)
 #include <cuda_runtime.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -38,9 +40,21 @@ int main(int argc, char** argv) {
   const size_t n = bytes / 4;
   std::vector<float> h(n, float(rank + 1));
   float *in = nullptr, *out = nullptr;
-  cudaMalloc(&in, bytes);
-  cudaMalloc(&out, bytes);
-  cudaMemcpy(in, h.data(), bytes, cudaMemcpyHostToDevice);
+  const bool hostbuf = getenv("HOSTBUF") && atoi(getenv("HOSTBUF")) != 0;
+  if (hostbuf) {
+    float *hin = nullptr, *hout = nullptr;
+    if (cudaHostAlloc(&hin, bytes, cudaHostAllocMapped) != cudaSuccess || cudaHostAlloc(&hout, bytes, cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(&in, hin, 0) != cudaSuccess || cudaHostGetDevicePointer(&out, hout, 0) != cudaSuccess) {
+      fprintf(stderr, "HOSTBUF: pinned allocation failed\n");
+      return 1;
+    }
+    memcpy(hin, h.data(), bytes);
+    if (rank == 0) printf("# HOSTBUF=1: user buffers in pinned host memory\n");
+  } else {
+    cudaMalloc(&in, bytes);
+    cudaMalloc(&out, bytes);
+    cudaMemcpy(in, h.data(), bytes, cudaMemcpyHostToDevice);
+  }
   cudaStream_t st;
   cudaStreamCreate(&st);
   for (int i = 0; i < 20; i++)

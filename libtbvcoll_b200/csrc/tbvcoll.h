@@ -135,8 +135,8 @@ int tbv_comm_breadcrumbs(tbv_comm* c, int r, unsigned long long out[8]);
 // ---- process-global API with the reference's names ------------------------------
 // devs: "cpu" selects the CPU backend, "cuda:N" / "N" a device; any other string
 // (e.g. the reference's rail list "usb4_rdma0,usb4_rdma5") means "current CUDA
-// device" and its comma count seeds the channel count.  World size is 2 unless
-// TBV_WORLD is set.  Idempotent.
+// device" (rails have no meaning here: channels are CTAs, see TBV_NCHAN).  World size
+// is 2 unless TBV_WORLD is set.  Idempotent.
 int tbv_ar_init(int rank, const char* devs, const char* peer_ip, int port, size_t cap);
 int tbv_ar_init_n(int rank, int world, int device, const char* peer_ip, int port, size_t cap);
 int tbv_ar_allreduce(const void* in, void* out, size_t nbytes, int dtype, void* stream);
