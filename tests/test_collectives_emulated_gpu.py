@@ -63,6 +63,8 @@ def test_stress_back_to_back_no_sync_4_slots(world, algo):
         assert bad == 0
         pre, xfer, post, enq, drain, n_calls = c.stats5()
         assert n_calls == iters and xfer >= 0
+        c.rails()                                            # per-peer arrival waits: read from the device and reset
+        c.hist()
     finally:
         c.destroy()
 
