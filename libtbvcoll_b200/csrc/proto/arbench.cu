@@ -88,6 +88,7 @@ int main(int argc, char** argv) {
   bool ok = true;
   for (size_t i = 0; i < (n < 1024 ? n : 1024); i++) ok &= (h[i] > want - 0.01f && h[i] < want + 0.01f);
   printf("rank %d verify=%s (expect %.1f, got %.3f) err=%d\n", rank, ok ? "OK" : "BAD", want, h[0], tbv_comm_err(c));
+  if (getenv("RAILS") && atoi(getenv("RAILS")) != 0) { tbv_comm_rails(c); tbv_comm_hist(c); }
   tbv_comm_destroy(c);
   return ok ? 0 : 1;
 }
