@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -39,7 +40,9 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
   extern __shared__ uint8_t smem_raw[];
   __shared__ gemm::Smem s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * gemm::kBM, n0 = blockIdx.y * p.bn;
+  // Launch order follows blockIdx.x.  With many token tiles the CTAs that share one 128-row weight tile
+  // must run together, so that the weights stream from HBM once and the activations stay in L2.
+  const int m0 = (p.raster ? blockIdx.y : blockIdx.x) * gemm::kBM, n0 = (p.raster ? blockIdx.x : blockIdx.y) * p.bn;
   const int S = p.splits;
   const int split = S > 1 ? int(cluster_ctarank()) : 0;
   const int kb_per = (p.kb_total + S - 1) / S;
@@ -272,6 +275,12 @@ int tbv_op_gemm(const void* w, const void* x, void* y, const void* bias, int M, 
                 int splits_hint, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || (ldy % 8) || (reinterpret_cast<uintptr_t>(y) & 15u)) return -2;
   if (epi == kEpiSiluMul && (M % 2)) return -2;
+  // Hundreds of tokens: the persistent kernel with tokens on the UMMA M axis.  TBV_GEMM_PERSIST: 0 = never,
+  // 1 (default) = where its tile count fills the SMs well, 2 = wherever the shape allows (tests).
+  const char* pe = getenv("TBV_GEMM_PERSIST");
+  const int persist = pe ? atoi(pe) : 1;
+  if (persist > 0 && splits_hint <= 0 && tbvops::gemm_tok_eligible(M, N, K, ldy, epi, persist > 1))
+    return tbvops::gemm_tok_launch(w, x, y, bias, M, N, K, ldx, ldy, epi, stream);
   int bn, splits, stages;
   tbvops::gemm_config(M, N, K, splits_hint, &bn, &splits, &stages);
   CUtensorMap tmA, tmB;
@@ -295,7 +304,9 @@ int tbv_op_gemm(const void* w, const void* x, void* y, const void* bias, int M, 
     }
     g_attr_done = true;
   }
-  const dim3 grid((M + 127) / 128, (N + bn - 1) / bn, splits);
+  const int mt = (M + 127) / 128, nt = (N + bn - 1) / bn;
+  p.raster = nt > 1 ? 1 : 0;
+  const dim3 grid(p.raster ? nt : mt, p.raster ? mt : nt, splits);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = epi == kEpiSiluMul ? pdl::launch(k_gemm<kEpiSiluMul>, grid, dim3(gemm::kThreads), smem, st, splits, tmA, tmB, p)
                                      : pdl::launch(k_gemm<kEpiStore>, grid, dim3(gemm::kThreads), smem, st, splits, tmA, tmB, p);

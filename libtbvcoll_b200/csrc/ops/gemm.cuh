@@ -30,6 +30,7 @@ struct Params {
   int splits;          // cluster size along K: 1, 2, 4 or 8
   int stages;
   int kb_total;        // ceil(K / 64)
+  int raster;          // 0: blockIdx.x = feature tile, .y = token tile; 1: swapped (token tiles launch first)
   const __nv_bfloat16* bias;  // [M] or null
   __nv_bfloat16* y;
   unsigned long long limit_ns;  // bound on every barrier wait

@@ -39,7 +39,7 @@ k_gemm_qkv_rope(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   __shared__ gemm::Smem s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.x, m0 = head * gemm::kBM, n0 = blockIdx.y * p.bn;
+  const int head = p.raster ? blockIdx.y : blockIdx.x, m0 = head * gemm::kBM, n0 = (p.raster ? blockIdx.x : blockIdx.y) * p.bn;
   const int S = p.splits;
   const int split = S > 1 ? int(cluster_ctarank()) : 0;
   const int kb_per = (p.kb_total + S - 1) / S;
@@ -184,7 +184,9 @@ extern "C" int tbv_op_gemm_qkv_rope(const void* w, const void* x, void* qkv, con
     g_attr = true;
   }
   const size_t smem = size_t(stages) * (gemm::kATileBytes + bn * 128) + 1024;
-  cudaError_t e = pdl::launch(k_gemm_qkv_rope, dim3(M / 128, (N + bn - 1) / bn, splits), dim3(gemm::kThreads), smem,
+  const int mt = M / 128, nt = (N + bn - 1) / bn;
+  p.raster = nt > 1 ? 1 : 0;   // token tiles of one head launch together: its weights stream from HBM once
+  cudaError_t e = pdl::launch(k_gemm_qkv_rope, dim3(p.raster ? nt : mt, p.raster ? mt : nt, splits), dim3(gemm::kThreads), smem,
                               static_cast<cudaStream_t>(stream), splits, tmA, tmB, p, ra);
   if (e != cudaSuccess) {
     fprintf(stderr, "[tbvops] qkv+rope gemm launch failed: %s\n", cudaGetErrorString(e));

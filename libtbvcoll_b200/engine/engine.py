@@ -22,6 +22,7 @@ import os
 import time
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -87,32 +88,41 @@ class Engine:
                 raise ValueError("prompt + new tokens exceed max_seq_len")
             self.bm.reserve(b, len(p) + reserve_new)
         self.bm.sync_to_device()
-        rows = [(b, i, t) for b, p in enumerate(prompts) for i, t in enumerate(p)]
+        # flat row arrays over all prompts (numpy: a 4096-row prefill must not spend milliseconds in Python loops)
+        lens = np.fromiter((len(p) for p in prompts), dtype=np.int64, count=B)
+        total = int(lens.sum())
+        seq_all = np.repeat(np.arange(B, dtype=np.int64), lens)
+        starts = np.cumsum(lens) - lens
+        pos_all = np.arange(total, dtype=np.int64) - np.repeat(starts, lens)
+        ids_all = np.concatenate([np.asarray(p, dtype=np.int64) for p in prompts]) if total else np.zeros(0, dtype=np.int64)
+        tables = self.bm.tables_host.numpy()
+        bsz = self.bm.block_size
+        slots_all = tables[seq_all, pos_all // bsz].astype(np.int64) * bsz + pos_all % bsz
+        is_last = pos_all == (lens[seq_all] - 1)
         first = [0] * B
         dev = self.device
-        for c0 in range(0, len(rows), self.prefill_chunk):
-            chunk = rows[c0:c0 + self.prefill_chunk]
-            T = len(chunk)
-            ids = torch.tensor([t for _, _, t in chunk], dtype=torch.int64)
-            pos = torch.tensor([i for _, i, _ in chunk], dtype=torch.int32)
-            seqof = torch.tensor([b for b, _, _ in chunk], dtype=torch.int32)
-            slots = torch.tensor([self.bm.slot(b, i) for b, i, _ in chunk], dtype=torch.int64)
-            last_rows = [(r, b) for r, (b, i, _) in enumerate(chunk) if i == len(prompts[b]) - 1]
-            n_log = len(last_rows)
+        for c0 in range(0, total, self.prefill_chunk):
+            c1 = min(total, c0 + self.prefill_chunk)
+            T = c1 - c0
+            pos = torch.from_numpy(pos_all[c0:c1].astype(np.int32))
+            seqof = torch.from_numpy(seq_all[c0:c1].astype(np.int32))
+            last_r = np.nonzero(is_last[c0:c1])[0]
+            n_log = int(last_r.size)
             out = torch.zeros(max(n_log, 1), dtype=torch.int64, device=dev)
-            logit_rows = torch.tensor([r for r, _ in last_rows] or [0], dtype=torch.int64).to(dev)
+            logit_rows = torch.from_numpy(last_r if n_log else np.zeros(1, dtype=np.int64)).to(dev)
             tiles = ops.prefill_tiles(seqof, self.model.nq // self.model.nkv).to(dev) if self.tiled_prefill_attention else None
+            ids_d, slots_d = torch.from_numpy(ids_all[c0:c1]).to(dev), torch.from_numpy(slots_all[c0:c1]).to(dev)
+            pos_d, ctx_d, seq_d = pos.to(dev), (pos + 1).to(dev), seqof.to(dev)
             if self.sp_prefill and self.model.sp_ok(T):
-                self.model.forward_sp(T, ids.to(dev), pos.to(dev), slots.to(dev), self.bm.tables, (pos + 1).to(dev), seqof.to(dev),
-                                      logit_rows, max(n_log, 1), out, prefill_tiles=tiles)
+                self.model.forward_sp(T, ids_d, pos_d, slots_d, self.bm.tables, ctx_d, seq_d, logit_rows, max(n_log, 1), out, prefill_tiles=tiles)
                 self.sp_chunks += 1
             else:
-                self.model.forward(T, ids.to(dev), pos.to(dev), slots.to(dev), self.bm.tables, (pos + 1).to(dev), seqof.to(dev),
-                                   logit_rows, max(n_log, 1), out, attn_splits=1, prefill_tiles=tiles)
+                self.model.forward(T, ids_d, pos_d, slots_d, self.bm.tables, ctx_d, seq_d, logit_rows, max(n_log, 1), out, attn_splits=1,
+                                   prefill_tiles=tiles)
             if n_log:
                 toks = out[:n_log].tolist()
-                for (r, b), t in zip(last_rows, toks):
-                    first[b] = t
+                for r, t in zip(last_r.tolist(), toks):
+                    first[int(seq_all[c0 + r])] = t
         return first
 
     # ---- decode -------------------------------------------------------------------------------

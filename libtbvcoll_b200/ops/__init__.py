@@ -274,16 +274,20 @@ def prefill_tiles(seq_of_row, group: int) -> torch.Tensor:
     int32 [ntiles, 2] (first row, count) list ``prefill_attention`` takes.  ``seq_of_row``: host
     sequence (list / CPU tensor) giving the sequence of every query row, rows grouped by sequence
     in position order."""
+    import numpy as np
     qt = max(1, 64 // group)
-    seqs = seq_of_row.tolist() if hasattr(seq_of_row, "tolist") else list(seq_of_row)
-    tiles, i, n = [], 0, len(seqs)
-    while i < n:
-        j = i
-        while j < n and j - i < qt and seqs[j] == seqs[i]:
-            j += 1
-        tiles.append((i, j - i))
-        i = j
-    return torch.tensor(tiles, dtype=torch.int32)
+    seqs = np.asarray(seq_of_row.numpy() if hasattr(seq_of_row, "numpy") else list(seq_of_row), dtype=np.int64)
+    n = int(seqs.size)
+    if n == 0:
+        return torch.zeros(0, 2, dtype=torch.int32)
+    run_start = np.concatenate(([0], np.nonzero(seqs[1:] != seqs[:-1])[0] + 1))      # first row of every run of equal sequence ids
+    run_len = np.diff(np.concatenate((run_start, [n])))
+    per_run = (run_len + qt - 1) // qt                                              # tiles per run
+    run_of_tile = np.repeat(np.arange(run_start.size), per_run)
+    k = np.arange(int(per_run.sum())) - np.repeat(np.cumsum(per_run) - per_run, per_run)   # tile index inside its run
+    first = run_start[run_of_tile] + k * qt
+    count = np.minimum(qt, run_len[run_of_tile] - k * qt)
+    return torch.from_numpy(np.stack([first, count], axis=1).astype(np.int32))
 
 
 def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor, ctx_lens: torch.Tensor,
