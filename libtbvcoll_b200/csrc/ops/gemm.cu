@@ -79,11 +79,15 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
 #pragma unroll
         for (int j = 0; j < 16; j++) stage_f[(c + j) * 128 + ml] = __uint_as_float(r[j]);
       } else if (EPI == kEpiSiluMul) {
+        // Even lanes hold gate rows, odd lanes the matching up rows.  Per pair of token columns the two lanes
+        // swap one value each, so that the even lane finishes column j and the odd lane column j + 1: every
+        // lane does useful SiLU work and one shuffle serves two outputs.
 #pragma unroll
-        for (int j = 0; j < 16; j++) {
-          float v = __uint_as_float(r[j]) + bias;
-          float o = __shfl_xor_sync(0xffffffffu, v, 1);
-          if ((lane & 1) == 0) stage_h[(c + j) * 64 + (ml >> 1)] = __float2bfloat16_rn(silu_mul_bf16(v, o));
+        for (int j = 0; j < 16; j += 2) {
+          const float v0 = __uint_as_float(r[j]) + bias, v1 = __uint_as_float(r[j + 1]) + bias;
+          const float recv = __shfl_xor_sync(0xffffffffu, (lane & 1) ? v0 : v1, 1);
+          const float o = (lane & 1) ? silu_mul_bf16(recv, v1) : silu_mul_bf16(v0, recv);
+          stage_h[(c + j + (lane & 1)) * 64 + (ml >> 1)] = __float2bfloat16_rn(o);
         }
       } else {
 #pragma unroll

@@ -33,6 +33,22 @@ from ..utils.weights import RandomSource, shard_for_rank
 from .kv_cache import BlockManager
 
 
+def prefill_rows(prompts: Sequence[Sequence[int]], tables: np.ndarray, block_size: int):
+    """Flat per-row arrays over all prompts, rows grouped by sequence in position order:
+    (total rows, sequence of row, position, token id, KV-cache slot, is-last-row-of-its-prompt).
+    numpy throughout: a 4096-row prefill must not spend milliseconds in Python loops."""
+    B = len(prompts)
+    lens = np.fromiter((len(p) for p in prompts), dtype=np.int64, count=B)
+    total = int(lens.sum())
+    seq_all = np.repeat(np.arange(B, dtype=np.int64), lens)
+    starts = np.cumsum(lens) - lens
+    pos_all = np.arange(total, dtype=np.int64) - np.repeat(starts, lens)
+    ids_all = np.concatenate([np.asarray(p, dtype=np.int64) for p in prompts]) if total else np.zeros(0, dtype=np.int64)
+    slots_all = tables[seq_all, pos_all // block_size].astype(np.int64) * block_size + pos_all % block_size
+    is_last = pos_all == (lens[seq_all] - 1)
+    return total, seq_all, pos_all, ids_all, slots_all, is_last
+
+
 class Engine:
     def __init__(self, cfg: ModelConfig, tp: Optional[TPGroup] = None, device="cuda:0", weights: Optional[Dict[str, torch.Tensor]] = None,
                  source=None, seed: int = 0, max_batch: int = 8, max_seq_len: int = 1024, block_size: int = 16,
@@ -88,17 +104,7 @@ class Engine:
                 raise ValueError("prompt + new tokens exceed max_seq_len")
             self.bm.reserve(b, len(p) + reserve_new)
         self.bm.sync_to_device()
-        # flat row arrays over all prompts (numpy: a 4096-row prefill must not spend milliseconds in Python loops)
-        lens = np.fromiter((len(p) for p in prompts), dtype=np.int64, count=B)
-        total = int(lens.sum())
-        seq_all = np.repeat(np.arange(B, dtype=np.int64), lens)
-        starts = np.cumsum(lens) - lens
-        pos_all = np.arange(total, dtype=np.int64) - np.repeat(starts, lens)
-        ids_all = np.concatenate([np.asarray(p, dtype=np.int64) for p in prompts]) if total else np.zeros(0, dtype=np.int64)
-        tables = self.bm.tables_host.numpy()
-        bsz = self.bm.block_size
-        slots_all = tables[seq_all, pos_all // bsz].astype(np.int64) * bsz + pos_all % bsz
-        is_last = pos_all == (lens[seq_all] - 1)
+        total, seq_all, pos_all, ids_all, slots_all, is_last = prefill_rows(prompts, self.bm.tables_host.numpy(), self.bm.block_size)
         first = [0] * B
         dev = self.device
         for c0 in range(0, total, self.prefill_chunk):
