@@ -36,7 +36,13 @@ class TPGroup:
         self.fallbacks += 1
         if self.fallback_group is None and not (torch.distributed.is_available() and torch.distributed.is_initialized()):
             raise RuntimeError("tbvcoll declined the call and no torch.distributed fallback is initialised")
-        torch.distributed.all_reduce(x, group=self.fallback_group)
+        if x.is_contiguous():
+            torch.distributed.all_reduce(x, group=self.fallback_group)
+        else:
+            # torch.distributed wants dense tensors (NCCL raises, gloo reduces the wrong elements)
+            dense = x.contiguous()
+            torch.distributed.all_reduce(dense, group=self.fallback_group)
+            x.copy_(dense)
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         """In place SUM."""

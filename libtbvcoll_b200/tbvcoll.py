@@ -21,6 +21,7 @@ worlds on one GPU for tests).
 from __future__ import annotations
 
 import atexit
+import collections
 import ctypes
 import os
 from typing import Optional, Sequence
@@ -141,6 +142,10 @@ class Comm:
         self.world = l.tbv_comm_world(self._h)
         self.cap = l.tbv_comm_cap(self._h)
         self.device = device
+        # CPU backend: the progress thread reads the caller's buffers after the call has returned.  At most
+        # TBV_MAXSLOT (32) calls are ever queued, so holding the last 40 tensor pairs keeps every buffer of a
+        # queued call alive even when the caller passed a temporary.  (On CUDA, stream order does this job.)
+        self._keep = collections.deque(maxlen=40) if device < 0 else None
 
     @classmethod
     def local(cls, world: int, device: int = 0, cap_bytes: int = 8 << 20) -> "Comm":
@@ -168,6 +173,8 @@ class Comm:
             return True
         if nb > self.cap:
             return False
+        if self._keep is not None:
+            self._keep.append((t, out))
         rc = self._l.tbv_comm_allreduce(self._h, c_vp(t.data_ptr()), c_vp(out.data_ptr()) if out is not None else None,
                                         nb, dt, _stream_of(t))
         if rc == -2:
@@ -316,6 +323,8 @@ class Comm:
         if dt is None or t.numel() != out.numel() * self.world:
             return False
         nb = out.numel() * out.element_size()
+        if self._keep is not None:
+            self._keep.append((t, out))
         rc = self._l.tbv_comm_reduce_scatter(self._h, c_vp(t.data_ptr()), c_vp(out.data_ptr()), nb, dt, _stream_of(t))
         if rc == -2:
             return False
@@ -325,13 +334,16 @@ class Comm:
 
     def all_gather(self, t: torch.Tensor, out: torch.Tensor) -> bool:
         """out[r] = rank r's t."""
-        if self._check(t, out) is None and t.dtype not in _DT:
-            # any dtype can be gathered: bytes are copied
-            if not t.is_contiguous() or not out.is_contiguous():
-                return False
+        # any dtype can be gathered (bytes are copied), but only real, contiguous tensors on the communicator's side
+        if type(t) is not torch.Tensor or type(out) is not torch.Tensor or not t.is_contiguous() or not out.is_contiguous():
+            return False
+        if (self.device >= 0) != t.is_cuda or out.device != t.device or out.dtype is not t.dtype:
+            return False
         if out.numel() * out.element_size() != t.numel() * t.element_size() * self.world:
             return False
         nb = t.numel() * t.element_size()
+        if self._keep is not None:
+            self._keep.append((t, out))
         rc = self._l.tbv_comm_all_gather(self._h, c_vp(t.data_ptr()), c_vp(out.data_ptr()), nb, _stream_of(t))
         if rc == -2:
             return False

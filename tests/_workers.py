@@ -486,3 +486,42 @@ def cpu_torch_baseline_tp(rank, world, port):
         toks = m.generate([[5, 9, 100, 7]], 4)
     dist.destroy_process_group()
     return {"err": (tp_logits - ref).abs().max().item(), "scale": ref.abs().max().item(), "toks": toks, "ars": m.all_reduces}
+
+
+# ---- TPGroup over the CPU backend with a gloo fallback ----------------------------------
+def cpu_tp_group_fallback(rank, world, port, gloo_port):
+    import torch
+    import torch.distributed as dist
+    from libtbvcoll_b200.parallel.tp import TPGroup
+    from libtbvcoll_b200.tbvcoll import Comm
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{gloo_port}", rank=rank, world_size=world)
+    comm = Comm(rank, world, -1, "127.0.0.1", port, cap_bytes=4096)
+    tp = TPGroup(rank, world, comm)
+    try:
+        small = [gen(10 + r, (256,), torch.float32) for r in range(world)]       # 1 KiB: the library takes it
+        big = [gen(20 + r, (4096,), torch.float32) for r in range(world)]        # 16 KiB > cap: declined -> torch.distributed
+        x, y = small[rank].clone(), big[rank].clone()
+        tp.all_reduce(x)
+        tp.all_reduce(y)
+        comm.synchronize()                                                               # the CPU backend completes calls on its progress thread
+        ok_small = torch.equal(x, oracle_sum(small))
+        ok_big = torch.allclose(y, oracle_sum(big), rtol=1e-6, atol=1e-6)
+        strided = gen(30 + rank, (64, 8), torch.float32)[:, ::2]                  # non-contiguous: declined as well
+        want = oracle_sum([gen(30 + r, (64, 8), torch.float32)[:, ::2] for r in range(world)])
+        tp.all_reduce(strided)
+        ok_strided = torch.allclose(strided, want, rtol=1e-6, atol=1e-6)
+        # gather / scatter through the library
+        part = gen(40 + rank, (32,), torch.float32)
+        gathered = torch.empty(32 * world)
+        tp.all_gather(part, gathered)
+        comm.synchronize()
+        ok_ag = torch.equal(gathered, torch.cat([gen(40 + r, (32,), torch.float32) for r in range(world)]))
+        full = [gen(50 + r, (32 * world,), torch.float32) for r in range(world)]
+        mine = torch.empty(32)
+        tp.reduce_scatter(full[rank].clone(), mine)
+        comm.synchronize()
+        ok_rs = torch.equal(mine, oracle_sum(full)[rank * 32:(rank + 1) * 32])
+        return {"ok": [ok_small, ok_big, ok_strided, ok_ag, ok_rs], "calls": tp.calls, "fallbacks": tp.fallbacks, "launches": tp.launches}
+    finally:
+        comm.destroy()
+        dist.destroy_process_group()
