@@ -159,7 +159,7 @@ def run_ours(args, rank, world, local):
     B, L = args.batch, args.prompt_len
     e2e_steps = args.e2e_steps or args.steps
     new_tokens = max(256, args.steps + args.warmup + 2, e2e_steps + 2)
-    chunk = 2048
+    chunk = 2048 if world > 1 else 4096       # prefill rows per forward pass (bounds the collective slot size when world > 1)
     comm = None
     if world > 1:
         port = int(os.environ.get("MASTER_PORT", "29500")) + 101

@@ -280,11 +280,13 @@ int tbv_op_gemm(const void* w, const void* x, void* y, const void* bias, int M, 
   if (M <= 0 || N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || (ldy % 8) || (reinterpret_cast<uintptr_t>(y) & 15u)) return -2;
   if (epi == kEpiSiluMul && (M % 2)) return -2;
   // Hundreds of tokens: the persistent kernel with tokens on the UMMA M axis.  TBV_GEMM_PERSIST: 0 = never,
-  // 1 (default) = where its tile count fills the SMs well, 2 = wherever the shape allows (tests).
+  // 1 (default) = where it is estimated to be faster, 2 / 3 = its 128- / 256-token tile wherever the shape allows.
   const char* pe = getenv("TBV_GEMM_PERSIST");
   const int persist = pe ? atoi(pe) : 1;
-  if (persist > 0 && splits_hint <= 0 && tbvops::gemm_tok_eligible(M, N, K, ldy, epi, persist > 1))
-    return tbvops::gemm_tok_launch(w, x, y, bias, M, N, K, ldx, ldy, epi, stream);
+  if (persist > 0 && splits_hint <= 0) {
+    const int th = tbvops::gemm_tok_choose(M, N, K, ldy, epi, persist);
+    if (th > 0) return tbvops::gemm_tok_launch(w, x, y, bias, M, N, K, ldx, ldy, epi, th, stream);
+  }
   int bn, splits, stages;
   tbvops::gemm_config(M, N, K, splits_hint, &bn, &splits, &stages);
   CUtensorMap tmA, tmB;

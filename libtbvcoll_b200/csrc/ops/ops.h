@@ -9,8 +9,9 @@ int* gemm_err_flag();
 int sm_count();
 void gemm_config(int M, int N, int K, int splits_hint, int* bn_out, int* splits_out, int* stages_out);
 // many-token (prefill) persistent kernel, gemm_persist.cu
-bool gemm_tok_eligible(int M, int N, int K, int ldy, int epi, bool any_fill);
-int gemm_tok_launch(const void* w, const void* x, void* y, const void* bias, int M, int N, int K, int ldx, int ldy, int epi, void* stream);
+int gemm_tok_choose(int M, int N, int K, int ldy, int epi, int mode);
+int gemm_tok_launch(const void* w, const void* x, void* y, const void* bias, int M, int N, int K, int ldx, int ldy, int epi, int th,
+                    void* stream);
 // threads per CTA for the row-normalisation kernels; the fused collective uses the same
 // mapping so that both produce identical bits
 inline int norm_threads(int hidden) {

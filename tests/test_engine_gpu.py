@@ -70,3 +70,29 @@ def test_safetensors_checkpoint_round_trip(tmp_path):
     a = Engine(cfg, device=dev, source=RandomSource(cfg, seed=9, device="cpu"), max_batch=1, max_seq_len=64, prefill_chunk=16).generate(prompts, 5)
     b = Engine(cfg, device=dev, source=SafetensorsSource(str(tmp_path)), max_batch=1, max_seq_len=64, prefill_chunk=16).generate(prompts, 5)
     assert a == b
+
+
+@pytest.mark.parametrize("mode", ["2", "3"])
+def test_long_prefill_through_the_many_token_gemm(monkeypatch, mode):
+    """A 448-row prefill chunk sends every plain and SiLU-mul GEMM through the persistent many-token kernel
+    (TBV_GEMM_PERSIST=2: 128-token tiles, 3: 256-token tiles) inside the engine (strided activations, programmatic dependent launch); the logits
+    must agree with the same prefill on the decode-form kernel."""
+    from libtbvcoll_b200 import ops
+    from libtbvcoll_b200.engine.engine import Engine
+    from libtbvcoll_b200.models.config import get_config
+    cfg = get_config("tiny")
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (400, 48)]
+    eng = Engine(cfg, device=dev, seed=11, max_batch=2, max_seq_len=480, prefill_chunk=448)
+    monkeypatch.setenv("TBV_GEMM_PERSIST", "0")
+    first_a = eng.prefill(prompts, 4)
+    logits_a = eng.model.logits[:2].float().clone()
+    monkeypatch.setenv("TBV_GEMM_PERSIST", mode)
+    first_b = eng.prefill(prompts, 4)
+    logits_b = eng.model.logits[:2].float().clone()
+    torch.cuda.synchronize()
+    assert not ops.gemm_error()
+    err = (logits_a - logits_b).abs().max().item()
+    assert err <= 0.02 * logits_a.abs().max().item() + 0.02, err
+    assert len(first_a) == len(first_b) == 2
