@@ -17,6 +17,7 @@ Two decode loops over the same captured step:
 """
 from __future__ import annotations
 
+import contextlib
 import math
 import os
 import time
@@ -31,6 +32,13 @@ from ..models.llama import LlamaTP
 from ..parallel.tp import TPGroup
 from ..utils.weights import RandomSource, shard_for_rank
 from .kv_cache import BlockManager
+
+
+def _nvtx(name: str):
+    """NVTX range around a phase when TBV_NVTX=1 (the native library marks every collective under the same knob)."""
+    if os.environ.get("TBV_NVTX", "0") == "1" and torch.cuda.is_available():
+        return torch.cuda.nvtx.range(name)
+    return contextlib.nullcontext()
 
 
 def prefill_rows(prompts: Sequence[Sequence[int]], tables: np.ndarray, block_size: int):
@@ -189,8 +197,9 @@ class Engine:
         EOS is ignored unless ``eos_id`` is given (the reference bench sets ignore_eos)."""
         B = len(prompts)
         t0 = time.perf_counter()
-        first = self.prefill(prompts, max_new_tokens)
-        torch.cuda.synchronize(self.device)
+        with _nvtx("tbv.prefill"):
+            first = self.prefill(prompts, max_new_tokens)
+            torch.cuda.synchronize(self.device)
         t1 = time.perf_counter()
         outs = [[t] for t in first]
         lens = [len(p) for p in prompts]      # tokens already in the cache per row
