@@ -649,6 +649,7 @@ static size_t dtype_size(int dtype) { return dtype == TBV_F32 ? 4 : 2; }
 // mode: 0 all-reduce (nbytes = tensor), 1 reduce-scatter (nbytes = output), 2 all-gather (nbytes = input)
 static int gpu_collective(tbv_comm* c, const void* const* ins, void* const* outs, size_t nbytes, int dtype, void* stream,
                           int mode) {
+  NvtxRange nvtx(mode == 0 ? "tbv.allreduce" : (mode == 1 ? "tbv.reduce_scatter" : "tbv.all_gather"), nbytes);
   const double t0 = now_us();
   if (check_err(c)) { LOG("previous collective failed: unrecoverable"); return TBV_FAIL; }
   if (dtype < 0 || dtype > 2) return TBV_FALLBACK;
@@ -716,6 +717,7 @@ static int gpu_collective(tbv_comm* c, const void* const* ins, void* const* outs
 
 static int gpu_ar_rmsnorm(tbv_comm* c, const void* const* xs, const void* const* residuals, const void* gamma,
                           void* const* residual_outs, void* const* ys, int tokens, int hidden, float eps, void* stream) {
+  NvtxRange nvtx("tbv.allreduce_rmsnorm", size_t(tokens) * hidden * 2);
   const double t0 = now_us();
   if (check_err(c)) return TBV_FAIL;
   const size_t nbytes = size_t(tokens) * hidden * 2;

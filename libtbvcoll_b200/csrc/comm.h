@@ -12,6 +12,7 @@
 #include "ar_device.cuh"
 #include "bootstrap.h"
 #include "cpu_backend.h"
+#include "nvtx_range.h"
 #include "stats.h"
 #include "tbvcoll.h"
 

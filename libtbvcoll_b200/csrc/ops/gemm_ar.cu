@@ -265,6 +265,7 @@ int tbv_comm_gemm_allreduce_rmsnorm(tbv_comm* c, const void* w, const void* x, c
                                     void* residual_out, void* y, int tokens, int hidden, int k_local, int ldx, float eps,
                                     void* stream) {
   if (!c || c->local) return TBV_FAIL;
+  tbv::NvtxRange nvtx("tbv.gemm_allreduce_rmsnorm", size_t(tokens) * hidden * 2);
   return launch_fused(c, &w, &x, &residual, gamma, &residual_out, &y, tokens, hidden, k_local, ldx, eps, stream);
 }
 

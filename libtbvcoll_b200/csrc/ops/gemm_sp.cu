@@ -442,6 +442,7 @@ int tbv_comm_gemm_reduce_scatter(tbv_comm* c, const void* w, const void* x, void
                                  void* residual_out, void* y, int tokens, int hidden, int k_local, int ldx, float eps, int mode,
                                  void* stream) {
   if (!c || c->local) return TBV_FAIL;
+  tbv::NvtxRange nvtx("tbv.gemm_reduce_scatter", size_t(tokens) * hidden * 2);
   return launch_gemm_rs(c, &w, &x, &out, &residual, gamma, &residual_out, &y, tokens, hidden, k_local, ldx, eps, mode, stream);
 }
 int tbv_comm_gemm_reduce_scatter_local(tbv_comm* c, const void* const* ws, const void* const* xs, void* const* outs,
@@ -453,6 +454,7 @@ int tbv_comm_gemm_reduce_scatter_local(tbv_comm* c, const void* const* ws, const
 int tbv_comm_allgather_gemm(tbv_comm* c, const void* w, const void* x, void* y, int rows_per_rank, int M, int K, int ldx, int ldy,
                             void* stream) {
   if (!c || c->local) return TBV_FAIL;
+  tbv::NvtxRange nvtx("tbv.allgather_gemm", size_t(rows_per_rank) * K * 2);
   return launch_ag_gemm(c, &w, &x, &y, rows_per_rank, M, K, ldx, ldy, stream);
 }
 int tbv_comm_allgather_gemm_local(tbv_comm* c, const void* const* ws, const void* const* xs, void* const* ys, int rows_per_rank, int M,
