@@ -12,7 +12,14 @@ reports/10_tp_custom_allreduce.md:480).  Arms:
   --impl ours       this repository's engine (sm_100a kernels + tbvcoll collectives)   [default]
   --impl nccl       the path being replaced: stock PyTorch (cuBLAS) + NCCL all-reduce, CUDA-graphed
   --impl reference  the unmodified reference: HIP + Thunderbolt ibverbs, cannot exist on this box
-Rank 0 prints ONE JSON line.
+Rank 0 prints ONE JSON line.  With 2 or more GPUs the line of ``--impl ours`` also carries
+  nccl_same_engine   the SAME engine and kernels with every collective sent to torch.distributed (NCCL at its
+                     default settings) and the plain add+RMSNorm operator — the reference's own experiment
+                     (one engine, the all-reduce swapped: step3b/vllm_tp_bench.py:119-124);
+  p50_allreduce_us   all-reduce latency at decode sizes (8 KB, 64 KB, 256 KB; bf16), this library against NCCL,
+                     device time of calls captured in one CUDA graph, max over ranks, bit-exactness asserted.
+``--shard-of N`` (one GPU): rank 0's shard of a TP=N model with every collective replaced by its local
+arithmetic — no communication, wrong values; it exists to attribute the compute part of a TP=N step.
 """
 from __future__ import annotations
 
@@ -39,11 +46,15 @@ def parse():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end arm (0 = same as --steps)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the line INVALID)")
+    ap.add_argument("--repeats", type=int, default=0, help="timed regions of --steps steps each (0 = enough for about 0.5 s in total, at most 12)")
+    ap.add_argument("--shard-of", type=int, default=0, help="attribution only (marks the line INVALID): one GPU runs one rank's shard of a TP=N model, collectives replaced by local arithmetic")
+    ap.add_argument("--no-extras", action="store_true", help="skip the same-engine NCCL arm and the all-reduce latencies")
     return ap.parse_args()
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of this rank's GPU, sampled every 200 ms."""
+    """nvidia-smi clocks and throttle reasons of this rank's GPU, sampled every 50 ms; started a few
+    periods before the timed region so that the region itself is covered."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -53,8 +64,9 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
+            time.sleep(0.3)
         except OSError:
             self.proc = None
 
@@ -65,7 +77,7 @@ class ClockSampler:
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
+        time.sleep(0.1)
         self.proc.terminate()
         sm, mx, reasons = [], [], set()
         for r in self.rows:
@@ -82,10 +94,8 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    # The one offline install was attempted once:
-    #   pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref <reference>
-    # -> "Directory is not installable. Neither 'setup.py' nor 'pyproject.toml' found."
-    # Its only build recipe is `hipcc --offload-arch=gfx1151 ... -libverbs` (README.md:6-7): no hipcc, no
+    # The one offline pip install of the reference tree was attempted once and refused: "Directory is not
+    # installable. Neither 'setup.py' nor 'pyproject.toml' found."  Its only build recipe is `hipcc --offload-arch=gfx1151 ... -libverbs` (README.md:6-7): no hipcc, no
     # libibverbs, no AMD GPU and no Thunderbolt RDMA device exist on a B200 box.
     here = os.path.dirname(os.path.abspath(__file__))
     if os.path.exists(os.path.join(here, "baseline", "_ref", "libtbvcoll.so")):
@@ -130,20 +140,76 @@ def barrier(world):
     torch.cuda.synchronize()
 
 
-def timed_replays(replay, steps, warmup, world):
-    """W untimed + K timed replays bracketed by barrier + synchronize; device time by CUDA events."""
+def timed_replays(replay, steps, warmup, world, repeats=1):
+    """W untimed replays, then `repeats` timed regions of EXACTLY K replays each, every region bracketed
+    by barrier + synchronize on both sides; device time by CUDA events, max over ranks.  Returns the
+    list of ms per step, one per region."""
     import torch
     for _ in range(warmup):
         replay()
-    barrier(world)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        replay()
-    e1.record()
+    out = []
+    for _ in range(max(1, repeats)):
+        barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            replay()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier(world)
+        out.append(max_over_ranks(e0.elapsed_time(e1), world) / steps)
+    return out
+
+
+def decode_arm(eng, prompts, new_tokens, B, L, args, world, repeats, sampler=None):
+    """Prefill, capture the decode step with the device-side feedback kernel, time it."""
+    import torch
+    first = eng.prefill(prompts, new_tokens)
     torch.cuda.synchronize()
-    barrier(world)
-    return max_over_ranks(e0.elapsed_time(e1), world) / steps
+    t_pf = time.perf_counter()
+    first = eng.prefill(prompts, new_tokens)
+    torch.cuda.synchronize()
+    prefill_ms = max_over_ranks((time.perf_counter() - t_pf) * 1e3, world)
+    splits = eng.attn_splits_for(B, L + new_tokens)
+    eng._load_decode_inputs(B, first, [L] * B)
+    eng.step_counter.zero_()
+    graph = eng.capture(B, splits, True)
+    torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.start()
+    ms_all = timed_replays(graph.replay, args.steps, args.warmup, world, repeats)
+    clocks = sampler.stop() if sampler is not None else None
+    return ms_all, prefill_ms, splits, clocks
+
+
+def allreduce_latencies(comm, world):
+    """p50 device latency (us) of one all-reduce at decode sizes, this library (auto) and NCCL: 20 calls
+    captured in one CUDA graph, median over 15 replays, max over ranks; this library's result is
+    compared bit for bit with the fixed-order fp32 oracle first."""
+    import torch
+    import torch.distributed as dist
+    from libtbvcoll_b200.bench_allreduce import graph_us
+    rank = dist.get_rank()
+    out = {}
+    for nbytes in (8192, 65536, 262144):
+        n = nbytes // 2
+        xs = [torch.randn(n, generator=torch.Generator().manual_seed(4000 + r)).to(torch.bfloat16).cuda() for r in range(world)]
+        acc = xs[0].float()
+        for t in xs[1:]:
+            acc = acc + t.float()
+        want, x = acc.to(torch.bfloat16), xs[rank]
+        y = torch.empty_like(x)
+        if not comm.all_reduce(x, y):
+            continue
+        torch.cuda.synchronize()
+        exact = bool(torch.equal(y, want))
+        ours = graph_us(lambda: comm.all_reduce(x, y), 20, world)
+        z = x.clone()
+        nccl = graph_us(lambda: dist.all_reduce(z), 20, world)
+        out[str(nbytes)] = {"ours": round(ours, 2), "nccl": round(nccl, 2), "bit_exact_vs_fixed_order_oracle": exact}
+        if not exact:
+            raise SystemExit(f"all-reduce of {nbytes} bytes is not bit-exact")
+    return out
 
 
 def run_ours(args, rank, world, local):
@@ -158,37 +224,26 @@ def run_ours(args, rank, world, local):
         cfg.num_layers = args.layers
     B, L = args.batch, args.prompt_len
     e2e_steps = args.e2e_steps or args.steps
-    new_tokens = max(256, args.steps + args.warmup + 2, e2e_steps + 2)
+    repeats = args.repeats or max(1, min(12, -(-250 // max(1, args.steps))))     # about 250 timed steps in total
+    new_tokens = max(256, args.steps * repeats + args.warmup + 2, e2e_steps + 2)
     chunk = 2048 if world > 1 else 4096       # prefill rows per forward pass (bounds the collective slot size when world > 1)
     comm = None
     if world > 1:
         port = int(os.environ.get("MASTER_PORT", "29500")) + 101
         comm = Comm(rank, world, local, os.environ.get("MASTER_ADDR", "127.0.0.1"), port, cap_bytes=chunk * cfg.hidden_size * 2)
-    tp = TPGroup(rank, world, comm)
+    if args.shard_of > 1:
+        assert world == 1, "--shard-of runs on one GPU"
+        tp = TPGroup(0, args.shard_of, None, local_stand_in=True)
+    else:
+        tp = TPGroup(rank, world, comm)
     eng = Engine(cfg, tp, device=f"cuda:{local}", seed=0, max_batch=B, max_seq_len=L + new_tokens + 16, prefill_chunk=chunk)
     g = torch.Generator().manual_seed(1234)
     prompts = [torch.randint(0, cfg.vocab_size, (L,), generator=g).tolist() for _ in range(B)]
 
     # ---- device-timed decode steps: the captured step replayed back to back (device loop) ----
     torch.cuda.synchronize()
-    t_pf = time.perf_counter()
-    first = eng.prefill(prompts, new_tokens)
-    torch.cuda.synchronize()
-    prefill_ms = (time.perf_counter() - t_pf) * 1e3          # first call: includes one-time set-up
-    t_pf = time.perf_counter()
-    first = eng.prefill(prompts, new_tokens)
-    torch.cuda.synchronize()
-    prefill_ms = max_over_ranks((time.perf_counter() - t_pf) * 1e3, world)
-    lens = [L] * B
-    splits = eng.attn_splits_for(B, L + new_tokens)
-    eng._load_decode_inputs(B, first, lens)
-    eng.step_counter.zero_()
-    graph = eng.capture(B, splits, True)
-    torch.cuda.synchronize()
-    sampler = ClockSampler(local)
-    sampler.start()
-    ms = timed_replays(graph.replay, args.steps, args.warmup, world)
-    clocks = sampler.stop()
+    ms_all, prefill_ms, splits, clocks = decode_arm(eng, prompts, new_tokens, B, L, args, world, repeats, ClockSampler(local))
+    ms = statistics.median(ms_all)
     value = B / (ms * 1e-3)
 
     # ---- end to end through the public API: Engine.generate, host loop ----
@@ -197,16 +252,20 @@ def run_ours(args, rank, world, local):
     eng.generate(prompts, e2e_steps + 1)
     e2e = B * e2e_steps / max_over_ranks(eng.last_stats["decode_s"], world)
     fallbacks = tp.fallbacks
+    invalid = ("" if not args.layers else f"-INVALID-{args.layers}-layers") + ("" if args.shard_of <= 1 else f"-INVALID-shard-of-tp{args.shard_of}-no-communication")
     out = {
         "metric": "tp_decode_tokens_per_s", "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": round(value / REF_TOK_S_BATCH8, 2), "dtype": "bf16", "data": "synthetic (random token ids, random-init weights)",
         "impl": "ours",
-        "config": {"model": cfg.name + ("" if not args.layers else f"-INVALID-{args.layers}-layers"), "global_batch": B, "seq_len": L,
-                   "decode_context": f"{L}..{L + args.steps + args.warmup}", "parallelism": f"tp{world}",
+        "config": {"model": cfg.name + invalid, "global_batch": B, "seq_len": L,
+                   "decode_context": f"{L}..{L + args.steps * repeats + args.warmup}", "parallelism": f"tp{world}",
                    "l2": "inputs larger than L2: every step streams the rank's full weight shard "
                          f"({cfg.param_count() * 2 / world / 1e9:.1f} GB) from HBM",
-                   "timing": "CUDA events around K graph replays, max over ranks", "attn_splits": splits},
+                   "timing": f"CUDA events around K graph replays, max over ranks; {repeats} such regions back to back "
+                             "(each bracketed by barrier + synchronize), value = median region",
+                   "attn_splits": splits},
+        "timed_regions_ms_per_step": [round(m, 4) for m in ms_all], "ms_per_step_min": round(min(ms_all), 4),
         "clocks": clocks,
         "e2e": {"value": round(e2e, 2), "unit": "tokens/s", "h2d_bytes_per_step": 24 * B, "d2h_bytes_per_step": 8 * B,
                 "steps": e2e_steps, "api": "Engine.generate(prompts, max_new_tokens) host loop: per step H2D of ids/positions/slots/"
@@ -214,10 +273,24 @@ def run_ours(args, rank, world, local):
         "gpu_launches": eng.launches_per_step * args.steps,
         "launches_per_step": eng.launches_per_step,
         "collective_fallbacks_to_nccl": fallbacks,
+        "fused_gemm_allreduce": bool(world > 1 and tp.fuse_gemm),
         "prefill": {"ms": round(prefill_ms, 2), "tokens": B * L, "tokens_per_s": round(B * L / (prefill_ms * 1e-3), 1),
                     "sequence_parallel_chunks": eng.sp_chunks, "note": "wall clock with synchronize, second call, not part of the metric"},
         "baseline_note": "vs_baseline divides by the reference's published 170.9 tok/s (Qwen2.5-7B, vLLM TP=2, 2x gfx1151 laptops)",
     }
+    if world > 1 and not args.no_extras:
+        # the same engine (same weights, same kernels) with the collectives on NCCL at its default settings
+        tp_n = TPGroup(rank, world, None)
+        eng_n = Engine(cfg, tp_n, device=f"cuda:{local}", weights=eng.model.w, max_batch=B, max_seq_len=L + new_tokens + 16, prefill_chunk=chunk)
+        ms_n, _, _, _ = decode_arm(eng_n, prompts, new_tokens, B, L, args, world, min(repeats, 3))
+        m = statistics.median(ms_n)
+        out["nccl_same_engine"] = {"ms_per_step": round(m, 4), "value": round(B / (m * 1e-3), 2), "unit": "tokens/s",
+                                   "launches_per_step": eng_n.launches_per_step, "nccl_calls_per_step": 2 * cfg.num_layers + 2,
+                                   "what": "this engine and its kernels; all-reduce / all-gather by torch.distributed (NCCL defaults, "
+                                           "captured in the same CUDA graph), then the plain add+RMSNorm operator"}
+        out["ours_over_nccl_same_engine"] = round(m / ms, 3)
+        del eng_n
+        out["p50_allreduce_us"] = allreduce_latencies(comm, world)
     if comm is not None:
         comm.destroy()
     return out
@@ -246,12 +319,13 @@ def run_nccl(args, rank, world, local):
         dec.capture()
     sampler = ClockSampler(local)
     sampler.start()
-    ms = timed_replays(dec.replay, args.steps, args.warmup, world)
+    ms = statistics.median(timed_replays(dec.replay, args.steps, args.warmup, world, 3))
     clocks = sampler.stop()
     value = B / (ms * 1e-3)
     return {"metric": "tp_decode_tokens_per_s", "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / REF_TOK_S_BATCH8, 2), "dtype": "bf16", "data": "synthetic", "impl": "nccl+cublas (stock PyTorch)",
+            "vs_baseline": round(value / REF_TOK_S_BATCH8, 2), "dtype": "bf16", "data": "synthetic",
+            "impl": "nccl+cublas (plain PyTorch ops, unoptimised: unfused norm/RoPE, mask-path attention)",
             "config": {"model": cfg.name, "global_batch": B, "seq_len": L, "parallelism": f"tp{world}",
                        "note": "fixed context of prompt_len+1 per step (static shapes under CUDA graph)"},
             "clocks": clocks, "gpu_launches": 0}

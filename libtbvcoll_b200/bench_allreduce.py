@@ -6,7 +6,8 @@ result of this library is checked bit for bit against a fixed-order fp32 oracle 
 timed.  Timing is stream-ordered like the reference's microbenchmark ("stream-ordered" mode of
 step4/allreduce2.cpp:188-200 and step4/test_tbvcoll.py:52-63): calls are issued back to back
 without host synchronisation, device time is taken with CUDA events around groups of calls,
-the p50 over groups is reported, and the maximum over ranks is what counts.
+the p50 over groups is reported, and the maximum over ranks is what counts.  NCCL runs at its
+default settings (NVLink SHARP / NVLS reduction in the switch included where NCCL chooses it).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
         --master-port 29511 -m libtbvcoll_b200.bench_allreduce [--max-tokens 8192] [--json out.json]
@@ -72,6 +73,7 @@ def graph_us(fn, inner, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-tokens", type=int, default=8192)
+    ap.add_argument("--min-tokens", type=int, default=1)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--json", default="")
     ap.add_argument("--algos", default="auto,ll,oneshot,twoshot,nvls")
@@ -85,7 +87,7 @@ def main():
     comm = Comm(rank, world, local, "127.0.0.1", port, cap_bytes=cap)
     algos = [a for a in args.algos.split(",") if a != "nvls" or comm.has_nvls()]
     rows = []
-    tokens = 1
+    tokens = max(1, args.min_tokens)
     while tokens <= args.max_tokens:
         n = tokens * args.hidden
         nbytes = n * 2

@@ -29,7 +29,7 @@ struct DevState {
   unsigned int arrive;      // CTA completion counter of the running kernel
   unsigned int err;         // sticky: first device-side error code
   unsigned int tag_bad;     // seq-stamp mismatches seen (debug mode)
-  unsigned int pad;
+  unsigned int gemm_done;   // fused GEMM + all-reduce: GEMM CTAs of the running call that have pushed their tile
 };
 
 struct TraceRec {
@@ -45,7 +45,9 @@ struct TraceRec {
 // into the host-mapped record below.
 struct DevMirror {
   unsigned long long bc[8];  // breadcrumbs: 0 enter, 1 pushed, 2 wait-pass, 3 done (seq values)
-  unsigned long long tag_bad;
+  unsigned long long tag_bad;      // sequence stamps that did not match after their flag had been seen (TBV_TAG=1)
+  unsigned long long tag_checked;  // sequence stamps compared
+  unsigned long long ts[8];        // %globaltimer stamps of the last fused GEMM + all-reduce call (see tbv_comm_timestamps)
   unsigned long long peer_wait_ns[TBV_MAXRANK];  // channel 0: time spent waiting for each source rank's flag
   unsigned long long peer_n[TBV_MAXRANK];
   TraceRec ring[kTraceN];
@@ -75,6 +77,7 @@ struct RankCtx {
   unsigned int* flags[TBV_MAXRANK];
   char* ll[TBV_MAXRANK];           // ll[p]: rank p's LL packet area (only ever holds LL packets)
   unsigned long long ll_cap;       // bytes per (slot, source-rank) LL region
+  unsigned long long* tags[TBV_MAXRANK];  // tags[p]: rank p's sequence-stamp area, one word per flag, outside the payload regions
   char* mc_data;                   // multicast (NVLS) mapping of the slot memory, or null
   DevState* st;
   DevMirror* dm;
@@ -244,6 +247,7 @@ __device__ __forceinline__ void call_end(const RankCtx& c, const CallInfo& ci, u
     unsigned old = atomicAdd(&c.st->arrive, 1u);
     if (old == nctas - 1) {
       c.st->arrive = 0;
+      c.st->gemm_done = 0;   // the next call's GEMM CTAs push only after this grid has completed
       r->t_done = globaltimer();
       r->seq = ci.seq;
       c.dm->bc[3] = ci.seq;
@@ -252,10 +256,44 @@ __device__ __forceinline__ void call_end(const RankCtx& c, const CallInfo& ci, u
   }
 }
 
+// ---- 16-byte units of a caller's tensor ---------------------------------------------------------
+// Channel ranges and the choice of kernel depend on the byte count only, never on where a
+// rank's tensor happens to sit, so every rank launches the same protocol.  A tensor that is
+// not 16-byte aligned is read and written element by element; slot memory is always aligned.
+template <typename T>
+__device__ __forceinline__ uint4 ld_unit(const T* p, size_t u, bool aligned) {
+  if (aligned) return reinterpret_cast<const uint4*>(p)[u];
+  constexpr int N = 16 / sizeof(T);
+  union { uint4 v; T e[N]; } x;
+#pragma unroll
+  for (int i = 0; i < N; i++) x.e[i] = p[u * N + i];
+  return x.v;
+}
+template <typename T>
+__device__ __forceinline__ void st_unit(T* p, size_t u, const uint4& v, bool aligned) {
+  if (aligned) { reinterpret_cast<uint4*>(p)[u] = v; return; }
+  constexpr int N = 16 / sizeof(T);
+  union { uint4 v; T e[N]; } x;
+  x.v = v;
+#pragma unroll
+  for (int i = 0; i < N; i++) p[u * N + i] = x.e[i];
+}
+enum : int { kInAligned = 1, kOutAligned = 2 };
+
 // publish: all threads' stores are done (caller did __syncthreads); thread 0 fences
-// at system scope once and then stores the flag to every peer.
+// at system scope once and then stores the flag to every peer.  With the sequence-stamp
+// diagnostic on (TBV_TAG=1) the same thread first writes the call's sequence number into
+// the peer's stamp word of this (slot, phase, source, channel): a plain store issued after
+// the payload and before the fence, so a receiver that sees the flag must also see the
+// stamp.  The stamp has a word of its own next to the flags and never overlaps a payload.
+// (The reference carried the stamp behind the payload in a widened slot stride,
+// step4/libtbvcoll.cpp:88-91,296-297, and compared it in k_tagchk, :143-150.)
 __device__ __forceinline__ void publish(const RankCtx& c, const CallInfo& ci, int phase, int chan) {
   if (threadIdx.x == 0) {
+    if (c.debug_tag) {
+      for (int p = 0; p < c.world; p++)
+        if (p != c.rank) *(volatile unsigned long long*)(c.tags[p] + flag_index(c, ci.slot, phase, c.rank, chan)) = ci.seq;
+    }
     fence_sys();
     for (int p = 0; p < c.world; p++) {
       if (p == c.rank) continue;
@@ -268,22 +306,27 @@ __device__ __forceinline__ void wait_all(const RankCtx& c, const CallInfo& ci, i
                                          unsigned where) {
   if (threadIdx.x < unsigned(c.world) && int(threadIdx.x) != c.rank) {
     const unsigned long long t0 = chan == 0 ? globaltimer() : 0;
-    wait_flag(c, c.flags[c.rank] + flag_index(c, ci.slot, phase, threadIdx.x, chan), ci.want,
-              where, threadIdx.x, chan, ci.seq);
+    const bool ok = wait_flag(c, c.flags[c.rank] + flag_index(c, ci.slot, phase, threadIdx.x, chan), ci.want,
+                              where, threadIdx.x, chan, ci.seq);
     if (chan == 0) {  // arrival skew per peer, for the `rails` dump (one writer per entry: no atomics needed)
       c.dm->peer_wait_ns[threadIdx.x] += globaltimer() - t0;
       c.dm->peer_n[threadIdx.x] += 1;
+    }
+    if (c.debug_tag && ok) {
+      const unsigned long long tag = *(volatile unsigned long long*)(c.tags[c.rank] + flag_index(c, ci.slot, phase, threadIdx.x, chan));
+      atomicAdd(&c.dm->tag_checked, 1ull);
+      if (tag != ci.seq) { atomicAdd(&c.st->tag_bad, 1u); atomicAdd(&c.dm->tag_bad, 1ull); }
     }
   }
   __syncthreads();
 }
 
 // ---- one-shot all-reduce ------------------------------------------------------------
-// VEC: 16-byte units (pointers 16-byte aligned, nbytes % 16 == 0); otherwise one
-// element per unit.
+// VEC: 16-byte units (nbytes % 16 == 0); otherwise one element per unit.  io: kInAligned /
+// kOutAligned say whether the caller's tensors can be accessed 16 bytes at a time.
 template <typename T, bool VEC>
 __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* out, size_t nbytes,
-                                int nchan, int chan, unsigned long long* sh_seq) {
+                                int nchan, int chan, int io, unsigned long long* sh_seq) {
   unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   CallInfo ci = call_begin(c, sh_seq);
   const size_t unit_bytes = VEC ? 16 : sizeof(T);
@@ -291,12 +334,13 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   const size_t per = (units + nchan - 1) / nchan;
   const size_t u0 = per * chan;
   const size_t u1 = (u0 + per < units) ? (u0 + per) : units;
+  const bool in_al = io & kInAligned, out_al = io & kOutAligned;
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
 
   // push my range to every peer's [slot][src = me] region
   for (size_t u = u0 + threadIdx.x; u < u1; u += blockDim.x) {
     if (VEC) {
-      uint4 v = reinterpret_cast<const uint4*>(in)[u];
+      uint4 v = ld_unit(in, u, in_al);
       for (int p = 0; p < c.world; p++)
         if (p != c.rank) reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, c.rank))[u] = v;
     } else {
@@ -305,28 +349,12 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
         if (p != c.rank) reinterpret_cast<T*>(slot_region(c, p, ci.slot, c.rank))[u] = v;
     }
   }
-  if (c.debug_tag && chan == 0 && threadIdx.x == 0) {
-    // seq stamp behind the payload (debug): the receiver checks it after the flag
-    for (int p = 0; p < c.world; p++)
-      if (p != c.rank)
-        *reinterpret_cast<unsigned long long*>(slot_region(c, p, ci.slot, c.rank) + c.cap - 8) = ci.seq;
-  }
   __syncthreads();
   publish(c, ci, 0, chan);
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
   wait_all(c, ci, 0, chan, kWherePhase0);
   unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
-  if (chan == 0 && threadIdx.x == 0) {
-    c.dm->bc[2] = ci.seq;
-    if (c.debug_tag) {
-      for (int p = 0; p < c.world; p++) {
-        if (p == c.rank) continue;
-        unsigned long long tag = *reinterpret_cast<volatile unsigned long long*>(
-            slot_region(c, c.rank, ci.slot, p) + c.cap - 8);
-        if (tag != ci.seq) { atomicAdd(&c.st->tag_bad, 1u); c.dm->tag_bad += 1; }
-      }
-    }
-  }
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[2] = ci.seq;
 
   // reduce in rank order, fp32, one rounding
   for (size_t u = u0 + threadIdx.x; u < u1; u += blockDim.x) {
@@ -334,7 +362,7 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
       float acc[Pack<T>::N];
 #pragma unroll
       for (int i = 0; i < Pack<T>::N; i++) acc[i] = 0.f;
-      uint4 mine = reinterpret_cast<const uint4*>(in)[u];
+      uint4 mine = ld_unit(in, u, in_al);
       for (int r = 0; r < c.world; r++) {
         uint4 v = (r == c.rank)
                       ? mine
@@ -344,7 +372,7 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
 #pragma unroll
         for (int i = 0; i < Pack<T>::N; i++) acc[i] = (r == 0) ? f[i] : acc[i] + f[i];
       }
-      reinterpret_cast<uint4*>(out)[u] = Pack<T>::pack(acc);
+      st_unit(out, u, Pack<T>::pack(acc), out_al);
     } else {
       float acc = 0.f;
       for (int r = 0; r < c.world; r++) {
@@ -368,28 +396,6 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
 __device__ __forceinline__ void st_v4(void* p, unsigned a, unsigned b, unsigned c2, unsigned d) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c2), "r"(d) : "memory");
 }
-// Poll one 16-byte LL line (two packets) until both flags equal `want`; bounded like wait_flag.
-__device__ __forceinline__ uint2 ll_wait_load(const RankCtx& c, const void* p, unsigned want, int peer, int chan,
-                                              unsigned long long seq) {
-  uint4 v = ld_volatile_v4(p);
-  unsigned spins = 0;
-  unsigned long long t0 = 0;
-  while (v.y != want || v.w != want) {
-    if (++spins > 4096u) {
-      unsigned long long now = globaltimer();
-      if (t0 == 0) {
-        t0 = now;
-        if (*(volatile unsigned*)&c.st->err != 0u) break;
-      } else if (now - t0 > c.wdog_ns) {
-        report_error(c, kErrTimeout, kWherePhase0, peer, chan, seq);
-        break;
-      }
-      __nanosleep(64);
-    }
-    v = ld_volatile_v4(p);
-  }
-  return make_uint2(v.x, v.z);
-}
 // push one 16-byte input unit `v` as two LL lines (32 bytes) at line index u of every peer's region
 __device__ __forceinline__ void ll_push_unit(const RankCtx& c, int slot, size_t u, const uint4& v, unsigned want) {
   for (int d = 1; d < c.world; d++) {
@@ -399,45 +405,101 @@ __device__ __forceinline__ void ll_push_unit(const RankCtx& c, int slot, size_t 
     st_v4(dst + 16, v.z, want, v.w, want);
   }
 }
-__device__ __forceinline__ uint4 ll_pull_unit(const RankCtx& c, int slot, int src, size_t u, unsigned want, int chan,
-                                              unsigned long long seq) {
-  const char* p = ll_region(c, c.rank, slot, src) + u * 32;
-  const uint2 a = ll_wait_load(c, p, want, src, chan, seq), b = ll_wait_load(c, p + 16, want, src, chan, seq);
-  return make_uint4(a.x, a.y, b.x, b.y);
-}
-
-template <typename T>
-__device__ void ar_oneshot_ll_body(const RankCtx& c, const T* __restrict__ in, T* out, size_t nbytes, int nchan, int chan,
-                                   unsigned long long* sh_seq) {
-  unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
-  const size_t units = nbytes / 16;
-  const size_t per = (units + nchan - 1) / nchan;
-  const size_t u0 = per * chan;
-  const size_t u1 = (u0 + per < units) ? (u0 + per) : units;
-  // the first unit's load is issued before the sequence number is known (they do not depend on each other)
-  const size_t uf = u0 + threadIdx.x;
-  uint4 first = make_uint4(0, 0, 0, 0);
-  if (uf < u1) first = reinterpret_cast<const uint4*>(in)[uf];
-  CallInfo ci = call_begin(c, sh_seq);
-  if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
-  for (size_t u = uf; u < u1; u += blockDim.x) {
-    const uint4 v = (u == uf) ? first : reinterpret_cast<const uint4*>(in)[u];
-    ll_push_unit(c, ci.slot, u, v, ci.want);
-  }
-  unsigned long long t_ready = 0;
-  for (size_t u = uf; u < u1; u += blockDim.x) {
-    const uint4 mine = (u == uf) ? first : reinterpret_cast<const uint4*>(in)[u];
-    float acc[Pack<T>::N];
+// Pull unit u (two LL lines) of every source rank in `mask` from this rank's own LL area.  All
+// the loads are issued before any flag is looked at, so a call pays one memory round trip once
+// the packets have landed instead of one per source; only lines that have not arrived are read
+// again.  Bounded like wait_flag: on expiry the error is recorded (naming the first silent
+// source) and whatever is there is returned.  Every loop is fully unrolled with constant
+// indices so that the lines stay in registers.
+__device__ __forceinline__ void ll_pull_all(const RankCtx& c, int slot, size_t u, unsigned want, unsigned mask, int chan,
+                                            unsigned long long seq, uint4 (&out)[TBV_MAXRANK]) {
+  uint4 lo[TBV_MAXRANK], hi[TBV_MAXRANK];
+  const char* base = c.ll[c.rank] + size_t(slot) * c.world * c.ll_cap + u * 32;
 #pragma unroll
-    for (int i = 0; i < Pack<T>::N; i++) acc[i] = 0.f;
-    for (int r = 0; r < c.world; r++) {
-      const uint4 v = (r == c.rank) ? mine : ll_pull_unit(c, ci.slot, r, u, ci.want, chan, ci.seq);
+  for (int r = 0; r < TBV_MAXRANK; r++)
+    if ((mask >> r) & 1u) {
+      const char* p = base + size_t(r) * c.ll_cap;
+      lo[r] = ld_volatile_v4(p);
+      hi[r] = ld_volatile_v4(p + 16);
+    }
+  unsigned pending = mask, spins = 0;
+  unsigned long long t0 = 0;
+  for (;;) {
+    unsigned still = 0;
+#pragma unroll
+    for (int r = 0; r < TBV_MAXRANK; r++)
+      if (((pending >> r) & 1u) && (lo[r].y != want || lo[r].w != want || hi[r].y != want || hi[r].w != want)) still |= 1u << r;
+    if (!still) break;
+    if (++spins > 4096u) {
+      const unsigned long long now = globaltimer();
+      if (t0 == 0) {
+        t0 = now;
+        if (*(volatile unsigned*)&c.st->err != 0u) break;
+      } else if (now - t0 > c.wdog_ns) {
+        report_error(c, kErrTimeout, kWherePhase0, __ffs(int(still)) - 1, chan, seq);
+        break;
+      }
+      __nanosleep(64);
+    }
+#pragma unroll
+    for (int r = 0; r < TBV_MAXRANK; r++)
+      if ((still >> r) & 1u) {
+        const char* p = base + size_t(r) * c.ll_cap;
+        lo[r] = ld_volatile_v4(p);
+        hi[r] = ld_volatile_v4(p + 16);
+      }
+    pending = still;
+  }
+#pragma unroll
+  for (int r = 0; r < TBV_MAXRANK; r++)
+    if ((mask >> r) & 1u) out[r] = make_uint4(lo[r].x, lo[r].z, hi[r].x, hi[r].z);
+}
+// rank-ordered fp32 sum of one unit: `mine` stands in for this rank unless its bit is set in `mask`
+template <typename T>
+__device__ __forceinline__ void ll_sum_unit(const RankCtx& c, const uint4 (&got)[TBV_MAXRANK], unsigned mask, const uint4& mine,
+                                            float* acc) {
+#pragma unroll
+  for (int r = 0; r < TBV_MAXRANK; r++) {
+    if (r < c.world) {
+      const uint4 v = ((mask >> r) & 1u) ? got[r] : mine;
       float f[Pack<T>::N];
       Pack<T>::unpack(v, f);
 #pragma unroll
       for (int i = 0; i < Pack<T>::N; i++) acc[i] = (r == 0) ? f[i] : acc[i] + f[i];
     }
-    reinterpret_cast<uint4*>(out)[u] = Pack<T>::pack(acc);
+  }
+}
+
+template <typename T>
+__device__ void ar_oneshot_ll_body(const RankCtx& c, const T* __restrict__ in, T* out, size_t nbytes, int nchan, int chan,
+                                   int io, unsigned long long* sh_seq) {
+  unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
+  const size_t units = nbytes / 16;
+  const size_t per = (units + nchan - 1) / nchan;
+  const size_t u0 = per * chan;
+  const size_t u1 = (u0 + per < units) ? (u0 + per) : units;
+  const bool in_al = io & kInAligned, out_al = io & kOutAligned;
+  // the first unit's load is issued before the sequence number is known (they do not depend on each other)
+  const size_t uf = u0 + threadIdx.x;
+  uint4 first = make_uint4(0, 0, 0, 0);
+  if (uf < u1) first = ld_unit(in, uf, in_al);
+  CallInfo ci = call_begin(c, sh_seq);
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
+  for (size_t u = uf; u < u1; u += blockDim.x) {
+    const uint4 v = (u == uf) ? first : ld_unit(in, u, in_al);
+    ll_push_unit(c, ci.slot, u, v, ci.want);
+  }
+  const unsigned peers = ((1u << c.world) - 1u) & ~(1u << c.rank);
+  unsigned long long t_ready = 0;
+  for (size_t u = uf; u < u1; u += blockDim.x) {
+    const uint4 mine = (u == uf) ? first : ld_unit(in, u, in_al);
+    uint4 got[TBV_MAXRANK];
+    ll_pull_all(c, ci.slot, u, ci.want, peers, chan, ci.seq, got);
+    float acc[Pack<T>::N];
+#pragma unroll
+    for (int i = 0; i < Pack<T>::N; i++) acc[i] = 0.f;
+    ll_sum_unit<T>(c, got, peers, mine, acc);
+    st_unit(out, u, Pack<T>::pack(acc), out_al);
   }
   if (threadIdx.x == 0 && chan == 0) { t_ready = globaltimer(); c.dm->bc[2] = ci.seq; }
   call_end(c, ci, nchan, t_enter, t_ready, nbytes, TBV_ALGO_LL);
@@ -457,7 +519,7 @@ __device__ __forceinline__ void multimem_st_v4(void* p, const uint4& v) {
 //       2 = all-gather only (in holds this rank's chunk).
 template <typename T, bool VEC>
 __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* out, size_t nbytes,
-                                int nchan, int chan, int mode, unsigned long long* sh_seq) {
+                                int nchan, int chan, int mode, int io, unsigned long long* sh_seq) {
   unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   CallInfo ci = call_begin(c, sh_seq);
   const size_t unit_bytes = VEC ? 16 : sizeof(T);
@@ -465,6 +527,7 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   const size_t cu = (units + c.world - 1) / c.world;     // units per rank chunk
   const size_t per = (cu + nchan - 1) / nchan;           // units per channel inside a chunk
   const int W = c.world, me = c.rank;
+  const bool in_al = io & kInAligned, out_al = io & kOutAligned;
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
   const int R = W;  // index of the result region inside a slot
   unsigned long long t_ready = 0;
@@ -481,10 +544,18 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
     for (int d = 1; d < W; d++) {
       int p = (me + d) % W;
       size_t len = chunk_len(p), b = sub_begin(len), e = sub_end(len);
-      for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) {
-        if (VEC) reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, me))[i] =
-                     reinterpret_cast<const uint4*>(in)[cu * p + i];
-        else reinterpret_cast<T*>(slot_region(c, p, ci.slot, me))[i] = in[cu * p + i];
+      if (VEC) {
+        // four independent 16-byte loads per thread before the stores: large messages need megabytes in flight
+        uint4* dst = reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, me));
+        for (size_t i = b + threadIdx.x; i < e; i += size_t(4) * blockDim.x) {
+          uint4 v[4];
+#pragma unroll
+          for (int k = 0; k < 4; k++) { const size_t j = i + size_t(k) * blockDim.x; if (j < e) v[k] = ld_unit(in, cu * p + j, in_al); }
+#pragma unroll
+          for (int k = 0; k < 4; k++) { const size_t j = i + size_t(k) * blockDim.x; if (j < e) dst[j] = v[k]; }
+        }
+      } else {
+        for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) reinterpret_cast<T*>(slot_region(c, p, ci.slot, me))[i] = in[cu * p + i];
       }
     }
     __syncthreads();
@@ -501,13 +572,14 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
       if (VEC) {
         uint4 res;
         if (mode == 2) {
-          res = reinterpret_cast<const uint4*>(in)[i];
+          res = ld_unit(in, i, in_al);
         } else {
           float acc[Pack<T>::N];
 #pragma unroll
           for (int k = 0; k < Pack<T>::N; k++) acc[k] = 0.f;
+          const uint4 mine = ld_unit(in, cu * me + i, in_al);
           for (int r = 0; r < W; r++) {
-            uint4 v = (r == me) ? reinterpret_cast<const uint4*>(in)[cu * me + i]
+            uint4 v = (r == me) ? mine
                                 : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, me, ci.slot, r)) + i);
             float f[Pack<T>::N];
             Pack<T>::unpack(v, f);
@@ -517,9 +589,9 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
           res = Pack<T>::pack(acc);
         }
         if (mode == 1) {
-          reinterpret_cast<uint4*>(out)[i] = res;
+          st_unit(out, i, res, out_al);
         } else {
-          reinterpret_cast<uint4*>(out)[cu * me + i] = res;
+          st_unit(out, cu * me + i, res, out_al);
           if (c.mc_data) {
             // one store through the NVSwitch multicast object lands in every rank's result
             // region (the reduction above stays in rank order: results are still exact)
@@ -566,10 +638,18 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
     for (int d = 1; d < W; d++) {
       int p = (me + d) % W;
       size_t len = chunk_len(p), b = sub_begin(len), e = sub_end(len);
-      for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) {
-        if (VEC) reinterpret_cast<uint4*>(out)[cu * p + i] =
-                     ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, me, ci.slot, R)) + cu * p + i);
-        else out[cu * p + i] = *(reinterpret_cast<volatile const T*>(slot_region(c, me, ci.slot, R)) + cu * p + i);
+      if (VEC) {
+        const uint4* src = reinterpret_cast<const uint4*>(slot_region(c, me, ci.slot, R)) + cu * p;
+        for (size_t i = b + threadIdx.x; i < e; i += size_t(4) * blockDim.x) {
+          uint4 v[4];
+#pragma unroll
+          for (int k = 0; k < 4; k++) { const size_t j = i + size_t(k) * blockDim.x; if (j < e) v[k] = ld_volatile_v4(src + j); }
+#pragma unroll
+          for (int k = 0; k < 4; k++) { const size_t j = i + size_t(k) * blockDim.x; if (j < e) st_unit(out, cu * p + j, v[k], out_al); }
+        }
+      } else {
+        for (size_t i = b + threadIdx.x; i < e; i += blockDim.x)
+          out[cu * p + i] = *(reinterpret_cast<volatile const T*>(slot_region(c, me, ci.slot, R)) + cu * p + i);
       }
     }
   }
@@ -612,9 +692,12 @@ template <> struct Multimem<__nv_bfloat16> {
     return v;
   }
 };
+// `direct` (small and medium messages): after the staging flags every rank reduces the WHOLE
+// tensor through the switch straight into its output — one staging pass and one reduction
+// pass, no broadcast, no second flag round and no copy-out.
 template <typename T>
 __device__ void ar_nvls_body(const RankCtx& c, const T* __restrict__ in, T* out, size_t nbytes,
-                             int nchan, int chan, unsigned long long* sh_seq) {
+                             int nchan, int chan, int io, bool direct, unsigned long long* sh_seq) {
   unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   CallInfo ci = call_begin(c, sh_seq);
   const size_t units = nbytes / 16;
@@ -622,6 +705,7 @@ __device__ void ar_nvls_body(const RankCtx& c, const T* __restrict__ in, T* out,
   const size_t per = (cu + nchan - 1) / nchan;
   const int W = c.world, me = c.rank;
   const int R = W;
+  const bool in_al = io & kInAligned, out_al = io & kOutAligned;
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
   // stage: region 0 of my own slot memory; channel `chan` stages its sub-range of EVERY chunk
   uint4* stage = reinterpret_cast<uint4*>(slot_region(c, me, ci.slot, 0));
@@ -631,13 +715,26 @@ __device__ void ar_nvls_body(const RankCtx& c, const T* __restrict__ in, T* out,
     size_t b = per * chan; if (b > len) b = len;
     size_t e = per * chan + per; if (e > len) e = len;
     for (size_t i = b + threadIdx.x; i < e; i += blockDim.x)
-      stage[base + i] = reinterpret_cast<const uint4*>(in)[base + i];
+      stage[base + i] = ld_unit(in, base + i, in_al);
   }
   __syncthreads();
   publish(c, ci, 0, chan);
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
   wait_all(c, ci, 0, chan, kWherePhase0);
   unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
+  if (direct) {
+    const char* mc_stage = c.mc_data + size_t(ci.slot) * c.slot_stride;
+    for (int r = 0; r < W; r++) {
+      size_t base = cu * r;
+      size_t len = base >= units ? 0 : ((units - base < cu) ? units - base : cu);
+      size_t b = per * chan; if (b > len) b = len;
+      size_t e = per * chan + per; if (e > len) e = len;
+      for (size_t i = b + threadIdx.x; i < e; i += blockDim.x)
+        st_unit(out, base + i, Multimem<T>::ld_reduce(mc_stage + (base + i) * 16), out_al);
+    }
+    call_end(c, ci, nchan, t_enter, t_ready, nbytes, TBV_ALGO_NVLS);
+    return;
+  }
   {
     size_t base = cu * me;
     size_t len = base >= units ? 0 : ((units - base < cu) ? units - base : cu);
@@ -660,7 +757,7 @@ __device__ void ar_nvls_body(const RankCtx& c, const T* __restrict__ in, T* out,
     size_t b = per * chan; if (b > len) b = len;
     size_t e = per * chan + per; if (e > len) e = len;
     for (size_t i = b + threadIdx.x; i < e; i += blockDim.x)
-      reinterpret_cast<uint4*>(out)[base + i] = ld_volatile_v4(res + base + i);
+      st_unit(out, base + i, ld_volatile_v4(res + base + i), out_al);
   }
   call_end(c, ci, nchan, t_enter, t_ready, nbytes, TBV_ALGO_NVLS);
 }
@@ -717,6 +814,49 @@ __device__ __forceinline__ void rmsnorm_row_store(const float (*h)[8], int nunit
   }
 }
 
+// The same row normalisation run by a CTA of a different size.  `nt` is the thread count the
+// plain op uses for this hidden size (one 16-byte unit per thread: hidden <= 8192); each real
+// thread plays the "virtual" threads threadIdx.x + j * blockDim.x.  Sums are formed in the
+// order of the nt-thread CTA (per-unit, 32-lane butterfly per virtual warp, warps in order), so
+// the result has the same bits as rmsnorm_row_store with blockDim.x == nt.  blockDim.x % 32 == 0.
+template <int VPT>
+__device__ __forceinline__ void rmsnorm_row_store_virtual(const float (*h)[8], int nunits_row, int hidden, float eps,
+                                                          const uint4* __restrict__ gamma, uint4* y_row, float* sh, int nt) {
+  const int lane = threadIdx.x & 31, nvw = nt >> 5;
+  __syncthreads();  // protect sh from the previous use
+#pragma unroll
+  for (int j = 0; j < VPT; j++) {
+    const int vt = threadIdx.x + j * blockDim.x;
+    float ss = 0.f;
+    if (vt < nunits_row) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) ss += h[j][i] * h[j][i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const int vw = vt >> 5;
+    if (lane == 0 && vw < nvw) sh[vw] = ss;
+  }
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < nvw; i++) tot += sh[i];
+  const float rs = rsqrtf(tot / float(hidden) + eps);
+#pragma unroll
+  for (int j = 0; j < VPT; j++) {
+    const int u = threadIdx.x + j * blockDim.x;
+    if (u < nunits_row) {
+      float g[8], o[8];
+      Pack<__nv_bfloat16>::unpack(gamma[u], g);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        float n = __bfloat162float(__float2bfloat16_rn(h[j][i] * rs));
+        o[i] = g[i] * n;
+      }
+      y_row[u] = Pack<__nv_bfloat16>::pack(o);
+    }
+  }
+}
+
 // ---- fused all-reduce + residual add + RMSNorm (one-shot, bf16) ---------------------------
 // Channel c owns rows c, c + nchan, ...  It pushes those rows, flags once, waits once,
 // then for each row: s = bf16(sum in rank order); h = bf16(s + residual);
@@ -726,33 +866,24 @@ __device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __
                                        const __nv_bfloat16* __restrict__ gamma,
                                        __nv_bfloat16* residual_out, __nv_bfloat16* y, int tokens,
                                        int hidden, float eps, int nchan, int chan,
-                                       unsigned long long* sh_seq, float* sh_red, bool ll) {
+                                       unsigned long long* sh_seq, float* sh_red) {
   unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   const int upr = hidden / 8;  // 16-byte units per row
-  // first row's first unit: loaded before the sequence number is known
-  uint4 first = make_uint4(0, 0, 0, 0);
-  if (chan < tokens && int(threadIdx.x) < upr) first = reinterpret_cast<const uint4*>(x)[size_t(chan) * upr + threadIdx.x];
   CallInfo ci = call_begin(c, sh_seq);
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
   for (int row = chan; row < tokens; row += nchan) {
     const uint4* src = reinterpret_cast<const uint4*>(x) + size_t(row) * upr;
     for (int u = threadIdx.x; u < upr; u += blockDim.x) {
-      uint4 v = (row == chan && u == int(threadIdx.x)) ? first : src[u];
-      if (ll) {
-        ll_push_unit(c, ci.slot, size_t(row) * upr + u, v, ci.want);
-      } else {
-        for (int p = 0; p < c.world; p++)
-          if (p != c.rank)
-            reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, c.rank))[size_t(row) * upr + u] = v;
-      }
+      const uint4 v = src[u];
+      for (int p = 0; p < c.world; p++)
+        if (p != c.rank)
+          reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, c.rank))[size_t(row) * upr + u] = v;
     }
   }
-  if (!ll) {
-    __syncthreads();
-    publish(c, ci, 0, chan);
-    if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
-    wait_all(c, ci, 0, chan, kWhereFused);
-  }
+  __syncthreads();
+  publish(c, ci, 0, chan);
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
+  wait_all(c, ci, 0, chan, kWhereFused);
   unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   for (int row = chan; row < tokens; row += nchan) {
     float h[kNormMaxUnits][8];
@@ -765,8 +896,7 @@ __device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __
         uint4 mine = reinterpret_cast<const uint4*>(x)[off];
         for (int r = 0; r < c.world; r++) {
           uint4 v = (r == c.rank) ? mine
-                    : (ll ? ll_pull_unit(c, ci.slot, r, off, ci.want, chan, ci.seq)
-                          : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, ci.slot, r)) + off));
+                                  : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, ci.slot, r)) + off);
           float f[8];
           Pack<__nv_bfloat16>::unpack(v, f);
 #pragma unroll
@@ -786,6 +916,61 @@ __device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __
                       reinterpret_cast<uint4*>(y) + size_t(row) * upr, sh_red);
   }
   call_end(c, ci, nchan, t_enter, t_ready, size_t(tokens) * hidden * 2, TBV_ALGO_ONESHOT);
+}
+
+// The same with LL packets: no fence, no flag, no flag wait — a row is pushed as self-announcing
+// packets and the packets of all peers are pulled with one batch of loads.  Runs with at most 512
+// threads (128 registers each for the batch); a hidden size whose plain norm kernel uses more
+// threads is handled by two virtual threads per thread, same bits.  hidden <= 8192.
+constexpr int kLLNormVPT = 2;
+__device__ inline void ar_rmsnorm_ll_body(const RankCtx& c, const __nv_bfloat16* __restrict__ x,
+                                          const __nv_bfloat16* residual, const __nv_bfloat16* __restrict__ gamma,
+                                          __nv_bfloat16* residual_out, __nv_bfloat16* y, int tokens, int hidden, float eps,
+                                          int nchan, int chan, int norm_threads, unsigned long long* sh_seq, float* sh_red) {
+  unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
+  const int upr = hidden / 8;
+  // first row's first unit: loaded before the sequence number is known
+  uint4 first = make_uint4(0, 0, 0, 0);
+  if (chan < tokens && int(threadIdx.x) < upr) first = reinterpret_cast<const uint4*>(x)[size_t(chan) * upr + threadIdx.x];
+  CallInfo ci = call_begin(c, sh_seq);
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
+  for (int row = chan; row < tokens; row += nchan) {
+    const uint4* src = reinterpret_cast<const uint4*>(x) + size_t(row) * upr;
+    for (int u = threadIdx.x; u < upr; u += blockDim.x) {
+      const uint4 v = (row == chan && u == int(threadIdx.x)) ? first : src[u];
+      ll_push_unit(c, ci.slot, size_t(row) * upr + u, v, ci.want);
+    }
+  }
+  if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
+  const unsigned peers = ((1u << c.world) - 1u) & ~(1u << c.rank);
+  unsigned long long t_ready = 0;
+  for (int row = chan; row < tokens; row += nchan) {
+    float h[kLLNormVPT][8];
+#pragma unroll
+    for (int j = 0; j < kLLNormVPT; j++) {
+      const int u = threadIdx.x + j * blockDim.x;
+      if (u < upr) {
+        const size_t off = size_t(row) * upr + u;
+        const uint4 mine = (row == chan && j == 0) ? first : reinterpret_cast<const uint4*>(x)[off];
+        uint4 got[TBV_MAXRANK];
+        ll_pull_all(c, ci.slot, off, ci.want, peers, chan, ci.seq, got);
+        float acc[8];
+        ll_sum_unit<__nv_bfloat16>(c, got, peers, mine, acc);
+        float res[8];
+        Pack<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(residual)[off], res);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          float s = __bfloat162float(__float2bfloat16_rn(acc[i]));
+          h[j][i] = __bfloat162float(__float2bfloat16_rn(s + res[i]));
+        }
+        reinterpret_cast<uint4*>(residual_out)[off] = Pack<__nv_bfloat16>::pack(h[j]);
+      }
+    }
+    if (row == chan && threadIdx.x == 0 && chan == 0) { t_ready = globaltimer(); c.dm->bc[2] = ci.seq; }
+    rmsnorm_row_store_virtual<kLLNormVPT>(h, upr, hidden, eps, reinterpret_cast<const uint4*>(gamma),
+                                          reinterpret_cast<uint4*>(y) + size_t(row) * upr, sh_red, norm_threads);
+  }
+  call_end(c, ci, nchan, t_enter, t_ready, size_t(tokens) * hidden * 2, TBV_ALGO_LL);
 }
 
 }  // namespace tbv

@@ -66,6 +66,7 @@ Knobs Knobs::from_env() {
   k.init_timeout_s = env_double("TBV_INIT_TIMEOUT", 60.0);
   k.ll_max = env_long("TBV_LL_MAX", -1);  // -1: chosen from the world size when the communicator is created
   k.nvls_min = env_long("TBV_NVLS_MIN", LONG_MAX);  // auto never picks the switch-reduced kernel unless asked
+  k.nvls_direct_max = env_long("TBV_NVLS_DIRECT_MAX", 1l << 20);
   const char* a = getenv("TBV_ALGO");
   if (a) {
     if (!strcmp(a, "oneshot")) k.algo = TBV_ALGO_ONESHOT;
@@ -159,83 +160,115 @@ struct LocalPtrs {
   void* out[TBV_MAXRANK];
   const void* aux[TBV_MAXRANK];   // residual
   void* aux_out[TBV_MAXRANK];     // residual_out
+  int io;                          // kInAligned | kOutAligned, over all emulated ranks
+  int mute;                        // emulated rank whose CTAs leave at once (a rank that never makes the call), or -1
 };
 
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(512) k_ar_oneshot(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
+__global__ void __launch_bounds__(512) k_ar_oneshot(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes, int io) {
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
-  ar_oneshot_body<T, VEC>(c, in, out, nbytes, gridDim.x, blockIdx.x, &sh_seq);
+  ar_oneshot_body<T, VEC>(c, in, out, nbytes, gridDim.x, blockIdx.x, io, &sh_seq);
 }
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(512) k_ar_oneshot_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p, size_t nbytes) {
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
+  if (int(blockIdx.y) == p.mute) return;
   ar_oneshot_body<T, VEC>(ctxs[blockIdx.y], static_cast<const T*>(p.in[blockIdx.y]), static_cast<T*>(p.out[blockIdx.y]),
-                          nbytes, gridDim.x, blockIdx.x, &sh_seq);
+                          nbytes, gridDim.x, blockIdx.x, p.io, &sh_seq);
 }
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(512) k_ar_twoshot(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes, int mode) {
+__global__ void __launch_bounds__(512) k_ar_twoshot(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes, int mode, int io) {
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
-  ar_twoshot_body<T, VEC>(c, in, out, nbytes, gridDim.x, blockIdx.x, mode, &sh_seq);
+  ar_twoshot_body<T, VEC>(c, in, out, nbytes, gridDim.x, blockIdx.x, mode, io, &sh_seq);
 }
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(512) k_ar_twoshot_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p, size_t nbytes, int mode) {
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
+  if (int(blockIdx.y) == p.mute) return;
   ar_twoshot_body<T, VEC>(ctxs[blockIdx.y], static_cast<const T*>(p.in[blockIdx.y]), static_cast<T*>(p.out[blockIdx.y]),
-                          nbytes, gridDim.x, blockIdx.x, mode, &sh_seq);
+                          nbytes, gridDim.x, blockIdx.x, mode, p.io, &sh_seq);
 }
 template <typename T>
-__global__ void __launch_bounds__(512) k_ar_ll(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
+__global__ void __launch_bounds__(512) k_ar_ll(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes, int io) {
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();
-  ar_oneshot_ll_body<T>(c, in, out, nbytes, gridDim.x, blockIdx.x, &sh_seq);
+  ar_oneshot_ll_body<T>(c, in, out, nbytes, gridDim.x, blockIdx.x, io, &sh_seq);
 }
 template <typename T>
 __global__ void __launch_bounds__(512) k_ar_ll_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p, size_t nbytes) {
   __shared__ unsigned long long sh_seq;
+  if (int(blockIdx.y) == p.mute) return;
   ar_oneshot_ll_body<T>(ctxs[blockIdx.y], static_cast<const T*>(p.in[blockIdx.y]), static_cast<T*>(p.out[blockIdx.y]), nbytes,
-                        gridDim.x, blockIdx.x, &sh_seq);
+                        gridDim.x, blockIdx.x, p.io, &sh_seq);
 }
 template <typename T>
-__global__ void __launch_bounds__(512) k_ar_nvls(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
+__global__ void __launch_bounds__(512) k_ar_nvls(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes, int io, bool direct) {
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
-  ar_nvls_body<T>(c, in, out, nbytes, gridDim.x, blockIdx.x, &sh_seq);
+  ar_nvls_body<T>(c, in, out, nbytes, gridDim.x, blockIdx.x, io, direct, &sh_seq);
 }
 __global__ void __launch_bounds__(1024) k_ar_rmsnorm(const __grid_constant__ RankCtx c, const __nv_bfloat16* x,
                                                      const __nv_bfloat16* residual, const __nv_bfloat16* gamma,
                                                      __nv_bfloat16* residual_out, __nv_bfloat16* y, int tokens, int hidden,
-                                                     float eps, bool ll) {
+                                                     float eps) {
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
   __shared__ float sh_red[32];
-  ar_rmsnorm_body(c, x, residual, gamma, residual_out, y, tokens, hidden, eps, gridDim.x, blockIdx.x, &sh_seq, sh_red, ll);
+  ar_rmsnorm_body(c, x, residual, gamma, residual_out, y, tokens, hidden, eps, gridDim.x, blockIdx.x, &sh_seq, sh_red);
 }
 __global__ void __launch_bounds__(1024) k_ar_rmsnorm_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p,
-                                                           const __nv_bfloat16* gamma, int tokens, int hidden, float eps, bool ll) {
+                                                           const __nv_bfloat16* gamma, int tokens, int hidden, float eps) {
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
   __shared__ float sh_red[32];
   const int r = blockIdx.y;
+  if (r == p.mute) return;
   ar_rmsnorm_body(ctxs[r], static_cast<const __nv_bfloat16*>(p.in[r]), static_cast<const __nv_bfloat16*>(p.aux[r]), gamma,
                   static_cast<__nv_bfloat16*>(p.aux_out[r]), static_cast<__nv_bfloat16*>(p.out[r]), tokens, hidden, eps,
-                  gridDim.x, blockIdx.x, &sh_seq, sh_red, ll);
+                  gridDim.x, blockIdx.x, &sh_seq, sh_red);
+}
+__global__ void __launch_bounds__(512) k_ar_rmsnorm_ll(const __grid_constant__ RankCtx c, const __nv_bfloat16* x,
+                                                       const __nv_bfloat16* residual, const __nv_bfloat16* gamma,
+                                                       __nv_bfloat16* residual_out, __nv_bfloat16* y, int tokens, int hidden,
+                                                       float eps, int norm_threads) {
+  __shared__ unsigned long long sh_seq;
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();  // before the device sequence number or any input is read
+  __shared__ float sh_red[32];
+  ar_rmsnorm_ll_body(c, x, residual, gamma, residual_out, y, tokens, hidden, eps, gridDim.x, blockIdx.x, norm_threads, &sh_seq, sh_red);
+}
+__global__ void __launch_bounds__(512) k_ar_rmsnorm_ll_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p,
+                                                             const __nv_bfloat16* gamma, int tokens, int hidden, float eps,
+                                                             int norm_threads) {
+  __shared__ unsigned long long sh_seq;
+  pdl::launch_dependents();
+  pdl::grid_dependency_wait();  // before the device sequence number or any input is read
+  __shared__ float sh_red[32];
+  const int r = blockIdx.y;
+  if (r == p.mute) return;
+  ar_rmsnorm_ll_body(ctxs[r], static_cast<const __nv_bfloat16*>(p.in[r]), static_cast<const __nv_bfloat16*>(p.aux[r]), gamma,
+                     static_cast<__nv_bfloat16*>(p.aux_out[r]), static_cast<__nv_bfloat16*>(p.out[r]), tokens, hidden, eps,
+                     gridDim.x, blockIdx.x, norm_threads, &sh_seq, sh_red);
 }
 
 // ---- sizing tables --------------------------------------------------------------------------
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Which kernel runs is a function of (bytes, world, knobs) only — never of a pointer — and the
+// knobs that enter it are checked for agreement between the ranks when the communicator is
+// created: ranks that picked different kernels would wait on flags nobody raises.
 static int pick_algo(const tbv_comm* c, size_t nbytes, bool vec) {
   int a = c->knobs.algo;
   if (a == TBV_ALGO_NVLS && !(c->nvls && vec)) a = TBV_ALGO_AUTO;
@@ -257,7 +290,9 @@ static int pick_nchan(const tbv_comm* c, int algo, size_t units_per_rankchunk, i
   size_t per_chan_units = c->knobs.chunk > 0 ? std::max<size_t>(1, size_t(c->knobs.chunk) / 16)
                                              : size_t(threads);  // one 16-byte unit per thread and pass (measured: fatter channels leave two-shot latency-bound at 8 ranks)
   size_t n = (units_per_rankchunk + per_chan_units - 1) / per_chan_units;
-  int cap = (algo == TBV_ALGO_ONESHOT || algo == TBV_ALGO_LL) ? 32 : 64;
+  // two-shot: 64 channels keep the latency of mid-size messages low; from 4096 units (64 KiB) per channel on,
+  // bandwidth is what counts and more CTAs put more bytes in flight
+  int cap = (algo == TBV_ALGO_ONESHOT || algo == TBV_ALGO_LL) ? 32 : (units_per_rankchunk >= size_t(64) * 4096 ? 128 : 64);
   return int(std::max<size_t>(1, std::min<size_t>(n, size_t(std::min(cap, maxchan)))));
 }
 
@@ -291,10 +326,13 @@ static int alloc_rank_state(tbv_comm* c, GpuRank& g) {
 
 static void compute_sizes(tbv_comm* c) {
   // LL packets double the bytes and every rank writes to every peer, so the size up to which they win
-  // shrinks with the world (measured, graph-timed: 2 ranks 4.6 vs 6.3 us at 8 KB and ahead up to 256 KB;
-  // 8 ranks 11.2 vs 9.8 us at 8 KB — plain one-shot is better there).
-  if (c->knobs.ll_max < 0) c->knobs.ll_max = c->world <= 2 ? (256 << 10) : (c->world <= 4 ? (64 << 10) : 0);
-  c->flag_bytes = (size_t(c->knobs.nslot) * 2 * c->world * TBV_MAXCHAN * sizeof(unsigned) + 4095) & ~size_t(4095);
+  // shrinks with the world.  The receiver fetches the packets of all sources with one batch of loads,
+  // so the cost of a call no longer grows with one memory round trip per peer.
+  if (c->knobs.ll_max < 0) c->knobs.ll_max = c->world <= 2 ? (256 << 10) : (c->world <= 4 ? (128 << 10) : (128 << 10));
+  const size_t nflag = size_t(c->knobs.nslot) * 2 * c->world * TBV_MAXCHAN;
+  c->tag_off = (nflag * sizeof(unsigned) + 255) & ~size_t(255);
+  // flags, then one 8-byte sequence stamp per flag (TBV_TAG diagnostic; its own words, never inside a payload region)
+  c->flag_bytes = (c->tag_off + nflag * sizeof(unsigned long long) + 4095) & ~size_t(4095);
   c->data_bytes = size_t(c->knobs.nslot) * size_t(c->world + 1) * c->cap;
   // LL area: two bytes on the wire per payload byte, one region per (slot, source)
   c->ll_cap = (size_t(std::max(0l, c->knobs.ll_max)) * 2 + 4095) & ~size_t(4095);
@@ -467,15 +505,29 @@ static int gpu_init(tbv_comm* c) {
   g.device = c->device;
   if (alloc_rank_state(c, g) != TBV_OK) return TBV_FAIL;
 
-  // agree on the parameters that shape the protocol
-  struct Hello { int world, nslot, tag, dev; unsigned long long cap; char uuid[16]; } me{}, all[TBV_MAXRANK];
+  // agree on the parameters that shape the protocol and on every knob that enters the choice of
+  // kernel or of the channel count (ranks that chose differently would wait on flags nobody raises)
+  struct Hello {
+    int world, nslot, tag, dev, algo, nchan, nvls;
+    long long ll_max, oneshot_max, chunk, nvls_min;
+    unsigned long long cap;
+    char uuid[16];
+  } me{}, all[TBV_MAXRANK];
   me.world = c->world; me.nslot = c->knobs.nslot; me.tag = c->knobs.tag; me.dev = c->device; me.cap = c->cap;
+  me.algo = c->knobs.algo; me.nchan = c->knobs.nchan; me.nvls = c->knobs.nvls; me.ll_max = c->knobs.ll_max;
+  me.oneshot_max = c->knobs.oneshot_max; me.chunk = c->knobs.chunk; me.nvls_min = c->knobs.nvls_min;
   memcpy(me.uuid, &prop.uuid, 16);
   if (c->bs.allgather(&me, all, sizeof(Hello)) != 0) { c->errmsg = c->bs.error(); return TBV_FAIL; }
   for (int p = 0; p < c->world; p++) {
     if (all[p].world != me.world || all[p].nslot != me.nslot || all[p].cap != me.cap || all[p].tag != me.tag) {
       c->errmsg = "ranks disagree on world/nslot/cap/tag";
       LOG("rank %d: %s (rank %d has nslot=%d cap=%llu)", c->rank, c->errmsg.c_str(), p, all[p].nslot, all[p].cap);
+      return TBV_FAIL;
+    }
+    if (all[p].algo != me.algo || all[p].nchan != me.nchan || all[p].nvls != me.nvls || all[p].ll_max != me.ll_max ||
+        all[p].oneshot_max != me.oneshot_max || all[p].chunk != me.chunk || all[p].nvls_min != me.nvls_min) {
+      c->errmsg = "ranks disagree on TBV_ALGO/TBV_NCHAN/TBV_NVLS/TBV_LL_MAX/TBV_RAIL1MAX/TBV_CHUNK/TBV_NVLS_MIN";
+      LOG("rank %d: %s (compared with rank %d)", c->rank, c->errmsg.c_str(), p);
       return TBV_FAIL;
     }
     if (p != c->rank && !memcmp(all[p].uuid, me.uuid, 16)) {
@@ -504,6 +556,7 @@ static int gpu_init(tbv_comm* c) {
   fill_ctx(c, g, c->rank);
   for (int p = 0; p < c->world; p++) {
     g.ctx.flags[p] = reinterpret_cast<unsigned*>(c->peer_maps[p]);
+    g.ctx.tags[p] = reinterpret_cast<unsigned long long*>(static_cast<char*>(c->peer_maps[p]) + c->tag_off);
     g.ctx.data[p] = static_cast<char*>(c->peer_maps[p]) + c->flag_bytes;
     g.ctx.ll[p] = static_cast<char*>(c->peer_maps[p]) + c->flag_bytes + c->data_bytes;
   }
@@ -536,6 +589,7 @@ static int gpu_init_local(tbv_comm* c) {
     fill_ctx(c, g, r);
     for (int p = 0; p < c->world; p++) {
       g.ctx.flags[p] = reinterpret_cast<unsigned*>(c->ranks[p].base);
+      g.ctx.tags[p] = reinterpret_cast<unsigned long long*>(c->ranks[p].base + c->tag_off);
       g.ctx.data[p] = c->ranks[p].base + c->flag_bytes;
       g.ctx.ll[p] = c->ranks[p].base + c->flag_bytes + c->data_bytes;
     }
@@ -609,18 +663,19 @@ static void note_stream(tbv_comm* c, void* stream) {
 // ---- launch -----------------------------------------------------------------------------------
 template <typename T>
 static cudaError_t launch_ar_t(tbv_comm* c, int algo, bool vec, int nchan, int threads, const void* in, void* out,
-                               size_t nbytes, cudaStream_t st, int mode) {
+                               size_t nbytes, cudaStream_t st, int mode, int io) {
   const RankCtx& x = c->ranks[0].ctx;
   const T* i = static_cast<const T*>(in);
   T* o = static_cast<T*>(out);
   const dim3 g(nchan), b(threads);
-  if (algo == TBV_ALGO_NVLS) return pdl::launch(k_ar_nvls<T>, g, b, 0, st, 1, x, i, o, nbytes);
-  if (algo == TBV_ALGO_LL) return pdl::launch(k_ar_ll<T>, g, b, 0, st, 1, x, i, o, nbytes);
+  // switch-reduced kernel: below TBV_NVLS_DIRECT_MAX every rank reduces the whole tensor itself (one pass)
+  if (algo == TBV_ALGO_NVLS) return pdl::launch(k_ar_nvls<T>, g, b, 0, st, 1, x, i, o, nbytes, io, long(nbytes) <= c->knobs.nvls_direct_max);
+  if (algo == TBV_ALGO_LL) return pdl::launch(k_ar_ll<T>, g, b, 0, st, 1, x, i, o, nbytes, io);
   if (algo == TBV_ALGO_ONESHOT)
-    return vec ? pdl::launch(k_ar_oneshot<T, true>, g, b, 0, st, 1, x, i, o, nbytes)
-               : pdl::launch(k_ar_oneshot<T, false>, g, b, 0, st, 1, x, i, o, nbytes);
-  return vec ? pdl::launch(k_ar_twoshot<T, true>, g, b, 0, st, 1, x, i, o, nbytes, mode)
-             : pdl::launch(k_ar_twoshot<T, false>, g, b, 0, st, 1, x, i, o, nbytes, mode);
+    return vec ? pdl::launch(k_ar_oneshot<T, true>, g, b, 0, st, 1, x, i, o, nbytes, io)
+               : pdl::launch(k_ar_oneshot<T, false>, g, b, 0, st, 1, x, i, o, nbytes, io);
+  return vec ? pdl::launch(k_ar_twoshot<T, true>, g, b, 0, st, 1, x, i, o, nbytes, mode, io)
+             : pdl::launch(k_ar_twoshot<T, false>, g, b, 0, st, 1, x, i, o, nbytes, mode, io);
 }
 
 template <typename T>
@@ -644,6 +699,13 @@ static cudaError_t launch_ar_local_t(tbv_comm* c, int algo, bool vec, int nchan,
   return cudaLaunchCooperativeKernel(fn, grid, dim3(threads), args, 0, st);
 }
 
+// Emulated world only: the rank named by tbv_comm_mute_rank sits out this launch.
+static int take_mute(tbv_comm* c) {
+  if (!c->local || c->mute_left.load() <= 0) return -1;
+  c->mute_left.fetch_sub(1);
+  return c->mute_rank;
+}
+
 static size_t dtype_size(int dtype) { return dtype == TBV_F32 ? 4 : 2; }
 
 // mode: 0 all-reduce (nbytes = tensor), 1 reduce-scatter (nbytes = output), 2 all-gather (nbytes = input)
@@ -664,8 +726,15 @@ static int gpu_collective(tbv_comm* c, const void* const* ins, void* const* outs
     if (outs[0] != ins[0]) CUDA_TRY(c, cudaMemcpyAsync(outs[0], ins[0], nbytes, cudaMemcpyDeviceToDevice, st));
     return TBV_OK;
   }
-  bool vec = (nbytes % 16 == 0);
-  for (int r = 0; r < nr; r++) vec = vec && aligned16(ins[r]) && aligned16(outs[r]);
+  // 16-byte units whenever the byte count allows: the partition into channels and the choice of kernel
+  // must not depend on where a rank's tensor sits (ranks would disagree); a tensor that is not 16-byte
+  // aligned is only accessed element by element inside the same kernel
+  const bool vec = (nbytes % 16 == 0);
+  int io = kInAligned | kOutAligned;
+  for (int r = 0; r < nr; r++) {
+    if (!aligned16(ins[r])) io &= ~kInAligned;
+    if (!aligned16(outs[r])) io &= ~kOutAligned;
+  }
   int algo = mode == 0 ? pick_algo(c, nbytes, vec) : TBV_ALGO_TWOSHOT;
   if (mode != 0 && !vec && (nbytes % dtype_size(dtype))) return TBV_FALLBACK;
   if (c->local && algo == TBV_ALGO_NVLS) algo = TBV_ALGO_TWOSHOT;
@@ -682,6 +751,8 @@ static int gpu_collective(tbv_comm* c, const void* const* ins, void* const* outs
   if (c->local) {
     LocalPtrs p{};
     for (int r = 0; r < nr; r++) { p.in[r] = ins[r]; p.out[r] = outs[r]; }
+    p.io = io;
+    p.mute = take_mute(c);
     switch (dtype) {
       case TBV_F32: e = launch_ar_local_t<float>(c, algo, vec, nchan, threads, p, full, st, mode); break;
       case TBV_F16: e = launch_ar_local_t<__half>(c, algo, vec, nchan, threads, p, full, st, mode); break;
@@ -689,9 +760,9 @@ static int gpu_collective(tbv_comm* c, const void* const* ins, void* const* outs
     }
   } else {
     switch (dtype) {
-      case TBV_F32: e = launch_ar_t<float>(c, algo, vec, nchan, threads, ins[0], outs[0], full, st, mode); break;
-      case TBV_F16: e = launch_ar_t<__half>(c, algo, vec, nchan, threads, ins[0], outs[0], full, st, mode); break;
-      default: e = launch_ar_t<__nv_bfloat16>(c, algo, vec, nchan, threads, ins[0], outs[0], full, st, mode); break;
+      case TBV_F32: e = launch_ar_t<float>(c, algo, vec, nchan, threads, ins[0], outs[0], full, st, mode, io); break;
+      case TBV_F16: e = launch_ar_t<__half>(c, algo, vec, nchan, threads, ins[0], outs[0], full, st, mode, io); break;
+      default: e = launch_ar_t<__nv_bfloat16>(c, algo, vec, nchan, threads, ins[0], outs[0], full, st, mode, io); break;
     }
   }
   if (e != cudaSuccess) {
@@ -729,26 +800,33 @@ static int gpu_ar_rmsnorm(tbv_comm* c, const void* const* xs, const void* const*
   if (c->skip.load() > 0) { c->skip.fetch_sub(1); return TBV_OK; }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   note_stream(c, stream);
-  const int upr = hidden / 8;
-  const int threads = tbvops::norm_threads(hidden);  // same mapping as the plain norm op: identical bits
+  const int nt = tbvops::norm_threads(hidden);  // same mapping as the plain norm op: identical bits
   int maxchan = c->local ? std::max(1, std::min(TBV_MAXCHAN, c->sm_count / c->world)) : TBV_MAXCHAN;
   int nchan = std::min(tokens, c->knobs.nchan > 0 ? std::min(c->knobs.nchan, maxchan) : maxchan);
   cudaError_t e;
-  bool ll = (c->knobs.algo == TBV_ALGO_AUTO || c->knobs.algo == TBV_ALGO_LL) && nbytes * 2 <= c->ll_cap && long(nbytes) <= c->knobs.ll_max;
+  const bool ll = (c->knobs.algo == TBV_ALGO_AUTO || c->knobs.algo == TBV_ALGO_LL) && nbytes * 2 <= c->ll_cap &&
+                  long(nbytes) <= c->knobs.ll_max && hidden <= 8 * kLLNormVPT * 512;
+  const int threads = ll ? std::min(nt, 512) : nt;
+  const __nv_bfloat16* g = static_cast<const __nv_bfloat16*>(gamma);
   if (c->local) {
     LocalPtrs p{};
     for (int r = 0; r < nr; r++) { p.in[r] = xs[r]; p.out[r] = ys[r]; p.aux[r] = residuals[r]; p.aux_out[r] = residual_outs[r]; }
+    p.io = kInAligned | kOutAligned;
+    p.mute = take_mute(c);
     const RankCtx* ctxs = c->ctxs_dev;
-    const __nv_bfloat16* g = static_cast<const __nv_bfloat16*>(gamma);
-    void* args[] = {(void*)&ctxs, (void*)&p, (void*)&g, (void*)&tokens, (void*)&hidden, (void*)&eps, (void*)&ll};
-    e = cudaLaunchCooperativeKernel((void*)k_ar_rmsnorm_local, dim3(nchan, c->world), dim3(threads), args, 0, st);
+    int ntv = nt;
+    void* args[] = {(void*)&ctxs, (void*)&p, (void*)&g, (void*)&tokens, (void*)&hidden, (void*)&eps, (void*)&ntv};
+    e = cudaLaunchCooperativeKernel(ll ? (void*)k_ar_rmsnorm_ll_local : (void*)k_ar_rmsnorm_local, dim3(nchan, c->world), dim3(threads), args, 0, st);
   } else if (c->world == 1) {
     return TBV_FALLBACK;  // nothing to reduce: the caller uses the plain fused add+norm op
+  } else if (ll) {
+    e = pdl::launch(k_ar_rmsnorm_ll, dim3(nchan), dim3(threads), 0, st, 1, c->ranks[0].ctx,
+                    static_cast<const __nv_bfloat16*>(xs[0]), static_cast<const __nv_bfloat16*>(residuals[0]), g,
+                    static_cast<__nv_bfloat16*>(residual_outs[0]), static_cast<__nv_bfloat16*>(ys[0]), tokens, hidden, eps, nt);
   } else {
     e = pdl::launch(k_ar_rmsnorm, dim3(nchan), dim3(threads), 0, st, 1, c->ranks[0].ctx,
-                    static_cast<const __nv_bfloat16*>(xs[0]), static_cast<const __nv_bfloat16*>(residuals[0]),
-                    static_cast<const __nv_bfloat16*>(gamma), static_cast<__nv_bfloat16*>(residual_outs[0]),
-                    static_cast<__nv_bfloat16*>(ys[0]), tokens, hidden, eps, ll);
+                    static_cast<const __nv_bfloat16*>(xs[0]), static_cast<const __nv_bfloat16*>(residuals[0]), g,
+                    static_cast<__nv_bfloat16*>(residual_outs[0]), static_cast<__nv_bfloat16*>(ys[0]), tokens, hidden, eps);
   }
   if (e != cudaSuccess) {
     c->errmsg = std::string("kernel launch: ") + cudaGetErrorString(e);
@@ -855,6 +933,8 @@ int tbv_comm_destroy(tbv_comm* c) {
       if (g.hm) cudaFreeHost(g.hm);
     }
     if (c->ctxs_dev) cudaFree(c->ctxs_dev);
+    for (auto& kv : c->gather_maps) cudaFree(kv.second);   // tensor maps over this communicator's slot memory die with it
+    c->gather_maps.clear();
   }
   c->cpu.reset();
   c->bs.close_all();
@@ -936,6 +1016,19 @@ int tbv_comm_nslot(tbv_comm* c) { return c ? c->knobs.nslot : 0; }
 int tbv_comm_is_async(tbv_comm* c) { return c ? c->knobs.async : 0; }
 int tbv_comm_err(tbv_comm* c) { return c ? int(check_err(c)) : 1; }
 int tbv_comm_has_nvls(tbv_comm* c) { return c ? int(c->nvls) : 0; }
+// Sequence stamps (TBV_TAG=1) compared and found wrong since the communicator was created, summed over (emulated) ranks.
+int tbv_comm_tag_counts(tbv_comm* c, unsigned long long* checked, unsigned long long* bad) {
+  if (!c || c->cpu) return TBV_FAIL;
+  unsigned long long b = 0, k = 0;
+  for (auto& g : c->ranks) {
+    unsigned long long v[2] = {0, 0};
+    if (!g.dm || cudaMemcpy(v, &g.dm->tag_bad, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return TBV_FAIL;
+    b += v[0]; k += v[1];
+  }
+  if (checked) *checked = k;
+  if (bad) *bad = b;
+  return TBV_OK;
+}
 int tbv_comm_set_algo(tbv_comm* c, int algo) {
   if (!c || algo < 0 || algo > 4) return TBV_FAIL;
   c->knobs.algo = algo;
@@ -961,6 +1054,15 @@ int tbv_comm_set_wdog(tbv_comm* c, double seconds) {
 int tbv_comm_skip_next(tbv_comm* c, int n) {
   if (!c) return TBV_FAIL;
   c->skip.store(n);
+  return TBV_OK;
+}
+// Emulated world only, host-side fault injection: for the next n collective launches the CTAs of
+// emulated rank r return before they push anything, like a rank that never makes the call.  The other
+// ranks' bounded waits run out and report it; nothing faults.
+int tbv_comm_mute_rank(tbv_comm* c, int r, int n) {
+  if (!c || !c->local || r < 0 || r >= c->world || n < 0) return TBV_FAIL;
+  c->mute_rank = r;
+  c->mute_left.store(n);
   return TBV_OK;
 }
 int tbv_comm_ctx(tbv_comm* c, void* ctx_out, size_t ctx_bytes) {
@@ -991,12 +1093,12 @@ void tbv_comm_rails(tbv_comm* c) {
 void tbv_comm_hist(tbv_comm* c) {
   if (!c) return;
   harvest_trace(c);
-  unsigned long long bad = 0;
+  unsigned long long bad = 0, checked = 0;
   for (auto& g : c->ranks) {
-    unsigned long long v = 0;
-    if (g.dm && cudaMemcpy(&v, &g.dm->tag_bad, sizeof(v), cudaMemcpyDeviceToHost) == cudaSuccess) bad += v;
+    unsigned long long v[2] = {0, 0};   // tag_bad, tag_checked are adjacent in DevMirror
+    if (g.dm && cudaMemcpy(v, &g.dm->tag_bad, sizeof(v), cudaMemcpyDeviceToHost) == cudaSuccess) { bad += v[0]; checked += v[1]; }
   }
-  c->stats.dump_hist(c->rank, bad);
+  c->stats.dump_hist(c->rank, bad, checked);
 }
 // Device breadcrumbs of (emulated) rank r: bc[0..3] = sequence numbers at enter / pushed /
 // wait-pass / done; bc[4..7] = %globaltimer stamps of the last fused GEMM call (accumulator
@@ -1004,6 +1106,14 @@ void tbv_comm_hist(tbv_comm* c) {
 int tbv_comm_breadcrumbs(tbv_comm* c, int r, unsigned long long out[8]) {
   if (!c || c->cpu || r < 0 || r >= int(c->ranks.size())) return TBV_FAIL;
   return cudaMemcpy(out, c->ranks[r].dm->bc, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? TBV_OK : TBV_FAIL;
+}
+// %globaltimer stamps (ns) of the last fused GEMM + all-reduce + norm call on (emulated) rank r:
+// [0] first finisher resident, [1] its dependency wait passed, [2] this rank's GEMM CTAs have all pushed,
+// [3] first row's packets of all ranks pulled, [4] rows normalised, [5] last GEMM tile's CTA resident,
+// [6] its accumulator complete, [7] its packets issued.  Synchronous copy.
+int tbv_comm_timestamps(tbv_comm* c, int r, unsigned long long out[8]) {
+  if (!c || c->cpu || r < 0 || r >= int(c->ranks.size())) return TBV_FAIL;
+  return cudaMemcpy(out, c->ranks[r].dm->ts, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? TBV_OK : TBV_FAIL;
 }
 void tbv_comm_last_error(tbv_comm* c, unsigned long long out[4]) {
   out[0] = out[1] = out[2] = out[3] = 0;

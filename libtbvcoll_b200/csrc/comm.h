@@ -5,6 +5,8 @@
 // process; the `tbv_ar_*` functions operate on one default instance.
 #pragma once
 #include <atomic>
+#include <map>
+#include <tuple>
 #include <memory>
 #include <string>
 #include <vector>
@@ -33,6 +35,7 @@ struct Knobs {
   double init_timeout_s = 60.0;  // TBV_INIT_TIMEOUT
   long ll_max = -1;              // TBV_LL_MAX: largest message that uses flag-in-payload (LL) packets (-1: by world size)
   long nvls_min = 0x7fffffffffffffffl;  // TBV_NVLS_MIN: smallest message for the switch-reduced kernel in auto mode
+  long nvls_direct_max = 1l << 20;      // TBV_NVLS_DIRECT_MAX: up to here the switch-reduced kernel has every rank reduce the whole tensor (one pass)
   static Knobs from_env();
 };
 
@@ -61,6 +64,7 @@ struct tbv_comm {
   std::vector<tbv::GpuRank> ranks;       // size 1 (real) or world (emulated)
   tbv::RankCtx* ctxs_dev = nullptr;      // emulated: device array of contexts
   size_t flag_bytes = 0, data_bytes = 0, ll_bytes = 0, ll_cap = 0;
+  size_t tag_off = 0;                    // byte offset of the sequence-stamp words inside the flag area
   bool vmm = false, nvls = false;
   std::vector<void*> peer_maps;          // mapped peer bases (to unmap at teardown)
   std::vector<unsigned long long> vmm_handles;  // CUmemGenericAllocationHandle per rank (imported + own)
@@ -69,6 +73,11 @@ struct tbv_comm {
   size_t mc_bytes = 0;
   int sm_count = 148;
   std::atomic<int> skip{0};
+  int mute_rank = -1;                    // emulated world: rank that sits out the next `mute_left` launches
+  std::atomic<int> mute_left{0};
+  // device arrays of TMA tensor maps over this communicator's gather buffers, keyed by
+  // (emulated rank, rows per rank, K, tile rows); freed in tbv_comm_destroy
+  std::map<std::tuple<int, int, int, int>, void*> gather_maps;
   std::atomic<int> sticky_err{0};
   unsigned long long host_seq = 0, trace_read = 0;
   std::vector<tbv::TraceRec> trace_host;   // staging for the timing ring

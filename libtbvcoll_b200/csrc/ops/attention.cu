@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(kThreads) k_paged_attn(const AttnParams p) {
   pdl::grid_dependency_wait();
   const int qi = blockIdx.x, h = blockIdx.y, sp = blockIdx.z, S = p.splits;
   const int hw = threadIdx.x >> 4, l16 = threadIdx.x & 15;
-  const int ctx = p.ctx_lens[qi];
+  const int ctx = min(p.ctx_lens[qi], p.max_blocks * p.block_size);  // never walk past the block table (a captured loop replayed beyond the reserved length)
   const int seq = p.seq_of_query ? p.seq_of_query[qi] : qi;
   const int* bt = p.block_tables + size_t(seq) * p.max_blocks;
   int chunk = (ctx + S - 1) / S;
@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(kMW * 32) k_paged_attn_mma(const AttnParams p)
   const int qi = blockIdx.x, h = blockIdx.y, sp = blockIdx.z, S = p.splits;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = lane >> 2, quad = lane & 3;       // MMA row (query head) and column pair of this lane
-  const int ctx = p.ctx_lens[qi];
+  const int ctx = min(p.ctx_lens[qi], p.max_blocks * p.block_size);  // never walk past the block table (a captured loop replayed beyond the reserved length)
   const int seq = p.seq_of_query ? p.seq_of_query[qi] : qi;
   const int* bt = p.block_tables + size_t(seq) * p.max_blocks;
   int chunk = (ctx + S - 1) / S;
@@ -489,8 +489,9 @@ __global__ void __launch_bounds__(kPfWarps * 32) k_prefill_attn_mma(const Prefil
   const bool vlo = tlo < nrows, vhi = thi < nrows;
   const int seq = p.seq_of_query ? p.seq_of_query[row0] : row0;
   const int* bt = p.block_tables + size_t(seq) * p.max_blocks;
-  const int ctx_lo = vlo ? p.ctx_lens[row0 + tlo] : 0, ctx_hi = vhi ? p.ctx_lens[row0 + thi] : 0;
-  const int ctx_max = p.ctx_lens[row0 + nrows - 1];             // rows are in position order
+  const int ctx_cap = p.max_blocks * p.block_size;             // never walk past the block table
+  const int ctx_lo = vlo ? min(p.ctx_lens[row0 + tlo], ctx_cap) : 0, ctx_hi = vhi ? min(p.ctx_lens[row0 + thi], ctx_cap) : 0;
+  const int ctx_max = min(p.ctx_lens[row0 + nrows - 1], ctx_cap);   // rows are in position order
   (void)QT;
 
   uint32_t qa[kD / 16][4];

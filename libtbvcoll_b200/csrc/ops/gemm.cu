@@ -185,6 +185,7 @@ struct MapKeyHash {
 };
 std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 std::mutex g_maps_mu;
+int g_persist_mode = -1;   // TBV_GEMM_PERSIST, read on first use; tbv_op_gemm_persist_mode overrides it
 int* g_err_flag[16] = {nullptr};
 int g_sm_count[16] = {0};
 bool g_attr_done = false;
@@ -194,8 +195,11 @@ bool g_attr_done = false;
 namespace tbvops {
 
 // [rows, cols] bf16 row-major with row stride ld (elements); box = box_rows x 64, 128-byte swizzle.
+// The encoded map is a pure function of the arguments (it names addresses, it holds no
+// reference), so the memo below can never go stale; `cache = false` skips it for maps that a
+// caller keeps itself.
 int make_tensor_map_bf16(CUtensorMap* out, const void* ptr, unsigned long long rows, unsigned long long cols,
-                         unsigned long long ld, unsigned box_rows) {
+                         unsigned long long ld, unsigned box_rows, bool cache) {
   std::call_once(g_encode_once, [] {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -204,7 +208,7 @@ int make_tensor_map_bf16(CUtensorMap* out, const void* ptr, unsigned long long r
   });
   if (!g_encode) return -1;
   MapKey key{ptr, rows, cols, ld, box_rows};
-  {
+  if (cache) {
     std::lock_guard<std::mutex> g(g_maps_mu);
     auto it = g_maps.find(key);
     if (it != g_maps.end()) { *out = it->second; return 0; }
@@ -219,7 +223,7 @@ int make_tensor_map_bf16(CUtensorMap* out, const void* ptr, unsigned long long r
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return -3;
-  {
+  if (cache) {
     std::lock_guard<std::mutex> g(g_maps_mu);
     if (g_maps.size() > 65536) g_maps.clear();
     g_maps[key] = m;
@@ -257,7 +261,9 @@ void gemm_config(int M, int N, int K, int splits_hint, int* bn_out, int* splits_
   if (splits_hint > 0) {
     splits = splits_hint;
   } else {
-    while (splits < 8 && tiles * splits * 2 <= 2 * sms && kb / (splits * 2) >= 8) splits *= 2;
+    // a K range per CTA of at least `min_kb` 64-wide blocks (TBV_GEMM_MIN_KB, read once)
+    static const int min_kb = [] { const char* e = getenv("TBV_GEMM_MIN_KB"); int v = e ? atoi(e) : 8; return v < 1 ? 1 : v; }();
+    while (splits < 8 && tiles * splits * 2 <= 2 * sms && kb / (splits * 2) >= min_kb) splits *= 2;
   }
   while (splits > 1 && (kb + splits - 1) / splits * (splits - 1) >= kb) splits /= 2;  // every split gets work
   const int stage_bytes = gemm::kATileBytes + bn * 128;
@@ -274,17 +280,23 @@ void gemm_config(int M, int N, int K, int splits_hint, int* bn_out, int* splits_
 extern "C" {
 
 // y[N, M(/2)] = epilogue(x[N, K] @ w[M, K]^T).  ldx / ldy: row strides in elements.
-// epi: 0 = store (+bias), 1 = SiLU-mul over row-interleaved gate/up weights (M = 2 * out features).
+// epi (low byte): 0 = store (+bias), 1 = SiLU-mul over row-interleaved gate/up weights (M = 2 * out features).
+// CONTRACT: w is treated as a constant — its tiles are fetched before this kernel has waited for its
+// predecessor in the stream (that is what hides the weight stream behind the previous kernel).  If w was
+// written by a kernel launched just before (a dequantised or copied weight, an activation used as w), add
+// TBV_GEMM_W_NOT_CONSTANT (0x100) to epi: the fetch then follows the dependency wait.
 int tbv_op_gemm(const void* w, const void* x, void* y, const void* bias, int M, int N, int K, int ldx, int ldy, int epi,
                 int splits_hint, void* stream) {
+  const int w_not_constant = (epi & 0x100) ? 1 : 0;
+  epi &= 0xff;
   if (M <= 0 || N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || (ldy % 8) || (reinterpret_cast<uintptr_t>(y) & 15u)) return -2;
   if (epi == kEpiSiluMul && (M % 2)) return -2;
   // Hundreds of tokens: the persistent kernel with tokens on the UMMA M axis.  TBV_GEMM_PERSIST: 0 = never,
   // 1 (default) = where it is estimated to be faster, 2 / 3 = its 128- / 256-token tile wherever the shape allows.
-  const char* pe = getenv("TBV_GEMM_PERSIST");
-  const int persist = pe ? atoi(pe) : 1;
+  if (g_persist_mode == -1) { const char* pe = getenv("TBV_GEMM_PERSIST"); g_persist_mode = pe ? atoi(pe) : 1; }  // read once, not per launch
+  const int persist = g_persist_mode;
   if (persist > 0 && splits_hint <= 0) {
-    const int th = tbvops::gemm_tok_choose(M, N, K, ldy, epi, persist);
+    const int th = w_not_constant ? 0 : tbvops::gemm_tok_choose(M, N, K, ldy, epi, persist);   // the many-token kernel always prefetches w
     if (th > 0) return tbvops::gemm_tok_launch(w, x, y, bias, M, N, K, ldx, ldy, epi, th, stream);
   }
   int bn, splits, stages;
@@ -295,6 +307,7 @@ int tbv_op_gemm(const void* w, const void* x, void* y, const void* bias, int M, 
   Params p{};
   p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.bn = bn; p.splits = splits; p.stages = stages;
   p.kb_total = (K + 63) / 64;
+  p.a_after_wait = w_not_constant;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.y = static_cast<__nv_bfloat16*>(y);
   p.limit_ns = 2000000000ull;
@@ -323,6 +336,10 @@ int tbv_op_gemm(const void* w, const void* x, void* y, const void* bias, int M, 
   }
   return 0;
 }
+
+// Many-token kernel selection: 0 never, 1 where estimated faster, 2 / 3 force its 128- / 256-token tile;
+// -1 = take TBV_GEMM_PERSIST from the environment again at the next call.
+void tbv_op_gemm_persist_mode(int mode) { g_persist_mode = mode < -1 ? -1 : mode; }
 
 // 1 if any GEMM wait ever gave up on the current device (synchronises the device).
 int tbv_op_gemm_error(void) {

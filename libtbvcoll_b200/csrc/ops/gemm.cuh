@@ -31,6 +31,7 @@ struct Params {
   int stages;
   int kb_total;        // ceil(K / 64)
   int raster;          // 0: blockIdx.x = feature tile, .y = token tile; 1: swapped (token tiles launch first)
+  int a_after_wait;    // 1: operand A (w) may have been written by the preceding kernel: fetch it only after the dependency wait
   const __nv_bfloat16* bias;  // [M] or null
   __nv_bfloat16* y;
   unsigned long long limit_ns;  // bound on every barrier wait
@@ -93,13 +94,16 @@ __device__ __forceinline__ uint8_t* mainloop(const CUtensorMap* tmA, const CUten
     int issued = 0;
     // Weights are never written by any kernel: start streaming them into the ring before the
     // preceding kernel has finished, then wait for it and fetch the activations.
+    // (Contract: operand A is constant — a weight.  A caller whose A was produced by the kernel just
+    // before this one sets a_after_wait, and the early fetch is skipped.)
     const int pre = nkb < p.stages ? nkb : p.stages;
+    if (p.a_after_wait) pdl::grid_dependency_wait();
     for (int i = 0; i < pre; i++) {
       const uint32_t fb = smem_u32(&s.full[i]);
       mbar_expect_tx(fb, kATileBytes + b_tile_bytes);
       tma_load_2d_hint(a_base + i * kATileBytes, tmA, (kb0 + i) * kBK, m0, fb, pol_w);
     }
-    pdl::grid_dependency_wait();
+    if (!p.a_after_wait) pdl::grid_dependency_wait();
     for (int i = 0; i < pre; i++)
       tma_load_2d_hint(b_base + i * b_tile_bytes, tmB, (kb0 + i) * kBK, n0, smem_u32(&s.full[i]), pol_x);
     issued = pre;

@@ -2,18 +2,26 @@
 // RMSNorm that follows it, in ONE kernel over peer memory:
 //
 //   partial = X[T, K/tp] @ W[H, K/tp]^T            tcgen05 tiles, TMA-fed, TMEM accumulators
-//   every finished tile slice is rounded to bf16 and stored straight into the slot memory of
-//   every rank (plain 8-byte stores through the NVLink peer mappings — the epilogue IS the
-//   transfer), one sequence flag per M tile announces it;
-//   a few CTAs then wait for all tiles of all ranks, add the N copies in rank order in fp32,
-//   round, add the residual, and apply RMSNorm.
+//   GEMM CTAs: every finished tile slice is rounded to bf16 and stored straight into the LL
+//   packet area of EVERY rank (8-byte stores through the NVLink peer mappings, each carrying
+//   4 bytes of payload and the call's sequence number — the epilogue IS the transfer, there is
+//   no fence and no flag), after which the CTA gives its SM back;
+//   finisher CTAs (one per token row, resident from the start of the kernel, first in launch
+//   order): poll the row's packets of all ranks as they land, add the N copies in rank order in
+//   fp32, round, add the residual, and apply RMSNorm.
 //
-// This is what the reference's hook wraps as two separate steps (RowParallelLinear, then
-// GroupCoordinator.all_reduce: step3b/vllm_tp_bench.py:87-124) plus the norm it lists as future
-// work ("fuse k_acc + next RMSNorm", reports/12_references.md:136).  Semantics match the
-// unfused pipeline: the all-reduce operands are bf16, the sum is fp32 in rank order with one
-// rounding, so the residual stream has identical bits; the normalised output can differ in
-// the last bf16 digit because the variance is reduced by a 192-thread CTA here.
+// Nothing waits for a kernel boundary between the GEMM and the reduction, and the GEMM CTAs do
+// not stay for it: the next GEMM's CTAs take over their SMs and stream weights while the
+// finishers run.  This is what the reference's hook wraps as two separate steps
+// (RowParallelLinear, then GroupCoordinator.all_reduce: step3b/vllm_tp_bench.py:87-124) plus the
+// norm it lists as future work ("fuse k_acc + next RMSNorm", reports/12_references.md:136).
+//
+// Semantics are those of the unfused pipeline, bit for bit: the all-reduce operands are the bf16
+// partial sums, the sum is fp32 in rank order with one rounding, and the row normalisation forms
+// its sums in the order of the plain RMSNorm kernel (rmsnorm_row_store_virtual).
+//
+// Messages too large for LL packets (TBV_LL_MAX) are declined (TBV_FALLBACK): the caller composes
+// GEMM + fused all-reduce/norm, or the sequence-parallel GEMM -> reduce-scatter pair.
 //
 // Also here: the emulated-ranks form (blockIdx.y = rank, all ranks on one GPU) used to test
 // the protocol on a single GPU.
@@ -39,34 +47,104 @@ struct FusedPtrs {
   __nv_bfloat16* residual_out[TBV_MAXRANK];
   __nv_bfloat16* y[TBV_MAXRANK];
 };
-constexpr int kMaxWaiters = 128;  // CTAs that stay for the reduce + norm phase (at most half the grid)
-constexpr int kFusedMaxUnits = 6;  // 16-byte units per thread in the norm phase: hidden <= 8 * 6 * 192 = 9216
+// 256 threads and at most 128 registers: two CTAs fit on an SM, like the plain GEMM kernel when its grid is
+// larger than the GPU (512-thread CTAs ran the 256 tiles of a down projection in two waves and doubled its time).
+constexpr int kFusedThreads = 256;   // warps 0..5 have the GEMM roles; all 8 warps work in a finisher CTA
+constexpr int kMaxFinishers = 16;    // finisher CTAs per rank (rows are dealt round robin beyond that)
+constexpr int kFusedVPT = 4;         // 16-byte units per finisher thread: hidden <= 8 * 4 * 256 = 8192
 
-__global__ void __launch_bounds__(gemm::kThreads, 1)
+// grid (fx + m_tiles, ranks, S), cluster (1, 1, S).  blockIdx.x < fx: finisher clusters.
+__global__ void __launch_bounds__(kFusedThreads, 2)
 k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const RankCtx* ctxs, const __grid_constant__ FusedPtrs fp,
-                  const __nv_bfloat16* gamma, float eps, bool ll) {
+                  const __nv_bfloat16* gamma, float eps, int fx, int finishers, int norm_threads, int mute) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ gemm::Smem s;
   __shared__ unsigned long long sh_seq;
   __shared__ float sh_red[32];
   const int er = blockIdx.y;  // (emulated) rank index into the per-rank arrays; 0 for a real rank
+  if (er == mute) return;     // emulated world, host-made fault: this rank never makes the call
   const RankCtx& c = ctxs[er];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tile = blockIdx.x, m0 = m_tile * gemm::kBM;
   const int S = p.splits;
   const int split = S > 1 ? int(cluster_ctarank()) : 0;
+  const int T = p.N, H = p.M;
+  const unsigned n_cta = unsigned(finishers) + unsigned(gridDim.x - fx) * unsigned(S);
+
+  if (int(blockIdx.x) < fx) {
+    // ---------------- finisher: reduce + residual + RMSNorm of its token rows ----------------
+    const int fid = blockIdx.x * S + split;
+    if (fid >= finishers) return;   // padding CTA of the last finisher cluster
+    pdl::launch_dependents();
+    if (threadIdx.x == 0 && fid == 0) c.dm->ts[0] = tbv::globaltimer();   // finisher resident
+    pdl::grid_dependency_wait();    // the previous collective has completed: the device sequence number is stable
+    const unsigned long long t_enter = (threadIdx.x == 0 && fid == 0) ? tbv::globaltimer() : 0;
+    CallInfo ci = call_begin(c, &sh_seq);
+    if (fid == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
+    // While this rank's own GEMM CTAs are still streaming weights, one thread watches a single counter with
+    // a back-off instead of 512 threads hammering the packet lines (which the weight stream shares the L2
+    // with).  All ranks run the same step, so the peers' packets are at most a flight time behind.
+    if (threadIdx.x == 0) {
+      const unsigned n_gemm = unsigned(gridDim.x - fx) * unsigned(S);
+      unsigned long long t0 = 0;
+      for (unsigned spins = 0; *(volatile unsigned*)&c.st->gemm_done < n_gemm; spins++) {
+        __nanosleep(200);
+        if ((spins & 63u) == 63u) {
+          const unsigned long long now = tbv::globaltimer();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > c.wdog_ns || *(volatile unsigned*)&c.st->err != 0u) break;   // the packet wait below reports it
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && fid == 0) { c.dm->ts[1] = t_enter; c.dm->ts[2] = tbv::globaltimer(); }   // dependency passed; own GEMM CTAs have pushed
+    const int upr = H / 8;
+    const unsigned all = (1u << c.world) - 1u;   // own rank included: its GEMM CTAs write packets here too
+    unsigned long long t_ready = 0;
+    for (int row = fid; row < T; row += finishers) {
+      float h[kFusedVPT][8];
+#pragma unroll
+      for (int j = 0; j < kFusedVPT; j++) {
+        const int u = threadIdx.x + j * blockDim.x;
+        if (u < upr) {
+          const size_t off = size_t(row) * upr + u;
+          uint4 got[TBV_MAXRANK];
+          ll_pull_all(c, ci.slot, off, ci.want, all, fid, ci.seq, got);
+          float acc[8];
+          ll_sum_unit<__nv_bfloat16>(c, got, all, got[0], acc);
+          float res[8];
+          Pack<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(fp.residual[er])[off], res);
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const float sum = __bfloat162float(__float2bfloat16_rn(acc[i]));
+            h[j][i] = __bfloat162float(__float2bfloat16_rn(sum + res[i]));
+          }
+          reinterpret_cast<uint4*>(fp.residual_out[er])[off] = Pack<__nv_bfloat16>::pack(h[j]);
+        }
+      }
+      if (row == fid && threadIdx.x == 0 && fid == 0) { t_ready = tbv::globaltimer(); c.dm->bc[2] = ci.seq; c.dm->ts[3] = t_ready; }   // first row's packets pulled
+      rmsnorm_row_store_virtual<kFusedVPT>(h, upr, H, eps, reinterpret_cast<const uint4*>(gamma),
+                                           reinterpret_cast<uint4*>(fp.y[er]) + size_t(row) * upr, sh_red, norm_threads);
+    }
+    if (threadIdx.x == 0 && fid == 0) c.dm->ts[4] = tbv::globaltimer();   // rows normalised
+    call_end(c, ci, n_cta, t_enter, t_ready, size_t(T) * H * 2, TBV_ALGO_LL);
+    return;
+  }
+
+  // ---------------- GEMM CTA: one 128-feature tile over its K range, pushed as LL packets ----------------
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tile = blockIdx.x - fx, m0 = m_tile * gemm::kBM;
+  const bool stamp = blockIdx.x == gridDim.x - 1 && cluster_ctarank() == 0;   // the last tile in launch order
+  if (stamp && threadIdx.x == 0) c.dm->ts[5] = tbv::globaltimer();           // its CTA is resident
   const int kb_per = (p.kb_total + S - 1) / S;
   const int kb0 = split * kb_per;
   int nkb = p.kb_total - kb0;
   nkb = nkb < 0 ? 0 : (nkb > kb_per ? kb_per : nkb);
-  const int T = p.N, H = p.M;
-  const unsigned long long t_enter = (threadIdx.x == 0 && m_tile == 0 && split == 0) ? tbv::globaltimer() : 0;
 
   uint8_t* sm = gemm::mainloop(&maps.a[er], &maps.b[er], p, s, smem_raw, m0, 0, kb0, nkb);
   volatile int* abortp = &s.abort_flag;
   float* stage_f = reinterpret_cast<float*>(sm);
+  const bool epi = warp >= 2 && warp < 6;
 
-  if (warp >= 2) {
+  if (epi) {
     const int quarter = warp & 3, ml = quarter * 32 + lane;
     bool ok = nkb > 0 ? mbar_wait(smem_u32(&s.accum), 0, abortp, p.limit_ns) : true;
     ok = __all_sync(0xffffffffu, ok);
@@ -75,7 +153,7 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
     // previous collective has finished and the device sequence number is stable.
     if (threadIdx.x == 64) {
       sh_seq = *(volatile unsigned long long*)&c.st->seq + 1ull;
-      if (m_tile == 0 && split == 0) c.dm->bc[4] = tbv::globaltimer();  // accumulator ready
+      if (stamp) c.dm->ts[6] = tbv::globaltimer();   // its accumulator is complete
     }
     for (int col = 0; col < p.bn; col += 16) {
       uint32_t r[16];
@@ -93,17 +171,14 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
   __syncwarp();
   if (S > 1) cluster_sync_all(); else __syncthreads();
   CallInfo ci;
-  ci.seq = S > 1 ? 0 : sh_seq;
-  if (S > 1) {
-    // every CTA of the cluster read the same device word; take this CTA's own copy
-    ci.seq = sh_seq;
-  }
+  ci.seq = sh_seq;   // every CTA of the cluster read the same device word; this is the CTA's own copy
   ci.want = unsigned(ci.seq);
   ci.slot = int(ci.seq % (unsigned long long)c.nslot);
 
-  if (warp >= 2) {
+  if (epi) {
     // deterministic split-K (CTA j reduces feature slice j over the cluster's K ranges), then the
-    // bf16 slice goes to EVERY rank's slot region [src = me], own rank included
+    // bf16 slice goes to EVERY rank's LL area [src = me], own rank included: the finishers read all
+    // sources the same way
     const int te = threadIdx.x - 64;
     const int fs = 128 / S, q4 = fs / 4;
     const uint32_t stage_addr = smem_u32(sm);
@@ -123,77 +198,22 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
       uint2 pk;
       pk.x = *reinterpret_cast<uint32_t*>(&lo);
       pk.y = *reinterpret_cast<uint32_t*>(&hi);
-      const size_t off = (size_t(t) * H + m0 + f) * 2;
+      const size_t off = (size_t(t) * H + m0 + f) * 2;   // payload byte offset; packets take twice that
       for (int d = 0; d < c.world; d++) {
         const int peer = (c.rank + d) % c.world;
-        if (ll)  // two self-announcing packets: no fence and no flag are needed afterwards
-          st_v4(ll_region(c, peer, ci.slot, c.rank) + off * 2, pk.x, ci.want, pk.y, ci.want);
-        else
-          *reinterpret_cast<uint2*>(slot_region(c, peer, ci.slot, c.rank) + off) = pk;
+        st_v4(ll_region(c, peer, ci.slot, c.rank) + off * 2, pk.x, ci.want, pk.y, ci.want);
       }
     }
   }
-  // One flag per M tile covers all K-split slices: the cluster barrier below (release/acquire)
-  // orders every CTA's stores before the publishing thread's system-scope fence, which is
-  // cumulative.  (A fence per CTA was measured: +4 us per call, no change in results.)
   __syncwarp();
-  if (S > 1) cluster_sync_all(); else __syncthreads();  // all slices of this M tile are stored; peers' shared memory no longer needed
-  gemm::teardown(p, s);                                   // TMEM back before the waiting phase
-  if (!ll && split == 0 && threadIdx.x == 0) {
-    fence_sys();
-    for (int peer = 0; peer < c.world; peer++)
-      st_relaxed_sys(c.flags[peer] + flag_index(c, ci.slot, 0, c.rank, m_tile), ci.want);
-    if (m_tile == 0) { c.dm->bc[1] = ci.seq; c.dm->bc[5] = tbv::globaltimer(); }  // flag published
-  }
-
-  // ---- a few CTAs finish the job: wait for every tile of every rank, reduce, residual, norm ----
-  const int n_cta = gridDim.x * S, cta_id = m_tile * S + split;
-  int waiters = T < kMaxWaiters ? T : kMaxWaiters;
-  if (waiters > n_cta / 2) waiters = n_cta / 2 > 0 ? n_cta / 2 : 1;
-  unsigned long long t_ready = 0;
-  if (cta_id < waiters) {
-    const int n_tiles = gridDim.x;
-    if (!ll) {
-      for (int i = threadIdx.x; i < c.world * n_tiles; i += blockDim.x) {
-        const int src = i / n_tiles, ch = i % n_tiles;
-        wait_flag(c, c.flags[c.rank] + flag_index(c, ci.slot, 0, src, ch), ci.want, kWhereFused, src, ch, ci.seq);
-      }
-      __syncthreads();
-    }
-    if (threadIdx.x == 0 && cta_id == 0) { t_ready = tbv::globaltimer(); c.dm->bc[2] = ci.seq; c.dm->bc[6] = t_ready; }
-    const int upr = H / 8;
-    for (int row = cta_id; row < T; row += waiters) {
-      float h[kFusedMaxUnits][8];
-#pragma unroll
-      for (int k = 0; k < kFusedMaxUnits; k++) {
-        const int u = threadIdx.x + k * blockDim.x;
-        if (u < upr) {
-          const size_t off = size_t(row) * upr + u;
-          float acc[8];
-          for (int r = 0; r < c.world; r++) {
-            uint4 v = ll ? ll_pull_unit(c, ci.slot, r, off, ci.want, m_tile, ci.seq)
-                         : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, ci.slot, r)) + off);
-            float f[8];
-            Pack<__nv_bfloat16>::unpack(v, f);
-#pragma unroll
-            for (int i = 0; i < 8; i++) acc[i] = (r == 0) ? f[i] : acc[i] + f[i];
-          }
-          float res[8];
-          Pack<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(fp.residual[er])[off], res);
-#pragma unroll
-          for (int i = 0; i < 8; i++) {
-            const float sum = __bfloat162float(__float2bfloat16_rn(acc[i]));
-            h[k][i] = __bfloat162float(__float2bfloat16_rn(sum + res[i]));
-          }
-          reinterpret_cast<uint4*>(fp.residual_out[er])[off] = Pack<__nv_bfloat16>::pack(h[k]);
-        }
-      }
-      rmsnorm_row_store<kFusedMaxUnits>(h, upr, H, eps, reinterpret_cast<const uint4*>(gamma),
-                                        reinterpret_cast<uint4*>(fp.y[er]) + size_t(row) * upr, sh_red);
-    }
-  }
-  if (threadIdx.x == 0 && cta_id == 0) c.dm->bc[7] = t_enter;  // with bc[4..6]: time stamps of the last fused call
-  call_end(c, ci, unsigned(n_cta), t_enter, t_ready, size_t(T) * H * 2, TBV_ALGO_ONESHOT);
+  if (S > 1) cluster_sync_all(); else __syncthreads();  // peers' shared memory is no longer needed; this CTA's packets are issued
+  if (threadIdx.x == 0) {
+    atomicAdd(&c.st->gemm_done, 1u);
+    if (stamp) c.dm->ts[7] = tbv::globaltimer();     // its packets are issued
+  }  // tells this rank's finishers when to start looking at packets (a hint, not an ordering)
+  gemm::teardown(p, s);
+  if (m_tile == 0 && split == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
+  call_end(c, ci, n_cta, 0, 0, size_t(T) * H * 2, TBV_ALGO_LL);
 }
 
 bool g_attr_done = false;
@@ -209,25 +229,40 @@ static int launch_fused(tbv_comm* c, const void* const* ws, const void* const* x
   if (c->sticky_err.load()) return TBV_FAIL;
   for (auto& g : c->ranks)
     if (*(volatile unsigned*)&g.hm->err != 0) { c->sticky_err.store(1); return TBV_FAIL; }
-  if (tokens <= 0 || tokens > 256 || hidden % 128 || hidden / 128 > TBV_MAXCHAN || hidden > 8 * kFusedMaxUnits * gemm::kThreads ||
-      (k_local % 8) || (ldx % 8) || size_t(tokens) * hidden * 2 > c->cap)
+  const size_t nbytes = size_t(tokens) * hidden * 2;
+  // every condition below depends on the shape and the knobs only, so all ranks decide alike
+  if (tokens <= 0 || tokens > 256 || hidden % 128 || hidden > 8 * kFusedVPT * kFusedThreads || (k_local % 8) || (ldx % 8)) return TBV_FALLBACK;
+  if (!(c->knobs.algo == TBV_ALGO_AUTO || c->knobs.algo == TBV_ALGO_LL) || nbytes * 2 > c->ll_cap || long(nbytes) > c->knobs.ll_max)
     return TBV_FALLBACK;
+  for (int r = 0; r < nr; r++)
+    if ((reinterpret_cast<uintptr_t>(residuals[r]) | reinterpret_cast<uintptr_t>(residual_outs[r]) | reinterpret_cast<uintptr_t>(ys[r]) |
+         reinterpret_cast<uintptr_t>(gamma)) & 15u)
+      return TBV_FAIL;   // a per-rank property: declining would leave the other ranks alone in the call
   if (c->skip.load() > 0) { c->skip.fetch_sub(1); return TBV_OK; }
   int bn, splits, stages;
   tbvops::gemm_config(hidden, tokens, k_local, 0, &bn, &splits, &stages);
   if ((tokens + bn - 1) / bn != 1) return TBV_FALLBACK;
+  const int finishers = tokens < kMaxFinishers ? tokens : kMaxFinishers;
   if (c->local) {
-    // emulated ranks share one GPU without a cooperative launch: keep the whole grid resident
-    while (splits > 1 && (hidden / 128) * splits * nr > tbvops::sm_count()) splits /= 2;
-    if ((hidden / 128) * splits * nr > tbvops::sm_count()) return TBV_FALLBACK;
-    tbvops::gemm_config(hidden, tokens, k_local, splits, &bn, &splits, &stages);
+    // Emulated ranks share one GPU and their CTAs wait on one another: keep every finisher and at least
+    // one more cluster resident at any time.
+    if (nr * ((finishers + splits - 1) / splits) * splits + splits > tbvops::sm_count()) return TBV_FALLBACK;
+  }
+  const int fx = (finishers + splits - 1) / splits;
+  // Always the two-CTAs-per-SM shared-memory budget: the finisher CTAs inherit the launch configuration
+  // (cluster shape, dynamic shared memory) of the GEMM CTAs, and the next kernel's CTAs must find room beside
+  // this kernel's finishers, or they cannot stream their weights while the finishers wait for the peers.
+  {
+    const int stage_bytes = gemm::kATileBytes + bn * 128;
+    const int fit = (108 * 1024) / stage_bytes;
+    if (stages > fit) stages = fit < 2 ? 2 : fit;
   }
   while (stages * (gemm::kATileBytes + bn * 128) < bn * 512) stages++;  // fp32 staging reuses the ring
   Maps maps;
   FusedPtrs fp{};
   for (int r = 0; r < nr; r++) {
-    if (tbvops::make_tensor_map_bf16(&maps.a[r], ws[r], hidden, k_local, k_local, 128) != 0) return TBV_FALLBACK;
-    if (tbvops::make_tensor_map_bf16(&maps.b[r], xs[r], tokens, k_local, ldx, bn) != 0) return TBV_FALLBACK;
+    if (tbvops::make_tensor_map_bf16(&maps.a[r], ws[r], hidden, k_local, k_local, 128) != 0) return TBV_FAIL;
+    if (tbvops::make_tensor_map_bf16(&maps.b[r], xs[r], tokens, k_local, ldx, bn) != 0) return TBV_FAIL;
     fp.residual[r] = static_cast<const __nv_bfloat16*>(residuals[r]);
     fp.residual_out[r] = static_cast<__nv_bfloat16*>(residual_outs[r]);
     fp.y[r] = static_cast<__nv_bfloat16*>(ys[r]);
@@ -243,10 +278,11 @@ static int launch_fused(tbv_comm* c, const void* const* ws, const void* const* x
     g_attr_done = true;
   }
   const RankCtx* ctxs = c->ctxs_dev;
-  const size_t nbytes = size_t(tokens) * hidden * 2;
-  const bool ll = (c->knobs.algo == TBV_ALGO_AUTO || c->knobs.algo == TBV_ALGO_LL) && nbytes * 2 <= c->ll_cap && long(nbytes) <= c->knobs.ll_max;
-  cudaError_t e = pdl::launch(k_gemm_ar_rmsnorm, dim3(hidden / 128, nr, splits), dim3(gemm::kThreads), smem,
-                              static_cast<cudaStream_t>(stream), splits, maps, p, ctxs, fp, static_cast<const __nv_bfloat16*>(gamma), eps, ll);
+  int mute = -1;
+  if (c->local && c->mute_left.load() > 0) { c->mute_left.fetch_sub(1); mute = c->mute_rank; }
+  cudaError_t e = pdl::launch(k_gemm_ar_rmsnorm, dim3(fx + hidden / 128, nr, splits), dim3(kFusedThreads), smem,
+                              static_cast<cudaStream_t>(stream), splits, maps, p, ctxs, fp, static_cast<const __nv_bfloat16*>(gamma), eps,
+                              fx, finishers, tbvops::norm_threads(hidden), mute);
   if (e != cudaSuccess) {
     fprintf(stderr, "[tbvcoll] fused gemm+all-reduce launch failed: %s\n", cudaGetErrorString(e));
     c->sticky_err.store(1);
@@ -260,7 +296,9 @@ extern "C" {
 
 // y = RMSNorm(h) * gamma with h = bf16(sum over ranks of bf16(x @ w^T)) + residual; residual_out = h.
 // x: [tokens, k_local] (row stride ldx), w: [hidden, k_local] — this rank's shard of a row-parallel layer.
-// tokens <= 256, hidden % 128 == 0.  TBV_FALLBACK (-2): compose gemm + all-reduce + add-norm instead.
+// hidden % 128 == 0, hidden <= 8192, tokens * hidden * 2 bytes within the LL packet limit (TBV_LL_MAX).
+// TBV_FALLBACK (-2): compose gemm + all-reduce + add-norm instead (decided from shape and knobs only,
+// so every rank gets the same answer).
 int tbv_comm_gemm_allreduce_rmsnorm(tbv_comm* c, const void* w, const void* x, const void* residual, const void* gamma,
                                     void* residual_out, void* y, int tokens, int hidden, int k_local, int ldx, float eps,
                                     void* stream) {

@@ -20,8 +20,7 @@
 #include <cuda_runtime.h>
 #include <stdio.h>
 
-#include <map>
-#include <tuple>
+#include <vector>
 
 #include "../comm.h"
 #include "gemm.cuh"
@@ -301,26 +300,24 @@ int set_attrs() {
   return 0;
 }
 
-// device arrays of tensor maps over the gather buffers, one per (comm, emulated rank, rows, K, bn)
-std::map<std::tuple<const void*, int, int, int, int>, CUtensorMap*> g_gather_maps;
-
+// Device array of tensor maps over the gather buffers of (emulated) rank `er`, one map per (slot, source).
+// The communicator owns it (built on first use per shape, freed in tbv_comm_destroy): the maps name
+// addresses inside that communicator's slot memory and must not outlive it.
 const CUtensorMap* gather_maps(tbv_comm* c, int er, int rows_per_rank, int K, int bn) {
-  auto key = std::make_tuple(static_cast<const void*>(c), er, rows_per_rank, K, bn);
-  auto it = g_gather_maps.find(key);
-  if (it != g_gather_maps.end()) return it->second;
-  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  auto key = std::make_tuple(er, rows_per_rank, K, bn);
+  auto it = c->gather_maps.find(key);
+  if (it != c->gather_maps.end()) return static_cast<const CUtensorMap*>(it->second);
   const RankCtx& x = c->ranks[er].ctx;
   std::vector<CUtensorMap> host(size_t(x.nslot) * x.world);
   for (int slot = 0; slot < x.nslot; slot++)
     for (int src = 0; src < x.world; src++) {
       const char* base = x.data[x.rank] + size_t(slot) * x.slot_stride + size_t(src) * x.cap;
-      if (tbvops::make_tensor_map_bf16(&host[size_t(slot) * x.world + src], base, rows_per_rank, K, K, bn) != 0) return nullptr;
+      if (tbvops::make_tensor_map_bf16(&host[size_t(slot) * x.world + src], base, rows_per_rank, K, K, bn, /*cache=*/false) != 0) return nullptr;
     }
-  (void)cs;
   CUtensorMap* dev = nullptr;
   if (cudaMalloc(&dev, host.size() * sizeof(CUtensorMap)) != cudaSuccess) return nullptr;  // first use must not be under stream capture
-  if (cudaMemcpy(dev, host.data(), host.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
-  g_gather_maps[key] = dev;
+  if (cudaMemcpy(dev, host.data(), host.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(dev); return nullptr; }
+  c->gather_maps[key] = dev;
   return dev;
 }
 

@@ -201,7 +201,7 @@ __global__ void k_decode_advance(const long long* __restrict__ next_ids, long lo
     if (history && step < max_steps) history[size_t(step) * batch + b] = tok;
     const int pos = positions[b] + 1;
     positions[b] = pos;
-    ctx_lens[b] = pos + 1;
+    ctx_lens[b] = min(pos + 1, max_blocks * block_size);   // past the reserved length the step still runs, over the last full context
     const int blk = pos / block_size;
     slot_mapping[b] = blk < max_blocks ? (long long)block_tables[size_t(b) * max_blocks + blk] * block_size + pos % block_size : -1;
   }

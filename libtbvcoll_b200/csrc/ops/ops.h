@@ -4,7 +4,7 @@
 
 namespace tbvops {
 int make_tensor_map_bf16(CUtensorMap* out, const void* ptr, unsigned long long rows, unsigned long long cols,
-                         unsigned long long ld, unsigned box_rows);
+                         unsigned long long ld, unsigned box_rows, bool cache = true);
 int* gemm_err_flag();
 int sm_count();
 void gemm_config(int M, int N, int K, int splits_hint, int* bn_out, int* splits_out, int* stages_out);

@@ -57,11 +57,11 @@ struct Stats {
     t_pre = t_acc = t_post = t_enq = t_drain = 0;
     n_acc = n_enq = 0;
   }
-  void dump_hist(int rank, unsigned long long tag_bad) {
+  void dump_hist(int rank, unsigned long long tag_bad, unsigned long long tag_checked = 0) {
     std::lock_guard<std::mutex> g(mu);
     static const char* an[8] = {"auto", "oneshot", "twoshot", "nvls", "ll", "?", "?", "?"};
-    fprintf(stderr, "[tbvcoll] rank %d hist: streams=%llu switches=%llu fallbacks=%llu tag_bad=%llu\n", rank,
-            streams_seen, stream_switches, fallbacks, tag_bad);
+    fprintf(stderr, "[tbvcoll] rank %d hist: streams=%llu switches=%llu fallbacks=%llu tag_checked=%llu tag_bad=%llu\n", rank,
+            streams_seen, stream_switches, fallbacks, tag_checked, tag_bad);
     for (int b = 0; b < 32; b++) {
       if (!hb_n[b]) continue;
       int best = 1;

@@ -118,6 +118,17 @@ int tbv_comm_set_wdog(tbv_comm* c, double seconds);  // device + host watchdog
 // Fault injection on the HOST: the next `n` collective calls on this rank return
 // TBV_OK without launching/queueing anything, so the peers' bounded waits run out.
 int tbv_comm_skip_next(tbv_comm* c, int n);
+// Emulated world only, also on the host: for the next `n` collective launches the CTAs of
+// emulated rank `r` return before they push anything — a rank that never makes the call.  The
+// other ranks' bounded waits run out, the kernel ends, tbv_comm_err turns sticky and
+// tbv_comm_last_error names `r`.  This is how the device watchdog is exercised on one GPU.
+int tbv_comm_mute_rank(tbv_comm* c, int r, int n);
+// Device time stamps of the last fused GEMM + all-reduce + norm call on (emulated) rank r (see comm.cu).
+int tbv_comm_timestamps(tbv_comm* c, int r, unsigned long long out[8]);
+// TBV_TAG=1 diagnostic: every flag a rank raises is preceded by a sequence stamp in a word of
+// its own next to the flag; the receiver compares it after it has seen the flag.  Totals since
+// the communicator was created (synchronous device-to-host copy).
+int tbv_comm_tag_counts(tbv_comm* c, unsigned long long* checked, unsigned long long* bad);
 // Peer-visible buffers for fused producers (GEMM epilogues push straight into them).
 // Fills a device-side context blob (tbv::RankCtx) the fused kernels take by value.
 int tbv_comm_ctx(tbv_comm* c, void* ctx_out, size_t ctx_bytes);

@@ -33,6 +33,8 @@ def lib():
     I, F, LL, SZ = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_size_t
     l.tbv_op_gemm.argtypes = [c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, I, I, c_vp]
     l.tbv_op_gemm_error.restype = I
+    l.tbv_op_gemm_persist_mode.argtypes = [I]
+    l.tbv_op_gemm_persist_mode.restype = None
     l.tbv_op_gemm_qkv_rope.argtypes = [c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, I, c_vp]
     l.tbv_op_gemm_qkv_rope.restype = I
     l.tbv_op_gemm_config.argtypes = [I, I, I, I, ctypes.POINTER(I), ctypes.POINTER(I), ctypes.POINTER(I)]
@@ -74,6 +76,12 @@ def _chk(rc: int, name: str):
         raise RuntimeError(f"{name} failed rc={rc}")
 
 
+def gemm_persist_mode(mode: Optional[int]) -> None:
+    """Selection of the many-token (persistent) GEMM: 0 never, 1 where it is estimated faster, 2 / 3 force
+    its 128- / 256-token tile; None = read ``TBV_GEMM_PERSIST`` again (the library reads it once)."""
+    lib().tbv_op_gemm_persist_mode(-1 if mode is None else int(mode))
+
+
 launch_count = 0  # kernels launched through this module (for the bench's gpu_launches claim)
 
 
@@ -86,10 +94,15 @@ EPI_STORE, EPI_SILU_MUL = 0, 1
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
-         epi: int = EPI_STORE, splits: int = 0) -> torch.Tensor:
+         epi: int = EPI_STORE, splits: int = 0, w_is_constant: bool = True) -> torch.Tensor:
     """out[N, M] = x[N, K] @ w[M, K]^T (+ bias) on tcgen05 tensor cores.  ``epi=EPI_SILU_MUL``:
     ``w`` holds gate/up rows interleaved (row 2i = gate_i, row 2i+1 = up_i) and
-    out[N, M/2] = silu(gate) * up."""
+    out[N, M/2] = silu(gate) * up.
+
+    ``w`` is treated as a constant (a weight): the kernel starts fetching its tiles before it has
+    waited for the kernel launched before it.  Pass ``w_is_constant=False`` when ``w`` was produced
+    by the preceding kernel on the stream (a copied or dequantised weight, an activation used as
+    ``w``); the fetch then follows the dependency wait."""
     assert x.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and x.is_cuda and w.is_contiguous()
     assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.stride(1) == 1
     N, K = x.shape
@@ -98,7 +111,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, b
     if out is None:
         out = torch.empty((N, om), dtype=torch.bfloat16, device=x.device)
     assert out.shape == (N, om) and out.stride(1) == 1
-    _chk(lib().tbv_op_gemm(_p(w), _p(x), _p(out), _p(bias), M, N, K, x.stride(0), out.stride(0), epi, splits, _st()), "tbv_op_gemm")
+    _chk(lib().tbv_op_gemm(_p(w), _p(x), _p(out), _p(bias), M, N, K, x.stride(0), out.stride(0), epi | (0 if w_is_constant else 0x100), splits, _st()),
+         "tbv_op_gemm")
     _count()
     return out
 

@@ -18,14 +18,23 @@ from ..tbvcoll import Comm
 
 
 class TPGroup:
+    """``comm=None`` with ``world > 1`` sends every collective to ``torch.distributed`` (NCCL on GPUs):
+    the same model code then runs on the library this one replaces, which is how the benchmark's
+    same-engine NCCL arm is built (the reference's own experiment: one engine, the all-reduce swapped,
+    step3b/vllm_tp_bench.py:119-124).  ``local_stand_in=True`` replaces every collective by its local
+    arithmetic on this rank's partial result (no communication, wrong values): one GPU can then run
+    one rank's shard of a TP=N model to attribute the compute part of a step kernel by kernel."""
+
     def __init__(self, rank: int = 0, world: int = 1, comm: Optional[Comm] = None, fallback_group=None,
-                 fused_norm_max_bytes: int = 1 << 20):
+                 fused_norm_max_bytes: int = 1 << 20, local_stand_in: bool = False):
         self.rank, self.world, self.comm = rank, world, comm
         self.fallback_group = fallback_group
         self.fused_norm_max_bytes = fused_norm_max_bytes
-        # One-kernel GEMM + all-reduce + norm.  Off by default: at decode sizes the two-kernel form
-        # (GEMM, then fused all-reduce + norm overlapped by programmatic dependent launch) measures
-        # faster; TBV_FUSE_GEMM_AR=1 selects the single kernel.
+        self.local_stand_in = local_stand_in
+        # One-kernel GEMM + all-reduce + norm (LL packets from the GEMM epilogue, finisher CTAs reduce and
+        # normalise; same bits as the two-kernel form).  Off by default: measured slower than GEMM followed
+        # by the fused all-reduce + norm kernel (the finisher CTAs inherit the GEMM's cluster shape and shared
+        # memory, which keeps the next kernel's CTAs from becoming resident early).  TBV_FUSE_GEMM_AR=1 selects it.
         self.fuse_gemm = os.environ.get("TBV_FUSE_GEMM_AR", "0") == "1"
         self.calls = 0
         self.fallbacks = 0
@@ -33,6 +42,8 @@ class TPGroup:
 
     # -- plain collectives ---------------------------------------------------------------
     def _fallback_all_reduce(self, x: torch.Tensor) -> None:
+        if self.local_stand_in:
+            return
         self.fallbacks += 1
         if self.fallback_group is None and not (torch.distributed.is_available() and torch.distributed.is_initialized()):
             raise RuntimeError("tbvcoll declined the call and no torch.distributed fallback is initialised")
@@ -63,6 +74,9 @@ class TPGroup:
         if self.comm is not None and self.comm.all_gather(x, out):
             self.launches += 1
             return out
+        if self.local_stand_in:
+            out.view(self.world, -1).copy_(x.reshape(1, -1).expand(self.world, -1))
+            return out
         self.fallbacks += 1
         torch.distributed.all_gather_into_tensor(out, x, group=self.fallback_group)
         return out
@@ -74,6 +88,9 @@ class TPGroup:
         self.calls += 1
         if self.comm is not None and self.comm.reduce_scatter(x, out):
             self.launches += 1
+            return out
+        if self.local_stand_in:
+            out.view(-1).copy_(x.view(self.world, -1)[self.rank])
             return out
         self.fallbacks += 1
         torch.distributed.reduce_scatter_tensor(out, x, group=self.fallback_group)

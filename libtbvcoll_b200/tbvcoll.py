@@ -97,6 +97,10 @@ def load_library(so: Optional[str] = None) -> ctypes.CDLL:
     l.tbv_comm_set_nchan.argtypes = [c_vp, ctypes.c_int]
     l.tbv_comm_set_wdog.argtypes = [c_vp, ctypes.c_double]
     l.tbv_comm_skip_next.argtypes = [c_vp, ctypes.c_int]
+    l.tbv_comm_mute_rank.argtypes = [c_vp, ctypes.c_int, ctypes.c_int]
+    l.tbv_comm_mute_rank.restype = ctypes.c_int
+    l.tbv_comm_tag_counts.argtypes = [c_vp, c_ullp, c_ullp]
+    l.tbv_comm_tag_counts.restype = ctypes.c_int
     l.tbv_comm_ctx.argtypes = [c_vp, c_vp, ctypes.c_size_t]
     l.tbv_comm_stats5.argtypes = [c_vp] + [c_dp] * 5 + [c_ullp]
     l.tbv_comm_rails.argtypes = [c_vp]
@@ -104,6 +108,8 @@ def load_library(so: Optional[str] = None) -> ctypes.CDLL:
     l.tbv_comm_last_error.argtypes = [c_vp, c_ullp]
     l.tbv_comm_breadcrumbs.argtypes = [c_vp, ctypes.c_int, c_ullp]
     l.tbv_comm_breadcrumbs.restype = ctypes.c_int
+    l.tbv_comm_timestamps.argtypes = [c_vp, ctypes.c_int, c_ullp]
+    l.tbv_comm_timestamps.restype = ctypes.c_int
     for n in ("tbv_comm_create", "tbv_comm_create_local", "tbv_comm_destroy", "tbv_comm_allreduce", "tbv_comm_allreduce_local",
               "tbv_comm_allreduce_rmsnorm", "tbv_comm_allreduce_rmsnorm_local", "tbv_comm_reduce_scatter", "tbv_comm_all_gather",
               "tbv_comm_sync", "tbv_comm_set_algo", "tbv_comm_set_nchan", "tbv_comm_set_wdog", "tbv_comm_skip_next", "tbv_comm_ctx"):
@@ -383,6 +389,19 @@ class Comm:
         """Host-side fault injection: this rank silently drops its next ``n`` calls."""
         self._l.tbv_comm_skip_next(self._h, n)
 
+    def mute_rank(self, r: int, n: int = 1) -> None:
+        """Emulated world, host-side fault injection: emulated rank ``r`` sits out the next ``n``
+        collective launches (its CTAs return before pushing), so the others' bounded waits run out."""
+        if self._l.tbv_comm_mute_rank(self._h, r, n) != 0:
+            raise RuntimeError("tbv_comm_mute_rank: needs an emulated world and a valid rank")
+
+    def tag_counts(self):
+        """(checked, bad) sequence stamps since creation (``TBV_TAG=1``; both 0 otherwise)."""
+        a, b = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+        if self._l.tbv_comm_tag_counts(self._h, ctypes.byref(a), ctypes.byref(b)) != 0:
+            raise RuntimeError("tbv_comm_tag_counts failed")
+        return a.value, b.value
+
     def last_error(self):
         a = (ctypes.c_ulonglong * 4)()
         self._l.tbv_comm_last_error(self._h, a)
@@ -393,6 +412,13 @@ class Comm:
         a = (ctypes.c_ulonglong * 8)()
         if self._l.tbv_comm_breadcrumbs(self._h, r, a) != 0:
             raise RuntimeError("tbv_comm_breadcrumbs failed")
+        return list(a)
+
+    def timestamps(self, r: int = 0):
+        """%globaltimer stamps (ns) of the last fused GEMM + all-reduce + norm call (see tbv_comm_timestamps)."""
+        a = (ctypes.c_ulonglong * 8)()
+        if self._l.tbv_comm_timestamps(self._h, r, a) != 0:
+            raise RuntimeError("tbv_comm_timestamps failed")
         return list(a)
 
     def stats5(self):

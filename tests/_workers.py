@@ -332,15 +332,17 @@ def gpu_engine_tp(rank, world, port):
     eng2 = Engine(cfg, tp, device=dev, source=src, max_batch=4, max_seq_len=128, prefill_chunk=64)
     eng2.sp_prefill = False
     d = eng2.generate(prompts, 10, loop="host")
-    # and with the single-kernel GEMM + all-reduce + norm in the decode step
+    # and with the single-kernel GEMM + all-reduce + norm instead of the two-kernel form (GEMM, then fused
+    # all-reduce + norm) that the engines above used: same bits, so the same tokens
+    fused_was = tp.fuse_gemm
     tp.fuse_gemm = True
     eng3 = Engine(cfg, tp, device=dev, source=src, max_batch=4, max_seq_len=128, prefill_chunk=64)
     e = eng3.generate(prompts, 10, loop="host")
-    tp.fuse_gemm = False
+    tp.fuse_gemm = fused_was
     agree = sum(int(x == y) for xs_, ys_ in zip(a, e) for x, y in zip(xs_, ys_)) / sum(len(x) for x in a)
     out = {"hash": h(a), "loops_equal": h(a) == h(b) == h(cc), "logit_err": err, "logit_scale": want.abs().max().item(),
            "fallbacks": tp.fallbacks, "launches_per_step": eng.launches_per_step, "sp_chunks": eng.sp_chunks,
-           "sp_equals_allreduce_path": h(a) == h(d), "fused_gemm_token_agreement": agree}
+           "sp_equals_allreduce_path": h(a) == h(d), "fused_gemm_token_agreement": agree, "fused_gemm_default": fused_was}
     c.destroy()
     return out
 
@@ -394,29 +396,38 @@ def gpu_fused_gemm_ar(rank, world, port):
     dev = f"cuda:{rank}"
     out = {"ok": True, "hashes": []}
     c = Comm(rank, world, rank, "127.0.0.1", port, cap_bytes=64 * 4096 * 2)
-    for T, H, K in ((8, 4096, 2048), (1, 4096, 7168), (64, 4096, 2048), (33, 1024, 512)):
+    out["declined"] = []
+    for T, H, K in ((8, 4096, 2048), (1, 4096, 7168), (16, 8192, 1024), (33, 1024, 512), (64, 4096, 2048)):
         g = torch.Generator().manual_seed(T + H)
         xs = [torch.randn(T, K, generator=g).to(torch.bfloat16) for _ in range(world)]
         ws = [(torch.randn(H, K, generator=g) * 0.03).to(torch.bfloat16) for _ in range(world)]
         res0 = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
         gamma = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).to(dev)
         x, w = xs[rank].to(dev), ws[rank].to(dev)
-        for rep in range(3):
+        took = True
+        for rep in range(6):      # more calls than slots
             res, y = res0.clone(), torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
-            assert c.gemm_all_reduce_rmsnorm(x, w, res, gamma, 1e-5, y)
+            took = c.gemm_all_reduce_rmsnorm(x, w, res, gamma, 1e-5, y)
+            if not took:
+                break
             torch.cuda.synchronize()
+        if not took:
+            # above the LL packet limit of this world size: declined from the shape alone, on every rank alike
+            out["declined"].append((T, H, K))
+            out["ok"] &= T * H * 2 > (128 << 10)
+            continue
         partials = [ref.gemm(a.to(dev), b.to(dev)).to(torch.bfloat16) for a, b in zip(xs, ws)]
         want_y, want_h = ref.ar_residual_rmsnorm(partials, res0, gamma, 1e-5)
         eh = (res.float() - want_h.float()).abs().max().item() / want_h.float().abs().max().item()
         ey = (y.float() - want_y.float()).abs().max().item() / want_y.float().abs().max().item()
         out["ok"] &= eh <= 2 ** -6 and ey <= 2 ** -5
         out["hashes"].append(hashlib.sha256(res.cpu().view(torch.int16).numpy().tobytes() + y.cpu().view(torch.int16).numpy().tobytes()).hexdigest())
-        # the two-kernel composition gives the same residual stream bit for bit
+        # the two-kernel composition gives the same residual stream AND the same normalised output, bit for bit
         part = ops.gemm(x, w)
         res2 = res0.clone()
         assert c.all_reduce_rmsnorm(part, res2, gamma, 1e-5)
         torch.cuda.synchronize()
-        out["ok"] &= bool(torch.equal(res2, res))
+        out["ok"] &= bool(torch.equal(res2, res)) and bool(torch.equal(part, y))
     out["err"] = c.err()
     c.destroy()
     return out

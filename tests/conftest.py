@@ -23,3 +23,12 @@ def free_port() -> int:
 @pytest.fixture
 def port():
     return free_port()
+
+
+@pytest.fixture
+def persist_mode():
+    """Setter for the many-token GEMM selection (0 never, 2 / 3 forced tile shapes); the
+    environment's choice is restored afterwards."""
+    from libtbvcoll_b200 import ops
+    yield ops.gemm_persist_mode
+    ops.gemm_persist_mode(None)

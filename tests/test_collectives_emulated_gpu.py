@@ -132,11 +132,14 @@ def test_fused_allreduce_residual_rmsnorm(world, T, H):
         c.destroy()
 
 
-@pytest.mark.parametrize("world,T,H,K", [(2, 8, 512, 256), (4, 5, 1024, 1024), (2, 64, 4096, 2048), (2, 130, 512, 512)])
+@pytest.mark.parametrize("world,T,H,K", [(2, 8, 512, 256), (4, 5, 1024, 1024), (2, 32, 4096, 2048), (2, 130, 512, 512),
+                                         (8, 8, 4096, 512), (4, 8, 8192, 1024), (8, 1, 4096, 1792)])
 def test_fused_gemm_allreduce_residual_rmsnorm_emulated(world, T, H, K):
-    """Row-parallel GEMM whose epilogue stores into every rank's slot memory, then reduce +
-    residual + RMSNorm, all in one kernel; ranks emulated on one GPU."""
+    """Row-parallel GEMM whose epilogue stores LL packets into every rank's memory while finisher CTAs
+    reduce + residual + RMSNorm the rows as they land, all in one kernel; ranks emulated on one GPU.
+    Must equal the unfused pipeline (GEMM, all-reduce, add+norm op) bit for bit."""
     from libtbvcoll_b200.tbvcoll import Comm
+    from libtbvcoll_b200 import ops
     from libtbvcoll_b200.ops import reference as ref
     c = Comm.local(world, 0, cap_bytes=T * H * 2)
     try:
@@ -145,20 +148,161 @@ def test_fused_gemm_allreduce_residual_rmsnorm_emulated(world, T, H, K):
         ws = [(torch.randn(H, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV) for _ in range(world)]
         res0 = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
         gamma = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).to(DEV)
-        for rep in range(3):      # several calls: slot ring and sequence numbers advance
+        # unfused pipeline on the same kernels: GEMM per rank, exact all-reduce, add + norm
+        parts = [ops.gemm(x, w) for x, w in zip(xs, ws)]
+        summed = [torch.empty_like(p) for p in parts]
+        assert c.all_reduce_local(parts, summed)
+        y_unf, h_unf = ops.add_rmsnorm(summed[0].clone(), res0.clone(), gamma, 1e-5)
+        torch.cuda.synchronize()
+        for rep in range(6):      # more calls than slots: slot ring and sequence numbers advance
             res = [res0.clone() for _ in range(world)]
             ys = [torch.zeros(T, H, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
             ok = c.gemm_all_reduce_rmsnorm_local(xs, ws, res, gamma, 1e-5, ys)
             assert ok, "the fused kernel declined a shape it should take"
             torch.cuda.synchronize()
             assert not c.err()
-            partials = [ref.gemm(x, w).to(torch.bfloat16) for x, w in zip(xs, ws)]
-            want_y, want_h = ref.ar_residual_rmsnorm(partials, res0, gamma, 1e-5)
             for r in range(world):
-                assert torch.equal(res[r], res[0]) and torch.equal(ys[r], ys[0])         # identical bits on every rank
-            tol_h = 2 ** -6 * want_h.float().abs().max().item()
-            assert (res[0].float() - want_h.float()).abs().max().item() <= tol_h
-            assert (ys[0].float() - want_y.float()).abs().max().item() <= 2 ** -5 * want_y.float().abs().max().item()
+                assert torch.equal(res[r], h_unf), (rep, r)
+                assert torch.equal(ys[r], y_unf), (rep, r)
+        partials = [ref.gemm(x, w).to(torch.bfloat16) for x, w in zip(xs, ws)]
+        want_y, want_h = ref.ar_residual_rmsnorm(partials, res0, gamma, 1e-5)
+        tol_h = 2 ** -6 * want_h.float().abs().max().item()
+        assert (h_unf.float() - want_h.float()).abs().max().item() <= tol_h
+        assert (y_unf.float() - want_y.float()).abs().max().item() <= 2 ** -5 * want_y.float().abs().max().item()
+    finally:
+        c.destroy()
+
+
+def test_fused_gemm_allreduce_declines_large_messages_on_shape_alone():
+    """Above the LL packet limit the call is declined (the caller composes GEMM + collective); the answer
+    depends on the shape and the knobs only, so all ranks agree on it."""
+    from libtbvcoll_b200.tbvcoll import Comm
+    T, H, K, world = 128, 4096, 256, 2
+    c = Comm.local(world, 0, cap_bytes=T * H * 2)
+    try:
+        xs = [torch.zeros(T, K, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+        ws = [torch.zeros(H, K, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+        res = [torch.zeros(T, H, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+        ys = [torch.zeros(T, H, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+        gamma = torch.ones(H, dtype=torch.bfloat16, device=DEV)
+        assert c.gemm_all_reduce_rmsnorm_local(xs, ws, res, gamma, 1e-5, ys) is False
+        assert not c.err()
+    finally:
+        c.destroy()
+
+
+@pytest.mark.parametrize("kind", ["oneshot", "ll", "twoshot", "fused_norm", "fused_norm_ll", "fused_gemm"])
+def test_device_watchdog_when_one_emulated_rank_never_calls(kind):
+    """Failure detection on ONE GPU, made on the host: one emulated rank sits out a call (its CTAs
+    return before pushing anything).  The others' bounded waits run out after the watchdog period, the
+    kernel ENDS, the error is sticky, names the silent rank, later calls are refused, and the CUDA
+    context stays usable.  Nothing faults or traps."""
+    import time
+    from libtbvcoll_b200.tbvcoll import Comm
+    world, silent = 4, 2
+    T, H, K = 4, 1024, 256
+    c = Comm.local(world, 0, cap_bytes=1 << 20)
+    try:
+        c.set_wdog(0.05)
+        xs = [gen(r, T * H, torch.bfloat16).view(T, H) for r in range(world)]
+        outs = [torch.empty_like(x) for x in xs]
+        res = [gen(9, T * H, torch.bfloat16).view(T, H) for _ in range(world)]
+        gamma = gen(7, H, torch.bfloat16)
+        if kind in ("oneshot", "ll", "twoshot"):
+            c.set_algo(kind)
+        elif kind == "fused_norm":
+            c.set_algo("oneshot")
+        assert c.all_reduce_local(xs, outs) if kind in ("oneshot", "ll", "twoshot") else True    # a good call first
+        torch.cuda.synchronize()
+        assert not c.err()
+        c.mute_rank(silent, 1)
+        t0 = time.perf_counter()
+        if kind in ("oneshot", "ll", "twoshot"):
+            assert c.all_reduce_local(xs, outs)
+        elif kind in ("fused_norm", "fused_norm_ll"):
+            assert c.all_reduce_rmsnorm_local(xs, res, gamma, 1e-5, [torch.empty_like(x) for x in xs], outs)
+        else:
+            a = [gen(20 + r, T * K, torch.bfloat16).view(T, K) for r in range(world)]
+            w = [gen(30 + r, H * K, torch.bfloat16).view(H, K) * 0.05 for r in range(world)]
+            assert c.gemm_all_reduce_rmsnorm_local(a, w, res, gamma, 1e-5, outs)
+        torch.cuda.synchronize()                        # returns: every wait is bounded
+        elapsed = time.perf_counter() - t0
+        assert 0.04 < elapsed < 5.0, elapsed
+        assert c.err()                                   # sticky
+        last = c.last_error()
+        assert last["code"] == 1 and last["peer"] == silent, last
+        with pytest.raises(RuntimeError):
+            c.all_reduce_local(xs, outs)                 # refused: "previous collective failed: unrecoverable"
+        assert float((torch.ones(4, device=DEV) * 4).sum()) == 16.0     # the context is alive
+    finally:
+        c.destroy()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_sequence_stamp_diagnostic(world, monkeypatch):
+    """TBV_TAG=1: every flag is preceded by a sequence stamp in a word of its own; the receiver compares
+    it after the flag.  A message that fills the slot to the last byte is still exact (the stamp does
+    not live inside the payload), every flag wait is checked, none mismatches."""
+    from libtbvcoll_b200.tbvcoll import Comm
+    monkeypatch.setenv("TBV_TAG", "1")
+    nbytes = 57344
+    c = Comm.local(world, 0, cap_bytes=nbytes)          # capacity == message size
+    try:
+        n = nbytes // 2
+        calls = 0
+        for algo in ("oneshot", "twoshot"):
+            c.set_algo(algo)
+            for it in range(5):
+                ins = [gen(1000 * it + r, n, torch.bfloat16) for r in range(world)]
+                outs = [torch.empty_like(t) for t in ins]
+                assert c.all_reduce_local(ins, outs)
+                torch.cuda.synchronize()
+                assert all(torch.equal(o, oracle(ins)) for o in outs), (algo, it)
+                calls += 1
+        T, H = 7, 4096
+        c.set_algo("oneshot")
+        xs = [gen(r, T * H, torch.bfloat16).view(T, H) * 0.1 for r in range(world)]
+        res = [gen(99, T * H, torch.bfloat16).view(T, H) for _ in range(world)]
+        assert c.all_reduce_rmsnorm_local(xs, res, gen(7, H, torch.bfloat16), 1e-5, [torch.empty_like(x) for x in xs],
+                                          [torch.empty_like(x) for x in xs])
+        torch.cuda.synchronize()
+        checked, bad = c.tag_counts()
+        assert bad == 0 and checked >= calls * world * (world - 1)
+        c.hist()                                             # prints tag_checked / tag_bad
+        assert not c.err()
+    finally:
+        c.destroy()
+    monkeypatch.delenv("TBV_TAG")
+    c = Comm.local(world, 0, cap_bytes=nbytes)
+    try:
+        ins = [gen(r, nbytes // 2, torch.bfloat16) for r in range(world)]
+        assert c.all_reduce_local(ins)
+        torch.cuda.synchronize()
+        assert c.tag_counts() == (0, 0)                      # off by default: nothing stamped, nothing compared
+    finally:
+        c.destroy()
+
+
+def test_mixed_alignment_takes_the_same_kernel():
+    """A tensor that is not 16-byte aligned is accessed element by element inside the SAME kernel and
+    channel partition (the choice depends on the byte count only), so ranks whose tensors sit at
+    different alignments still run one protocol."""
+    from libtbvcoll_b200.tbvcoll import Comm
+    world, n = 4, 4096                                     # 8192 bytes: a multiple of 16
+    c = Comm.local(world, 0, cap_bytes=1 << 16)
+    try:
+        for algo in ("ll", "oneshot", "twoshot"):
+            c.set_algo(algo)
+            base = [torch.empty(n + 8, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+            ins = [b[(1 if r % 2 else 0):][:n] for r, b in enumerate(base)]      # odd ranks: 2-byte aligned views
+            for r, t in enumerate(ins):
+                t.copy_(gen(40 + r, n, torch.bfloat16))
+            outs = [torch.empty(n + 8, dtype=torch.bfloat16, device=DEV)[(0 if r % 2 else 3):][:n] for r in range(world)]
+            assert c.all_reduce_local(ins, outs)
+            torch.cuda.synchronize()
+            want = oracle([t.clone() for t in ins])
+            assert all(torch.equal(o, want) for o in outs), algo
+        assert not c.err()
     finally:
         c.destroy()
 
@@ -221,3 +365,30 @@ def test_allgather_gemm_emulated(world, rows, M, K):
         assert not c.err()
     finally:
         c.destroy()
+
+
+def test_allgather_gemm_after_destroy_and_create_with_the_same_shapes():
+    """The gathered-chunk tensor maps belong to their communicator: a second communicator created after
+    the first was destroyed (very likely at the same heap address, with the same shapes) builds its own
+    maps over its own slot memory."""
+    from libtbvcoll_b200.tbvcoll import Comm
+    from libtbvcoll_b200 import ops
+    world, rows, M, K = 2, 32, 256, 128
+    g = torch.Generator().manual_seed(8)
+    xs = [torch.randn(rows, K, generator=g).to(torch.bfloat16).to(DEV) for _ in range(world)]
+    ws = [(torch.randn(M, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV) for _ in range(world)]
+    full = torch.cat(xs, 0)
+    want = [ops.gemm(full, w, splits=1) for w in ws]
+    for life in range(3):
+        c = Comm.local(world, 0, cap_bytes=rows * K * 2)
+        junk = torch.empty(1 << 20, dtype=torch.uint8, device=DEV) if life % 2 else None   # shift the allocator between lives
+        try:
+            ys = [torch.zeros(world * rows, M, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+            assert c.allgather_gemm_local(xs, ws, ys)
+            torch.cuda.synchronize()
+            for r in range(world):
+                assert torch.equal(ys[r], want[r]), (life, r)
+            assert not c.err()
+        finally:
+            c.destroy()
+        del junk

@@ -73,7 +73,7 @@ def test_safetensors_checkpoint_round_trip(tmp_path):
 
 
 @pytest.mark.parametrize("mode", ["2", "3"])
-def test_long_prefill_through_the_many_token_gemm(monkeypatch, mode):
+def test_long_prefill_through_the_many_token_gemm(persist_mode, mode):
     """A 448-row prefill chunk sends every plain and SiLU-mul GEMM through the persistent many-token kernel
     (TBV_GEMM_PERSIST=2: 128-token tiles, 3: 256-token tiles) inside the engine (strided activations, programmatic dependent launch); the logits
     must agree with the same prefill on the decode-form kernel."""
@@ -85,10 +85,10 @@ def test_long_prefill_through_the_many_token_gemm(monkeypatch, mode):
     g = torch.Generator().manual_seed(4)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (400, 48)]
     eng = Engine(cfg, device=dev, seed=11, max_batch=2, max_seq_len=480, prefill_chunk=448)
-    monkeypatch.setenv("TBV_GEMM_PERSIST", "0")
+    persist_mode(0)
     first_a = eng.prefill(prompts, 4)
     logits_a = eng.model.logits[:2].float().clone()
-    monkeypatch.setenv("TBV_GEMM_PERSIST", mode)
+    persist_mode(int(mode))
     first_b = eng.prefill(prompts, 4)
     logits_b = eng.model.logits[:2].float().clone()
     torch.cuda.synchronize()
@@ -96,3 +96,30 @@ def test_long_prefill_through_the_many_token_gemm(monkeypatch, mode):
     err = (logits_a - logits_b).abs().max().item()
     assert err <= 0.02 * logits_a.abs().max().item() + 0.02, err
     assert len(first_a) == len(first_b) == 2
+
+
+def test_captured_decode_loop_replayed_past_the_reserved_length():
+    """The device-side decode loop keeps no host in it, so nothing but the kernels can stop it at the end
+    of the reserved cache: the advance kernel stops the context length at the block table's capacity and
+    hands out slot -1 (no cache write), and attention clamps the same way.  Replaying well past the
+    capacity must neither read outside the block table nor disturb the run: tokens stay valid ids."""
+    from libtbvcoll_b200 import ops
+    from libtbvcoll_b200.engine.engine import Engine
+    from libtbvcoll_b200.models.config import get_config
+    cfg = get_config("tiny")
+    eng = Engine(cfg, device="cuda:0", seed=3, max_batch=2, max_seq_len=32, block_size=16, prefill_chunk=16)
+    prompts = [[1, 2, 3, 4, 5, 6, 7, 8], [9, 10, 11]]
+    first = eng.prefill(prompts, 8)
+    eng._load_decode_inputs(2, first, [len(p) for p in prompts])
+    eng.step_counter.zero_()
+    g = eng.capture(2, 1, True)
+    cap = eng.bm.tables.shape[1] * eng.block_size
+    for _ in range(cap + 9):                      # runs past position `cap`
+        g.replay()
+    torch.cuda.synchronize()
+    assert not ops.gemm_error()
+    assert int(eng.ctx[:2].max()) == cap           # clamped, not cap + 9
+    assert int(eng.slots[:2].max()) == -1          # no cache slot past the table
+    toks = eng.out_tokens[:2].tolist()
+    assert all(0 <= t < cfg.vocab_size for t in toks)
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0

@@ -70,10 +70,10 @@ def test_gemm_silu_mul_epilogue_equals_unfused_bits(ops, N, I, K, splits):
 @pytest.mark.parametrize("mode", ["2", "3"])                    # 128-token tiles (two accumulators) / 256-token tiles
 @pytest.mark.parametrize("N,M,K,bias", [(384, 256, 64, False), (512, 1024, 2048, True), (1000, 656, 1088, True), (4096, 1536, 512, False),
                                         (777, 16, 192, False), (2500, 4096, 4096, False)])
-def test_gemm_many_tokens_persistent_kernel(ops, monkeypatch, N, M, K, bias, mode):
+def test_gemm_many_tokens_persistent_kernel(ops, persist_mode, N, M, K, bias, mode):
     """384 tokens and more (and no split hint) can take the persistent kernel: tokens on the UMMA M axis,
     TMEM fully used.  Ragged token / feature / K edges, a strided output and the bias are covered."""
-    monkeypatch.setenv("TBV_GEMM_PERSIST", mode)                # forced: also where the tile count fills the SMs badly
+    persist_mode(int(mode))                                     # forced: also where the tile count fills the SMs badly
     x, w = rnd(N, K, seed=21), rnd(M, K, scale=0.05, seed=22)
     b = rnd(M, seed=23) if bias else None
     outbuf = torch.zeros(N + 3, M + 64, dtype=torch.bfloat16, device=DEV)
@@ -92,8 +92,8 @@ def test_gemm_many_tokens_persistent_kernel(ops, monkeypatch, N, M, K, bias, mod
 
 @pytest.mark.parametrize("mode", ["2", "3"])
 @pytest.mark.parametrize("N,I,K", [(384, 128, 256), (1030, 1288, 1024), (4096, 512, 4096)])
-def test_gemm_many_tokens_silu_mul(ops, monkeypatch, N, I, K, mode):
-    monkeypatch.setenv("TBV_GEMM_PERSIST", mode)
+def test_gemm_many_tokens_silu_mul(ops, persist_mode, N, I, K, mode):
+    persist_mode(int(mode))
     x, wg, wu = rnd(N, K, seed=24), rnd(I, K, scale=0.05, seed=25), rnd(I, K, scale=0.05, seed=26)
     fused = ops.gemm(x, ops.interleave_gate_up(wg, wu), epi=ops.EPI_SILU_MUL)
     torch.cuda.synchronize()
