@@ -1,5 +1,5 @@
 #!/usr/bin/env python3
-"""All-reduce latency / bandwidth sweep: tbvcoll (one-shot, two-shot, NVLS, auto) vs NCCL.
+"""All-reduce latency / bandwidth sweep: tbvcoll (LL, one-shot, two-shot, NVLS, copy-engine, auto) vs NCCL.
 
 bf16 [tokens, 4096], tokens in {1, 2, 4, ..., 8192} (8 KB - 64 MB), values N(0,1); every
 result of this library is checked bit for bit against a fixed-order fp32 oracle before it is
@@ -85,7 +85,7 @@ def main():
     cap = args.max_tokens * args.hidden * 2
     port = int(os.environ.get("MASTER_PORT", "29500")) + 103
     comm = Comm(rank, world, local, "127.0.0.1", port, cap_bytes=cap)
-    algos = [a for a in args.algos.split(",") if a != "nvls" or comm.has_nvls()]
+    algos = [a for a in args.algos.split(",") if (a != "nvls" or comm.has_nvls()) and (a != "ce" or os.environ.get("TBV_CE") == "1")]
     rows = []
     tokens = max(1, args.min_tokens)
     while tokens <= args.max_tokens:
@@ -107,6 +107,8 @@ def main():
         groups = 40 if nbytes <= (4 << 20) else 12
         row = {"tokens": tokens, "bytes": nbytes}
         for algo in algos:
+            if algo == "ce" and nbytes < (1 << 20):
+                continue            # the copy-engine path is a large-message candidate only
             comm.set_algo(algo)
             assert comm.all_reduce(x, out)
             torch.cuda.synchronize()

@@ -656,6 +656,78 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   call_end(c, ci, nchan, t_enter, t_ready, nbytes, TBV_ALGO_TWOSHOT);
 }
 
+// ---- copy-engine two-shot (large messages, opt-in) -----------------------------------------------
+// The bulk transfers are stream-ordered device-to-device copies issued by the host (the copy
+// engines move the bytes, the SMs stay free); two small kernels do the signalling and the arithmetic.
+// This is the counterpart of the reference's memcpy + event path (TBV_GPUSIG=0,
+// step4/libtbvcoll.cpp:463-464,483).  Stream order per call:
+//   copies   chunk p of my input  -> rank p's CE region [src = me]           (W-1 copies)
+//   phase A  flag 0 to all, wait for all; reduce my chunk in rank order into out[chunk me]
+//   copies   out[chunk me]        -> every peer's CE result region            (W-1 copies)
+//   phase B  flag 1 to all, wait for all; copy the peers' chunks out; sequence number + 1
+// The CE regions are a fixed extra "slot" (index nslot), not part of the ring, so the copy
+// destinations do not depend on the sequence number and a captured graph replays correctly.
+// Reuse is safe without a ring: my kernel A of call s+1 passes only after every peer raised flag 0
+// of s+1, which each does after finishing its own call s entirely, so nobody still reads the
+// regions my next copies overwrite; the same holds for the result regions through flag 1.
+template <typename T>
+__device__ void ar_ce_phase_a(const RankCtx& c, const T* __restrict__ in, T* out, size_t nbytes, int nchan, int chan,
+                              unsigned long long* sh_seq) {
+  CallInfo ci = call_begin(c, sh_seq);
+  ci.slot = c.nslot;   // the fixed CE slot (flags and regions)
+  const size_t units = nbytes / 16, cu = units / c.world;
+  const size_t per = (cu + nchan - 1) / nchan;
+  const size_t b = per * chan < cu ? per * chan : cu, e = per * chan + per < cu ? per * chan + per : cu;
+  const int W = c.world, me = c.rank;
+  if (chan == 0 && threadIdx.x == 0) { c.dm->bc[0] = ci.seq; c.dm->ts[0] = globaltimer(); }
+  publish(c, ci, 0, chan);          // the copies before this kernel have completed: their bytes are in place
+  wait_all(c, ci, 0, chan, kWherePhase0);
+  if (chan == 0 && threadIdx.x == 0) { c.dm->bc[2] = ci.seq; c.dm->ts[1] = globaltimer(); }
+  const uint4* mine = reinterpret_cast<const uint4*>(in) + cu * me;
+  uint4* dst = reinterpret_cast<uint4*>(out) + cu * me;
+  for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) {
+    float acc[Pack<T>::N];
+#pragma unroll
+    for (int k = 0; k < Pack<T>::N; k++) acc[k] = 0.f;
+    const uint4 own = mine[i];
+    for (int r = 0; r < W; r++) {
+      const uint4 v = (r == me) ? own : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, me, ci.slot, r)) + i);
+      float f[Pack<T>::N];
+      Pack<T>::unpack(v, f);
+#pragma unroll
+      for (int k = 0; k < Pack<T>::N; k++) acc[k] = (r == 0) ? f[k] : acc[k] + f[k];
+    }
+    dst[i] = Pack<T>::pack(acc);
+  }
+}
+template <typename T>
+__device__ void ar_ce_phase_b(const RankCtx& c, T* out, size_t nbytes, int nchan, int chan, unsigned long long* sh_seq) {
+  CallInfo ci = call_begin(c, sh_seq);
+  const unsigned long long seq = ci.seq;
+  ci.slot = c.nslot;
+  const size_t units = nbytes / 16, cu = units / c.world;
+  const size_t per = (cu + nchan - 1) / nchan;
+  const size_t b = per * chan < cu ? per * chan : cu, e = per * chan + per < cu ? per * chan + per : cu;
+  const int W = c.world, me = c.rank;
+  publish(c, ci, 1, chan);
+  wait_all(c, ci, 1, chan, kWherePhase1);
+  const unsigned long long t_ready = (chan == 0 && threadIdx.x == 0) ? globaltimer() : 0;
+  const uint4* res = reinterpret_cast<const uint4*>(slot_region(c, me, ci.slot, W));
+  for (int d = 1; d < W; d++) {
+    const int p = (me + d) % W;
+    for (size_t i = b + threadIdx.x; i < e; i += size_t(4) * blockDim.x) {
+      uint4 v[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) { const size_t j = i + size_t(k) * blockDim.x; if (j < e) v[k] = ld_volatile_v4(res + cu * p + j); }
+#pragma unroll
+      for (int k = 0; k < 4; k++) { const size_t j = i + size_t(k) * blockDim.x; if (j < e) reinterpret_cast<uint4*>(out)[cu * p + j] = v[k]; }
+    }
+  }
+  ci.seq = seq;
+  ci.slot = int(seq % (unsigned long long)c.nslot);
+  call_end(c, ci, nchan, c.dm->ts[0], t_ready, nbytes, TBV_ALGO_CE);
+}
+
 // ---- NVLS all-reduce (multimem through the NVSwitch) -----------------------------------
 // Measured on B200: for fp32 the in-switch sum matched the oracle at N = 2; for bf16/fp16
 // (fp32 accumulate requested) about one element in five differs from round-to-nearest-even of

@@ -67,12 +67,14 @@ Knobs Knobs::from_env() {
   k.ll_max = env_long("TBV_LL_MAX", -1);  // -1: chosen from the world size when the communicator is created
   k.nvls_min = env_long("TBV_NVLS_MIN", LONG_MAX);  // auto never picks the switch-reduced kernel unless asked
   k.nvls_direct_max = env_long("TBV_NVLS_DIRECT_MAX", 1l << 20);
+  k.ce = int(env_long("TBV_CE", 0));
   const char* a = getenv("TBV_ALGO");
   if (a) {
     if (!strcmp(a, "oneshot")) k.algo = TBV_ALGO_ONESHOT;
     else if (!strcmp(a, "twoshot")) k.algo = TBV_ALGO_TWOSHOT;
     else if (!strcmp(a, "nvls")) k.algo = TBV_ALGO_NVLS;
     else if (!strcmp(a, "ll")) k.algo = TBV_ALGO_LL;
+    else if (!strcmp(a, "ce")) k.algo = TBV_ALGO_CE;
   }
   const char* m = getenv("TBV_MEM");
   if (m) k.mem = !strcmp(m, "vmm") ? 1 : (!strcmp(m, "ipc") ? 2 : 0);
@@ -263,6 +265,17 @@ __global__ void __launch_bounds__(512) k_ar_rmsnorm_ll_local(const RankCtx* ctxs
                      gridDim.x, blockIdx.x, norm_threads, &sh_seq, sh_red);
 }
 
+template <typename T>
+__global__ void __launch_bounds__(512) k_ar_ce_a(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes) {
+  __shared__ unsigned long long sh_seq;
+  ar_ce_phase_a<T>(c, in, out, nbytes, gridDim.x, blockIdx.x, &sh_seq);
+}
+template <typename T>
+__global__ void __launch_bounds__(512) k_ar_ce_b(const __grid_constant__ RankCtx c, T* out, size_t nbytes) {
+  __shared__ unsigned long long sh_seq;
+  ar_ce_phase_b<T>(c, out, nbytes, gridDim.x, blockIdx.x, &sh_seq);
+}
+
 // ---- sizing tables --------------------------------------------------------------------------
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -272,6 +285,7 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 static int pick_algo(const tbv_comm* c, size_t nbytes, bool vec) {
   int a = c->knobs.algo;
   if (a == TBV_ALGO_NVLS && !(c->nvls && vec)) a = TBV_ALGO_AUTO;
+  if (a == TBV_ALGO_CE && !(c->knobs.ce && !c->local && nbytes % (size_t(16) * c->world) == 0)) a = TBV_ALGO_AUTO;
   const bool ll_ok = vec && nbytes * 2 <= c->ll_cap;
   if (a == TBV_ALGO_LL && !ll_ok) a = TBV_ALGO_AUTO;
   if (a != TBV_ALGO_AUTO) return a;
@@ -329,11 +343,11 @@ static void compute_sizes(tbv_comm* c) {
   // shrinks with the world.  The receiver fetches the packets of all sources with one batch of loads,
   // so the cost of a call no longer grows with one memory round trip per peer.
   if (c->knobs.ll_max < 0) c->knobs.ll_max = c->world <= 2 ? (256 << 10) : (c->world <= 4 ? (128 << 10) : (128 << 10));
-  const size_t nflag = size_t(c->knobs.nslot) * 2 * c->world * TBV_MAXCHAN;
+  const size_t nflag = size_t(c->knobs.nslot + 1) * 2 * c->world * TBV_MAXCHAN;   // + the fixed slot of the copy-engine path
   c->tag_off = (nflag * sizeof(unsigned) + 255) & ~size_t(255);
   // flags, then one 8-byte sequence stamp per flag (TBV_TAG diagnostic; its own words, never inside a payload region)
   c->flag_bytes = (c->tag_off + nflag * sizeof(unsigned long long) + 4095) & ~size_t(4095);
-  c->data_bytes = size_t(c->knobs.nslot) * size_t(c->world + 1) * c->cap;
+  c->data_bytes = size_t(c->knobs.nslot + (c->knobs.ce ? 1 : 0)) * size_t(c->world + 1) * c->cap;   // TBV_CE=1: one more slot, outside the ring
   // LL area: two bytes on the wire per payload byte, one region per (slot, source)
   c->ll_cap = (size_t(std::max(0l, c->knobs.ll_max)) * 2 + 4095) & ~size_t(4095);
   c->ll_bytes = size_t(c->knobs.nslot) * c->world * c->ll_cap;
@@ -508,13 +522,13 @@ static int gpu_init(tbv_comm* c) {
   // agree on the parameters that shape the protocol and on every knob that enters the choice of
   // kernel or of the channel count (ranks that chose differently would wait on flags nobody raises)
   struct Hello {
-    int world, nslot, tag, dev, algo, nchan, nvls;
+    int world, nslot, tag, dev, algo, nchan, nvls, ce;
     long long ll_max, oneshot_max, chunk, nvls_min;
     unsigned long long cap;
     char uuid[16];
   } me{}, all[TBV_MAXRANK];
   me.world = c->world; me.nslot = c->knobs.nslot; me.tag = c->knobs.tag; me.dev = c->device; me.cap = c->cap;
-  me.algo = c->knobs.algo; me.nchan = c->knobs.nchan; me.nvls = c->knobs.nvls; me.ll_max = c->knobs.ll_max;
+  me.algo = c->knobs.algo; me.nchan = c->knobs.nchan; me.nvls = c->knobs.nvls; me.ce = c->knobs.ce; me.ll_max = c->knobs.ll_max;
   me.oneshot_max = c->knobs.oneshot_max; me.chunk = c->knobs.chunk; me.nvls_min = c->knobs.nvls_min;
   memcpy(me.uuid, &prop.uuid, 16);
   if (c->bs.allgather(&me, all, sizeof(Hello)) != 0) { c->errmsg = c->bs.error(); return TBV_FAIL; }
@@ -524,9 +538,9 @@ static int gpu_init(tbv_comm* c) {
       LOG("rank %d: %s (rank %d has nslot=%d cap=%llu)", c->rank, c->errmsg.c_str(), p, all[p].nslot, all[p].cap);
       return TBV_FAIL;
     }
-    if (all[p].algo != me.algo || all[p].nchan != me.nchan || all[p].nvls != me.nvls || all[p].ll_max != me.ll_max ||
+    if (all[p].algo != me.algo || all[p].nchan != me.nchan || all[p].nvls != me.nvls || all[p].ce != me.ce || all[p].ll_max != me.ll_max ||
         all[p].oneshot_max != me.oneshot_max || all[p].chunk != me.chunk || all[p].nvls_min != me.nvls_min) {
-      c->errmsg = "ranks disagree on TBV_ALGO/TBV_NCHAN/TBV_NVLS/TBV_LL_MAX/TBV_RAIL1MAX/TBV_CHUNK/TBV_NVLS_MIN";
+      c->errmsg = "ranks disagree on TBV_ALGO/TBV_NCHAN/TBV_NVLS/TBV_CE/TBV_LL_MAX/TBV_RAIL1MAX/TBV_CHUNK/TBV_NVLS_MIN";
       LOG("rank %d: %s (compared with rank %d)", c->rank, c->errmsg.c_str(), p);
       return TBV_FAIL;
     }
@@ -699,6 +713,35 @@ static cudaError_t launch_ar_local_t(tbv_comm* c, int algo, bool vec, int nchan,
   return cudaLaunchCooperativeKernel(fn, grid, dim3(threads), args, 0, st);
 }
 
+// Copy-engine two-shot: copies, kernel A, copies, kernel B on the caller's stream (see ar_device.cuh).
+template <typename T>
+static cudaError_t launch_ar_ce_t(tbv_comm* c, const void* in, void* out, size_t nbytes, cudaStream_t st) {
+  const RankCtx& x = c->ranks[0].ctx;
+  const int W = c->world, me = c->rank;
+  const size_t chunk = nbytes / W;
+  char* const ce0 = nullptr;
+  (void)ce0;
+  const size_t ce_off = size_t(x.nslot) * x.slot_stride;
+  int nchan = int(std::min<size_t>(64, std::max<size_t>(1, chunk / 16 / 512)));
+  if (c->knobs.nchan > 0) nchan = std::min(c->knobs.nchan, TBV_MAXCHAN);
+  cudaError_t e = cudaSuccess;
+  for (int d = 1; d < W && e == cudaSuccess; d++) {
+    const int p = (me + d) % W;
+    e = cudaMemcpyAsync(x.data[p] + ce_off + size_t(me) * x.cap, static_cast<const char*>(in) + chunk * p, chunk, cudaMemcpyDeviceToDevice, st);
+  }
+  if (e != cudaSuccess) return e;
+  k_ar_ce_a<T><<<nchan, 512, 0, st>>>(x, static_cast<const T*>(in), static_cast<T*>(out), nbytes);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  for (int d = 1; d < W && e == cudaSuccess; d++) {
+    const int p = (me + d) % W;
+    e = cudaMemcpyAsync(x.data[p] + ce_off + size_t(W) * x.cap + chunk * me, static_cast<const char*>(out) + chunk * me, chunk,
+                        cudaMemcpyDeviceToDevice, st);
+  }
+  if (e != cudaSuccess) return e;
+  k_ar_ce_b<T><<<nchan, 512, 0, st>>>(x, static_cast<T*>(out), nbytes);
+  return cudaGetLastError();
+}
+
 // Emulated world only: the rank named by tbv_comm_mute_rank sits out this launch.
 static int take_mute(tbv_comm* c) {
   if (!c->local || c->mute_left.load() <= 0) return -1;
@@ -758,7 +801,14 @@ static int gpu_collective(tbv_comm* c, const void* const* ins, void* const* outs
       case TBV_F16: e = launch_ar_local_t<__half>(c, algo, vec, nchan, threads, p, full, st, mode); break;
       default: e = launch_ar_local_t<__nv_bfloat16>(c, algo, vec, nchan, threads, p, full, st, mode); break;
     }
+  } else if (algo == TBV_ALGO_CE && mode == 0 && io == (kInAligned | kOutAligned)) {
+    switch (dtype) {
+      case TBV_F32: e = launch_ar_ce_t<float>(c, ins[0], outs[0], full, st); break;
+      case TBV_F16: e = launch_ar_ce_t<__half>(c, ins[0], outs[0], full, st); break;
+      default: e = launch_ar_ce_t<__nv_bfloat16>(c, ins[0], outs[0], full, st); break;
+    }
   } else {
+    if (algo == TBV_ALGO_CE) algo = TBV_ALGO_TWOSHOT;   // a tensor that cannot be copied 16 bytes at a time
     switch (dtype) {
       case TBV_F32: e = launch_ar_t<float>(c, algo, vec, nchan, threads, ins[0], outs[0], full, st, mode, io); break;
       case TBV_F16: e = launch_ar_t<__half>(c, algo, vec, nchan, threads, ins[0], outs[0], full, st, mode, io); break;
@@ -1030,7 +1080,7 @@ int tbv_comm_tag_counts(tbv_comm* c, unsigned long long* checked, unsigned long 
   return TBV_OK;
 }
 int tbv_comm_set_algo(tbv_comm* c, int algo) {
-  if (!c || algo < 0 || algo > 4) return TBV_FAIL;
+  if (!c || algo < 0 || algo > 5) return TBV_FAIL;
   c->knobs.algo = algo;
   return TBV_OK;
 }

@@ -30,6 +30,7 @@ struct Knobs {
   int cpu = -1;           // TBV_CPU: pin the CPU backend's progress thread
   int algo = TBV_ALGO_AUTO;  // TBV_ALGO
   int nchan = 0;          // TBV_NCHAN (0 = table)
+  int ce = 0;             // TBV_CE: 1 = reserve one more slot for the copy-engine two-shot path (TBV_ALGO=ce / set_algo)
   int nvls = 0;           // TBV_NVLS: 1 = set up a multicast object and allow the NVLS kernels
   int mem = 0;            // TBV_MEM: 0 = VMM with IPC fallback, 1 = VMM only, 2 = cudaIpc only
   double init_timeout_s = 60.0;  // TBV_INIT_TIMEOUT

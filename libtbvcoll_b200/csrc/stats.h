@@ -59,7 +59,7 @@ struct Stats {
   }
   void dump_hist(int rank, unsigned long long tag_bad, unsigned long long tag_checked = 0) {
     std::lock_guard<std::mutex> g(mu);
-    static const char* an[8] = {"auto", "oneshot", "twoshot", "nvls", "ll", "?", "?", "?"};
+    static const char* an[8] = {"auto", "oneshot", "twoshot", "nvls", "ll", "ce", "?", "?"};
     fprintf(stderr, "[tbvcoll] rank %d hist: streams=%llu switches=%llu fallbacks=%llu tag_checked=%llu tag_bad=%llu\n", rank,
             streams_seen, stream_switches, fallbacks, tag_checked, tag_bad);
     for (int b = 0; b < 32; b++) {

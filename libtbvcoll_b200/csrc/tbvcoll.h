@@ -31,6 +31,7 @@ extern "C" {
 #define TBV_ALGO_TWOSHOT 2
 #define TBV_ALGO_NVLS 3
 #define TBV_ALGO_LL 4   // one-shot with flag-in-payload packets (small messages)
+#define TBV_ALGO_CE 5   // two-shot whose bulk transfers are copy-engine copies (TBV_CE=1 at bring-up; large messages; never picked by auto)
 
 #define TBV_MAXRANK 8
 #define TBV_MAXSLOT 32

@@ -73,14 +73,14 @@ def main():
     if args.time_nccl:
         vllm_hook.install_nccl_timing()
     elif args.tbvcoll:
-        vllm_hook.install(eager=False)
+        # --tbv-eager: bring the library up NOW, before the engine exists, so that its slot memory is allocated
+        # before vLLM sizes its KV cache (step3b/vllm_tp_bench.py:129-139); all ranks are at the same point
+        vllm_hook.install(eager=args.tbv_eager)
     model = args.model or synth_model_dir(args.synth or "llama3-8b")
     dummy = not args.model
     llm = LLM(model=model, tensor_parallel_size=args.tp, distributed_executor_backend="external_launcher",
               enforce_eager=not args.compile, seed=1, max_model_len=args.max_model_len, gpu_memory_utilization=args.gpu_mem_util,
               **({"load_format": "dummy", "skip_tokenizer_init": True} if dummy else {}))
-    if args.tbvcoll and args.tbv_eager:
-        vllm_hook.install(eager=True)
     sp = SamplingParams(temperature=0.0, max_tokens=args.out_tokens, ignore_eos=True, **({"detokenize": False} if dummy else {}))
     if dummy:
         g = torch.Generator().manual_seed(1234)

@@ -123,7 +123,7 @@ def _stream_of(t: torch.Tensor):
     return c_vp(torch.cuda.current_stream(t.device).cuda_stream) if t.is_cuda else None
 
 
-ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "ll": 4}
+ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "ll": 4, "ce": 5}
 
 
 class Comm:
