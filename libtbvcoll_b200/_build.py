@@ -7,7 +7,7 @@ with ``-gencode arch=compute_100a,code=sm_100a`` and linked into ONE shared obje
 ``tbv_comm_*``) and the operator ABI (``tbv_op_*``).  Objects are rebuilt only when a
 source or header is newer.
 
-    python -m libtbvcoll_b200._build [--force] [--verbose]
+    python -m libtbvcoll_b200._build [--force] [--verbose] [--bounds]
 """
 from __future__ import annotations
 
@@ -22,6 +22,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "build"
 LIB = PKG / "libtbvcoll.so"
+LIB_BOUNDS = PKG / "libtbvcoll_bounds.so"     # the same sources with -DTBV_BOUNDS_CHECK (device-side extent guards)
 AR_BENCH = PKG / "tbv_arbench"
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -46,11 +47,11 @@ def _headers_mtime() -> float:
     return max((h.stat().st_mtime for h in hs), default=0.0)
 
 
-def _compile(src: Path, force: bool, verbose: bool, hdr_m: float) -> tuple[Path, str]:
-    obj = OBJ / (src.stem + ".o")
+def _compile(src: Path, force: bool, verbose: bool, hdr_m: float, bounds: bool = False) -> tuple[Path, str]:
+    obj = (OBJ / "bounds" if bounds else OBJ) / (src.stem + ".o")
     if not force and obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, hdr_m):
         return obj, ""
-    cmd = [nvcc(), *ARCH, *COMMON, "-c", str(src), "-o", str(obj)]
+    cmd = [nvcc(), *ARCH, *COMMON, *(["-DTBV_BOUNDS_CHECK"] if bounds else []), "-c", str(src), "-o", str(obj)]
     if src.suffix == ".cpp":
         cmd.insert(1, "-x")
         cmd.insert(2, "cu")
@@ -92,6 +93,23 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+def build_bounds(force: bool = False) -> Path:
+    """The bounds-checked debug library, ``libtbvcoll_bounds.so`` (load it with ``TBV_LIB=<path>``).
+    compute-sanitizer's stand-in for the collective kernels: see ``TBV_GUARD`` in csrc/ar_device.cuh."""
+    (OBJ / "bounds").mkdir(parents=True, exist_ok=True)
+    srcs = lib_sources()
+    hdr_m = _headers_mtime()
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
+        objs = [o for o, _ in ex.map(lambda s: _compile(s, force, False, hdr_m, bounds=True), srcs)]
+    newest = max(o.stat().st_mtime for o in objs)
+    if force or not LIB_BOUNDS.exists() or LIB_BOUNDS.stat().st_mtime < newest:
+        cmd = [nvcc(), *ARCH, "-shared", "-o", str(LIB_BOUNDS), *map(str, objs), "-lrt", "-lpthread", "-ldl"]
+        p = subprocess.run(cmd, capture_output=True, text=True)
+        if p.returncode != 0:
+            raise RuntimeError(f"link failed:\n{p.stdout}\n{p.stderr}")
+    return LIB_BOUNDS
+
+
 def ensure_built() -> Path:
     """Build if the shared object is missing or stale (cheap mtime check)."""
     try:
@@ -108,3 +126,5 @@ def ensure_built() -> Path:
 if __name__ == "__main__":
     out = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(out)
+    if "--bounds" in sys.argv:
+        print(build_bounds(force="--force" in sys.argv))

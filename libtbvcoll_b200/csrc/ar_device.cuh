@@ -64,8 +64,9 @@ struct HostMirror {
   unsigned long long tag_bad;
 };
 
-enum : unsigned { kErrNone = 0, kErrTimeout = 1, kErrTag = 2 };
-enum : unsigned { kWherePhase0 = 1, kWherePhase1 = 2, kWhereFused = 3 };
+enum : unsigned { kErrNone = 0, kErrTimeout = 1, kErrTag = 2, kErrBounds = 3 };
+enum : unsigned { kWherePhase0 = 1, kWherePhase1 = 2, kWhereFused = 3,
+                  kGuardSlotBytes = 16, kGuardLLBytes = 17, kGuardChannels = 18 };   // sites of the bounds-checked build
 
 // Everything a kernel needs to talk to the other ranks; passed by value.
 struct RankCtx {
@@ -73,6 +74,7 @@ struct RankCtx {
   unsigned long long cap;          // bytes per (slot, source-rank) region
   unsigned long long slot_stride;  // bytes per slot = (world + 1) * cap
   unsigned long long wdog_ns;      // bound on every device-side wait
+  unsigned long long guard_cap, guard_ll_cap;  // what the bounds-checked build compares extents with (= cap, ll_cap)
   char* data[TBV_MAXRANK];         // data[p]: rank p's slot memory as mapped here
   unsigned int* flags[TBV_MAXRANK];
   char* ll[TBV_MAXRANK];           // ll[p]: rank p's LL packet area (only ever holds LL packets)
@@ -162,6 +164,24 @@ __device__ __forceinline__ bool wait_flag(const RankCtx& c, const unsigned* f, u
   }
   return true;
 }
+
+// ---- bounds-checked build (-DTBV_BOUNDS_CHECK) -------------------------------------------------
+// compute-sanitizer's job, done by hand where it is not available: before a collective body touches
+// slot or packet memory it compares the extent it is about to use (and its channel count) with what
+// the communicator reserved.  A violation is RECORDED (sticky error kErrBounds, the site, the
+// offending value in place of the sequence number) and the body then moves no data at all — it still
+// raises its flags, so no peer is left waiting.  Compiled out of the normal build.
+#ifdef TBV_BOUNDS_CHECK
+__device__ __forceinline__ bool guard_extent(const RankCtx& c, unsigned long long need, unsigned long long have, unsigned site,
+                                             int chan) {
+  if (need <= have) return true;
+  report_error(c, kErrBounds, site, 0, chan, need);
+  return false;
+}
+#define TBV_GUARD(c, need, have, site, chan) guard_extent(c, (unsigned long long)(need), (unsigned long long)(have), site, chan)
+#else
+#define TBV_GUARD(c, need, have, site, chan) (true)
+#endif
 
 // ---- element packs ---------------------------------------------------------------
 template <typename T> struct Pack;  // 16 bytes of T <-> fp32 lanes
@@ -333,9 +353,11 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   const size_t units = nbytes / unit_bytes;
   const size_t per = (units + nchan - 1) / nchan;
   const size_t u0 = per * chan;
-  const size_t u1 = (u0 + per < units) ? (u0 + per) : units;
+  size_t u1 = (u0 + per < units) ? (u0 + per) : units;
   const bool in_al = io & kInAligned, out_al = io & kOutAligned;
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
+  if (!(TBV_GUARD(c, nbytes, c.guard_cap, kGuardSlotBytes, chan) && TBV_GUARD(c, nchan, TBV_MAXCHAN, kGuardChannels, chan)))
+    u1 = u0;   // bounds-checked build: nothing is moved after a violation
 
   // push my range to every peer's [slot][src = me] region
   for (size_t u = u0 + threadIdx.x; u < u1; u += blockDim.x) {
@@ -477,7 +499,8 @@ __device__ void ar_oneshot_ll_body(const RankCtx& c, const T* __restrict__ in, T
   const size_t units = nbytes / 16;
   const size_t per = (units + nchan - 1) / nchan;
   const size_t u0 = per * chan;
-  const size_t u1 = (u0 + per < units) ? (u0 + per) : units;
+  size_t u1 = (u0 + per < units) ? (u0 + per) : units;
+  if (!(TBV_GUARD(c, nbytes * 2, c.guard_ll_cap, kGuardLLBytes, chan) && TBV_GUARD(c, nchan, TBV_MAXCHAN, kGuardChannels, chan))) u1 = u0;
   const bool in_al = io & kInAligned, out_al = io & kOutAligned;
   // the first unit's load is issued before the sequence number is known (they do not depend on each other)
   const size_t uf = u0 + threadIdx.x;
@@ -523,7 +546,8 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   CallInfo ci = call_begin(c, sh_seq);
   const size_t unit_bytes = VEC ? 16 : sizeof(T);
-  const size_t units = nbytes / unit_bytes;              // whole (gathered) tensor
+  size_t units = nbytes / unit_bytes;                    // whole (gathered) tensor
+  if (!(TBV_GUARD(c, nbytes, c.guard_cap, kGuardSlotBytes, chan) && TBV_GUARD(c, nchan, TBV_MAXCHAN, kGuardChannels, chan))) units = 0;
   const size_t cu = (units + c.world - 1) / c.world;     // units per rank chunk
   const size_t per = (cu + nchan - 1) / nchan;           // units per channel inside a chunk
   const int W = c.world, me = c.rank;
@@ -943,6 +967,8 @@ __device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __
   const int upr = hidden / 8;  // 16-byte units per row
   CallInfo ci = call_begin(c, sh_seq);
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
+  if (!(TBV_GUARD(c, size_t(tokens) * hidden * 2, c.guard_cap, kGuardSlotBytes, chan) && TBV_GUARD(c, nchan, TBV_MAXCHAN, kGuardChannels, chan)))
+    tokens = 0;
   for (int row = chan; row < tokens; row += nchan) {
     const uint4* src = reinterpret_cast<const uint4*>(x) + size_t(row) * upr;
     for (int u = threadIdx.x; u < upr; u += blockDim.x) {
@@ -1001,6 +1027,7 @@ __device__ inline void ar_rmsnorm_ll_body(const RankCtx& c, const __nv_bfloat16*
                                           int nchan, int chan, int norm_threads, unsigned long long* sh_seq, float* sh_red) {
   unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   const int upr = hidden / 8;
+  if (!TBV_GUARD(c, size_t(tokens) * hidden * 4, c.guard_ll_cap, kGuardLLBytes, chan)) tokens = 0;
   // first row's first unit: loaded before the sequence number is known
   uint4 first = make_uint4(0, 0, 0, 0);
   if (chan < tokens && int(threadIdx.x) < upr) first = reinterpret_cast<const uint4*>(x)[size_t(chan) * upr + threadIdx.x];

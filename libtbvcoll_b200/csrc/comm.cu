@@ -292,8 +292,9 @@ static int pick_algo(const tbv_comm* c, size_t nbytes, bool vec) {
   if (ll_ok && long(nbytes) <= c->knobs.ll_max) return TBV_ALGO_LL;
   if (c->nvls && vec && long(nbytes) >= c->knobs.nvls_min) return TBV_ALGO_NVLS;
   long lim = c->knobs.oneshot_max;
-  // measured crossovers (graph-timed, B200 NVSwitch): N=2 one-shot wins up to ~2-4 MiB, N=4 up to ~2 MiB
-  if (lim < 0) lim = c->world <= 2 ? (2l << 20) : (c->world <= 4 ? (2l << 20) : (512l << 10));
+  // measured crossovers (graph-timed, B200 NVSwitch, one build): 2 ranks one-shot wins up to 2 MiB (17.6 vs 19.9 us) and
+  // loses at 4 MiB; 4 ranks up to 1 MiB (18.4 vs 20.2) and loses at 2 MiB (29.5 vs 23.2); 8 ranks up to 512 KiB (19.9 vs 25.8)
+  if (lim < 0) lim = c->world <= 2 ? (2l << 20) : (c->world <= 4 ? (1l << 20) : (512l << 10));
   return long(nbytes) <= lim ? TBV_ALGO_ONESHOT : TBV_ALGO_TWOSHOT;
 }
 // Channels (CTAs).  The rule must be a pure function of (bytes, world, knobs): every
@@ -320,6 +321,11 @@ static void fill_ctx(tbv_comm* c, GpuRank& g, int rank) {
   x.cap = c->cap;
   x.slot_stride = size_t(c->world + 1) * c->cap;
   x.ll_cap = c->ll_cap;
+  // TBV_DEBUG_CAP (meant for the bounds-checked build): the extent the device-side guards compare with, smaller than
+  // what is really reserved, so that a test can trip a guard with a call that stays inside real memory
+  const long dbg_cap = env_long("TBV_DEBUG_CAP", 0);
+  x.guard_cap = dbg_cap > 0 ? (unsigned long long)dbg_cap : c->cap;
+  x.guard_ll_cap = dbg_cap > 0 ? (unsigned long long)dbg_cap * 2 : c->ll_cap;
   x.wdog_ns = (unsigned long long)(c->knobs.wdog_s * 1e9);
   x.st = g.st;
   x.dm = g.dm;
@@ -1066,6 +1072,14 @@ int tbv_comm_nslot(tbv_comm* c) { return c ? c->knobs.nslot : 0; }
 int tbv_comm_is_async(tbv_comm* c) { return c ? c->knobs.async : 0; }
 int tbv_comm_err(tbv_comm* c) { return c ? int(check_err(c)) : 1; }
 int tbv_comm_has_nvls(tbv_comm* c) { return c ? int(c->nvls) : 0; }
+// 1 if this library was compiled with the device-side bounds guards (-DTBV_BOUNDS_CHECK)
+int tbv_bounds_checked_build(void) {
+#ifdef TBV_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
 // Sequence stamps (TBV_TAG=1) compared and found wrong since the communicator was created, summed over (emulated) ranks.
 int tbv_comm_tag_counts(tbv_comm* c, unsigned long long* checked, unsigned long long* bad) {
   if (!c || c->cpu) return TBV_FAIL;

@@ -37,16 +37,17 @@ struct Maps {
 };
 
 // ---------------------------------------------------------------- GEMM -> scatter
-// grid (m_tiles, n_tiles * nr, 1); tokens [T], rows_per_rank = T / world, rows_per_rank % bn == 0.
+// grid (n_tiles * nr, m_tiles, 1): token tiles are the fastest launch index, so the CTAs that share one 128-row
+// weight tile run together and the weights stream from HBM once; tokens [T], rows_per_rank = T / world, rows_per_rank % bn == 0.
 __global__ void __launch_bounds__(gemm::kThreads, 1)
 k_gemm_scatter(const __grid_constant__ Maps maps, const gemm::Params p, const RankCtx* ctxs, int n_tiles, int rows_per_rank) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ gemm::Smem s;
   __shared__ unsigned long long sh_seq;
-  const int er = blockIdx.y / n_tiles, n_tile = blockIdx.y % n_tiles;
+  const int er = blockIdx.x / n_tiles, n_tile = blockIdx.x % n_tiles;
   const RankCtx& c = ctxs[er];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tile = blockIdx.x, m0 = m_tile * gemm::kBM, n0 = n_tile * p.bn;
+  const int m_tile = blockIdx.y, m0 = m_tile * gemm::kBM, n0 = n_tile * p.bn;
   const unsigned long long t_enter = (threadIdx.x == 0 && m_tile == 0 && n_tile == 0) ? tbv::globaltimer() : 0;
   uint8_t* sm = gemm::mainloop(&maps.a[er], &maps.b[er], p, s, smem_raw, m0, n0, 0, p.kb_total);
   volatile int* abortp = &s.abort_flag;
@@ -84,7 +85,7 @@ k_gemm_scatter(const __grid_constant__ Maps maps, const gemm::Params p, const Ra
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (threadIdx.x == 64) {
       fence_sys();
-      const int chan = (row0 / p.bn) * gridDim.x + m_tile;
+      const int chan = (row0 / p.bn) * gridDim.y + m_tile;
       st_relaxed_sys(c.flags[dest] + flag_index(c, slot, 0, c.rank, chan), unsigned(seq));
     }
   }
@@ -94,7 +95,7 @@ k_gemm_scatter(const __grid_constant__ Maps maps, const gemm::Params p, const Ra
   ci.seq = sh_seq;   // written before the epilogue barrier; teardown's __syncthreads publishes it to all warps
   ci.want = unsigned(ci.seq);
   ci.slot = int(ci.seq % (unsigned long long)c.nslot);
-  call_end(c, ci, gridDim.x * unsigned(n_tiles), t_enter, 0, size_t(p.N) * H * 2, TBV_ALGO_TWOSHOT);
+  call_end(c, ci, gridDim.y * unsigned(n_tiles), t_enter, 0, size_t(p.N) * H * 2, TBV_ALGO_TWOSHOT);
 }
 
 // grid (rows_per_rank, nr); block = norm_threads(H).  mode 0: out = sum; mode 1: h = sum + residual ->
@@ -184,7 +185,8 @@ k_ag_push(const RankCtx* ctxs, const __grid_constant__ AgPtrs ptrs, int K, int l
   call_end(c, ci, gridDim.x, t_enter, 0, size_t(rows_per_rank) * K * 2, TBV_ALGO_TWOSHOT);
 }
 
-// grid (m_tiles, n_tiles_total, nr).  n tile order is rotated so that this rank's own rows come first.
+// grid (n_tiles_total, m_tiles, nr): token tiles fastest (the per-rank weights stream from HBM once, not once per
+// token tile); the n tile order is rotated so that this rank's own rows come first.
 struct AgOut { __nv_bfloat16* y[TBV_MAXRANK]; const CUtensorMap* gathered[TBV_MAXRANK]; };  // gathered[er]: [nslot * world] maps
 __global__ void __launch_bounds__(gemm::kThreads, 1)
 k_ag_gemm(const __grid_constant__ Maps maps, const gemm::Params p, const RankCtx* ctxs, const __grid_constant__ AgOut ao, int tiles_per_src) {
@@ -193,8 +195,8 @@ k_ag_gemm(const __grid_constant__ Maps maps, const gemm::Params p, const RankCtx
   const int er = blockIdx.z;
   const RankCtx& c = ctxs[er];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int src = (c.rank + blockIdx.y / tiles_per_src) % c.world, j = blockIdx.y % tiles_per_src;
-  const int m0 = blockIdx.x * gemm::kBM;
+  const int src = (c.rank + blockIdx.x / tiles_per_src) % c.world, j = blockIdx.x % tiles_per_src;
+  const int m0 = blockIdx.y * gemm::kBM;
   const int rows_per_rank = tiles_per_src * p.bn;
   const int n0_global = src * rows_per_rank + j * p.bn;
   // -- set-up identical to gemm::mainloop, but the producer resolves its activation tile first
@@ -372,7 +374,7 @@ static int launch_gemm_rs(tbv_comm* c, const void* const* ws, const void* const*
   p.err = tbvops::gemm_err_flag();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const RankCtx* ctxs = c->ctxs_dev;
-  cudaError_t e = pdl::launch(k_gemm_scatter, dim3(m_tiles, n_tiles * nr, 1), dim3(gemm::kThreads), size_t(stages) * stage_bytes + 1024, st, 1,
+  cudaError_t e = pdl::launch(k_gemm_scatter, dim3(n_tiles * nr, m_tiles, 1), dim3(gemm::kThreads), size_t(stages) * stage_bytes + 1024, st, 1,
                               maps, p, ctxs, n_tiles, rpr);
   if (e == cudaSuccess)
     e = pdl::launch(k_rs_reduce_norm, dim3(rpr, nr), dim3(tbvops::norm_threads(H)), 0, st, 1, ctxs, rp,
@@ -422,7 +424,7 @@ static int launch_ag_gemm(tbv_comm* c, const void* const* ws, const void* const*
   const RankCtx* ctxs = c->ctxs_dev;
   cudaError_t e = pdl::launch(k_ag_push, dim3(tiles_per_src, nr), dim3(512), 0, st, 1, ctxs, ap, K, ldx, bn, rows_per_rank);
   if (e == cudaSuccess)
-    e = pdl::launch(k_ag_gemm, dim3((M + 127) / 128, tiles_per_src * W, nr), dim3(gemm::kThreads), size_t(stages) * stage_bytes + 1024, st, 1,
+    e = pdl::launch(k_ag_gemm, dim3(tiles_per_src * W, (M + 127) / 128, nr), dim3(gemm::kThreads), size_t(stages) * stage_bytes + 1024, st, 1,
                     maps, p, ctxs, ao, tiles_per_src);
   if (e != cudaSuccess) {
     fprintf(stderr, "[tbvcoll] all-gather->gemm launch failed: %s\n", cudaGetErrorString(e));

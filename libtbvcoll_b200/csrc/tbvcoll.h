@@ -124,6 +124,10 @@ int tbv_comm_skip_next(tbv_comm* c, int n);
 // other ranks' bounded waits run out, the kernel ends, tbv_comm_err turns sticky and
 // tbv_comm_last_error names `r`.  This is how the device watchdog is exercised on one GPU.
 int tbv_comm_mute_rank(tbv_comm* c, int r, int n);
+// 1 if the library was built with -DTBV_BOUNDS_CHECK (python -m libtbvcoll_b200._build --bounds): every collective
+// body then compares the extent it is about to touch with what the communicator reserved, records a violation
+// (sticky error code 3, tbv_comm_last_error) and moves no data instead of making the access.
+int tbv_bounds_checked_build(void);
 // Device time stamps of the last fused GEMM + all-reduce + norm call on (emulated) rank r (see comm.cu).
 int tbv_comm_timestamps(tbv_comm* c, int r, unsigned long long out[8]);
 // TBV_TAG=1 diagnostic: every flag a rank raises is preceded by a sequence stamp in a word of

@@ -9,10 +9,12 @@ the weight fusions it names (q/k/v -> qkv, gate/up -> gate_up, :38).  Per layer:
     -> all-reduce + residual + RMSNorm (ONE kernel)  -> gate_up GEMM with SiLU-mul epilogue
     -> down_proj GEMM (partial sums) -> all-reduce + residual + next RMSNorm (ONE kernel)
 
-With TP > 1 the o_proj / down_proj GEMM, its all-reduce, the residual add and the norm are ONE
-kernel each (the GEMM epilogue stores into the peers' memory), i.e. 5 launches per layer, and
-the two row-parallel all-reduces the reference's hook intercepts (2 per layer;
-step3b/vllm_tp_bench.py:87-124) never appear as separate kernels.
+i.e. 7 launches per layer with TP > 1 (5 GEMM / attention kernels and the two fused collectives the
+reference's hook intercepts as plain all-reduces, 2 per layer; step3b/vllm_tp_bench.py:87-124), chained by
+programmatic dependent launch so that each GEMM streams its weights while the collective before it runs.
+``TBV_FUSE_GEMM_AR=1`` folds each row-parallel GEMM into its collective (one kernel whose epilogue stores LL
+packets into the peers' memory; 5 launches per layer, same bits); it is not the default because it measures
+slower (see ``parallel/tp.py``).
 All buffers are preallocated so a decode step can be captured in a CUDA graph.
 """
 from __future__ import annotations
