@@ -43,6 +43,9 @@ def parse():
     ap.add_argument("--time-nccl", action="store_true", help="per-call synchronised timing of the ORIGINAL all-reduce (invasive)")
     ap.add_argument("--dbo", action="store_true", help="accepted for parity; dual-batch overlap is not a goal here")
     ap.add_argument("--tbv-cap", type=int, default=4 << 20)
+    ap.add_argument("--ar-fusion", default="auto", choices=["auto", "on", "off"],
+                    help="--compile only: vLLM's own all-reduce + RMSNorm fusion pass (it compiles the TP all-reduce away, so a "
+                         "hook on the all-reduce is never called).  auto = off with --tbvcoll, vLLM's default otherwise")
     return ap.parse_args()
 
 
@@ -78,9 +81,16 @@ def main():
         vllm_hook.install(eager=args.tbv_eager)
     model = args.model or synth_model_dir(args.synth or "llama3-8b")
     dummy = not args.model
+    extra = {}
+    fusion_off = args.ar_fusion == "off" or (args.ar_fusion == "auto" and args.tbvcoll)
+    if args.compile and fusion_off:
+        # Under torch.compile current vLLM pattern-matches all_reduce + RMSNorm into its own fused kernel, after which the
+        # TP all-reduce this benchmark is about no longer exists as a call.  Comparable runs switch the pass off on both sides.
+        extra["compilation_config"] = {"pass_config": {"fuse_allreduce_rms": False}}
+        print("# vLLM's all-reduce + RMSNorm fusion pass is OFF for this run (--ar-fusion)", flush=True)
     llm = LLM(model=model, tensor_parallel_size=args.tp, distributed_executor_backend="external_launcher",
               enforce_eager=not args.compile, seed=1, max_model_len=args.max_model_len, gpu_memory_utilization=args.gpu_mem_util,
-              **({"load_format": "dummy", "skip_tokenizer_init": True} if dummy else {}))
+              **({"load_format": "dummy", "skip_tokenizer_init": True} if dummy else {}), **extra)
     sp = SamplingParams(temperature=0.0, max_tokens=args.out_tokens, ignore_eos=True, **({"detokenize": False} if dummy else {}))
     if dummy:
         g = torch.Generator().manual_seed(1234)
