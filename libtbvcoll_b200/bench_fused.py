@@ -66,6 +66,7 @@ def main():
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--tokens", default="1,8,64,256,1024,4096")
     ap.add_argument("--json", default="")
+    ap.add_argument("--stamps", action="store_true", help="print the device time stamps of the last one-kernel call of every size")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", os.environ["RANK"]))
     torch.cuda.set_device(local)
@@ -115,6 +116,11 @@ def main():
             y.copy_(gamma * (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-5)).to(torch.bfloat16))
 
         t_f = time_graph([(lambda w=w: fused(w)) for w in ws], world) if form else float("nan")
+        if args.stamps and form and form.startswith("one") and rank == 0:
+            ts = comm.timestamps(0)            # of the last call of the graph just replayed
+            names = ("finisher resident", "dependency wait passed", "own GEMM CTAs pushed", "first row pulled", "rows normalised",
+                     "last GEMM tile resident", "its accumulator done", "its packets issued")
+            print(f"# T={T} stamps (us after the first): " + "; ".join(f"{n} {(v - ts[0]) / 1e3:+.1f}" for n, v in zip(names, ts)), flush=True)
         t_2 = time_graph([(lambda w=w: two(w)) for w in ws], world)
         t_s = time_graph([(lambda w=w: stock(w)) for w in ws], world)
         flops = 2.0 * T * H * K
