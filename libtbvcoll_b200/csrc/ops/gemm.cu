@@ -299,6 +299,9 @@ int tbv_op_gemm(const void* w, const void* x, void* y, const void* bias, int M, 
     const int th = w_not_constant ? 0 : tbvops::gemm_tok_choose(M, N, K, ldy, epi, persist);   // the many-token kernel always prefetches w
     if (th > 0) return tbvops::gemm_tok_launch(w, x, y, bias, M, N, K, ldx, ldy, epi, th, stream);
   }
+  // Large weight matrices at decode batch sizes: the persistent kernel that splits the work evenly over the SMs.
+  if (tbvops::gemm_streamk_wants(M, N, K, epi, splits_hint, w_not_constant != 0))
+    return tbvops::gemm_streamk_launch(w, x, y, bias, M, N, K, ldx, ldy, epi, stream);
   int bn, splits, stages;
   tbvops::gemm_config(M, N, K, splits_hint, &bn, &splits, &stages);
   CUtensorMap tmA, tmB;

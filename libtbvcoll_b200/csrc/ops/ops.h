@@ -12,6 +12,10 @@ void gemm_config(int M, int N, int K, int splits_hint, int* bn_out, int* splits_
 int gemm_tok_choose(int M, int N, int K, int ldy, int epi, int mode);
 int gemm_tok_launch(const void* w, const void* x, void* y, const void* bias, int M, int N, int K, int ldx, int ldy, int epi, int th,
                     void* stream);
+// evenly-split (stream-K) decode GEMM, gemm_streamk.cu
+bool gemm_streamk_wants(int M, int N, int K, int epi, int splits_hint, bool w_not_constant);
+int gemm_streamk_launch(const void* w, const void* x, void* y, const void* bias, int M, int N, int K, int ldx, int ldy, int epi,
+                        void* stream);
 // threads per CTA for the row-normalisation kernels; the fused collective uses the same
 // mapping so that both produce identical bits
 inline int norm_threads(int hidden) {

@@ -86,9 +86,11 @@ class Engine:
         pin = lambda n, dt: torch.zeros(n, dtype=dt).pin_memory()
         self.ids_h, self.pos_h = pin(B, torch.int64), pin(B, torch.int32)
         self.slots_h, self.ctx_h, self.out_h = pin(B, torch.int64), pin(B, torch.int32), pin(B, torch.int64)
-        # sequence-parallel prefill (GEMM->reduce-scatter, all-gather->GEMM) for chunks whose row count
-        # divides evenly; TBV_SP_PREFILL=0 keeps the all-reduce path
-        self.sp_prefill = os.environ.get("TBV_SP_PREFILL", "1") != "0"
+        # Sequence-parallel prefill (GEMM->reduce-scatter, all-gather->GEMM) for chunks whose row count divides evenly.
+        # Off by default: measured slower than the all-reduce path, whose GEMMs are the persistent many-token kernel
+        # (8 x 512 tokens, 8B shape, TP=2: 62.7 vs 39.9 ms; 16384 tokens, 70B shape, TP=8: 1623 vs 559 ms).  TBV_SP_PREFILL=1
+        # or ``engine.sp_prefill = True`` selects it; both paths produce identical tokens.
+        self.sp_prefill = os.environ.get("TBV_SP_PREFILL", "0") == "1"
         self.sp_chunks = 0
         # query-tiled tensor-core attention for prompt rows (TBV_PREFILL_ATTN=rows: one CTA per query row)
         self.tiled_prefill_attention = os.environ.get("TBV_PREFILL_ATTN", "tiled") != "rows"

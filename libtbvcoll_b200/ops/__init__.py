@@ -35,6 +35,8 @@ def lib():
     l.tbv_op_gemm_error.restype = I
     l.tbv_op_gemm_persist_mode.argtypes = [I]
     l.tbv_op_gemm_persist_mode.restype = None
+    l.tbv_op_gemm_streamk_min_bytes.argtypes = [ctypes.c_long]
+    l.tbv_op_gemm_streamk_min_bytes.restype = None
     l.tbv_op_gemm_qkv_rope.argtypes = [c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, I, c_vp]
     l.tbv_op_gemm_qkv_rope.restype = I
     l.tbv_op_gemm_config.argtypes = [I, I, I, I, ctypes.POINTER(I), ctypes.POINTER(I), ctypes.POINTER(I)]
@@ -80,6 +82,12 @@ def gemm_persist_mode(mode: Optional[int]) -> None:
     """Selection of the many-token (persistent) GEMM: 0 never, 1 where it is estimated faster, 2 / 3 force
     its 128- / 256-token tile; None = read ``TBV_GEMM_PERSIST`` again (the library reads it once)."""
     lib().tbv_op_gemm_persist_mode(-1 if mode is None else int(mode))
+
+
+def gemm_streamk_min_bytes(nbytes: Optional[int]) -> None:
+    """Smallest weight matrix (bytes) that takes the evenly-split (stream-K) decode GEMM at up to 64 tokens:
+    0 = wherever the shape allows, -1 = never, None = read ``TBV_GEMM_SK_MIN`` again (default: never)."""
+    lib().tbv_op_gemm_streamk_min_bytes(-2 if nbytes is None else int(nbytes))
 
 
 launch_count = 0  # kernels launched through this module (for the bench's gpu_launches claim)

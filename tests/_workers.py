@@ -314,6 +314,7 @@ def gpu_engine_tp(rank, world, port):
     tp = TPGroup(rank, world, c)
     src = RandomSource(cfg, seed=3, device=dev)
     eng = Engine(cfg, tp, device=dev, source=src, max_batch=4, max_seq_len=128, prefill_chunk=64)
+    eng.sp_prefill = True          # this engine takes the sequence-parallel prefill path, eng2 below the all-reduce path
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (37, 5, 64, 20)]
     a = eng.generate(prompts, 10, loop="host")

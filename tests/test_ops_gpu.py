@@ -42,6 +42,79 @@ def test_gemm_matches_fp32(ops, N, M, K, splits):
     assert torch.equal(y, y2)
 
 
+@pytest.fixture
+def streamk_everywhere(ops):
+    """The evenly-split decode GEMM for every shape it can take (normally only large weight matrices)."""
+    ops.gemm_streamk_min_bytes(0)
+    yield
+    ops.gemm_streamk_min_bytes(None)
+
+
+def _elementwise_close(y, want, K):
+    """Per-element check: |err| <= bf16 rounding of the result + accumulated input rounding, NOT a fraction of the
+    largest output — a wrong K tail on a small-magnitude element must not hide behind a large one."""
+    err = (y.float() - want).abs()
+    bound = 2.0 ** -7 * want.abs() + 2.0 ** -8 * math.sqrt(K) * 0.05 + 1e-3
+    bad = err > bound
+    assert not bool(bad.any()), (int(bad.sum()), err.max().item())
+
+
+@pytest.mark.parametrize("N,M,K,bias", [(8, 4096, 4096, False), (1, 2048, 5120, True), (64, 1024, 9472, False), (13, 4200, 2056, True),
+                                        (16, 28672, 1024, False), (33, 640, 16384, True)])
+def test_gemm_streamk_matches_fp32(ops, streamk_everywhere, N, M, K, bias):
+    """Work split evenly over the SMs: tiles whose K range is shared by several CTAs are summed through global
+    scratch in a fixed order.  Ragged feature / K edges, one to 64 tokens, strided output, bias; deterministic;
+    correct under CUDA-graph replay (the finishing CTAs clear the flags they consumed)."""
+    x, w = rnd(N, K, seed=31), rnd(M, K, scale=0.05, seed=32)
+    b = rnd(M, seed=33) if bias else None
+    outbuf = torch.zeros(N + 2, M + 64, dtype=torch.bfloat16, device=DEV)
+    y = ops.gemm(x, w, out=outbuf[:N, :M], bias=b)
+    torch.cuda.synchronize()
+    assert not ops.gemm_error()
+    want = ref.gemm(x, w, b)
+    _elementwise_close(y, want, K)
+    assert outbuf[:, M:].abs().max().item() == 0 and outbuf[N:].abs().max().item() == 0
+    y1 = y.clone()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            ops.gemm(x, w, out=outbuf[:N, :M], bias=b)
+            ops.gemm(x, w, out=outbuf[:N, :M], bias=b)
+        for _ in range(3):
+            outbuf.zero_()
+            g.replay()
+            s.synchronize()
+            assert torch.equal(outbuf[:N, :M], y1)            # same bits on every replay
+    torch.cuda.current_stream().wait_stream(s)
+    y_tile = ops.gemm(x, w, bias=b, splits=1)                   # the tile kernel on the same problem
+    torch.cuda.synchronize()
+    assert (y_tile.float() - y1.float()).abs().max().item() <= 0.01 * want.abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("N,I,K", [(8, 14336, 4096), (2, 1280, 8192), (64, 2048, 4160)])
+def test_gemm_streamk_silu_mul(ops, streamk_everywhere, N, I, K):
+    x, wg, wu = rnd(N, K, seed=34), rnd(I, K, scale=0.05, seed=35), rnd(I, K, scale=0.05, seed=36)
+    fused = ops.gemm(x, ops.interleave_gate_up(wg, wu), epi=ops.EPI_SILU_MUL)
+    torch.cuda.synchronize()
+    assert not ops.gemm_error()
+    want = ref.silu_mul(torch.cat((ref.gemm(x, wg), ref.gemm(x, wu)), -1))
+    assert (fused.float() - want).abs().max().item() <= 0.02 * want.abs().max().item() + 1e-3
+    assert torch.equal(fused, ops.gemm(x, ops.interleave_gate_up(wg, wu), epi=ops.EPI_SILU_MUL))
+
+
+def test_gemm_ragged_k_per_element(ops):
+    """The tile kernel on a K that is not a multiple of the 64-wide block, checked element by element."""
+    N, M, K = 9, 384, 1096
+    x, w = rnd(N, K, seed=41), rnd(M, K, scale=0.05, seed=42)
+    w[:, -8:] *= 40.0                                            # the K tail carries real weight: dropping it must show
+    for splits in (1, 2, 4):
+        y = ops.gemm(x, w, splits=splits)
+        torch.cuda.synchronize()
+        _elementwise_close(y, ref.gemm(x, w), K)
+
+
 def test_gemm_bias_and_strided_rows(ops):
     N, M, K = 12, 256, 512
     big = rnd(N, K + 64, seed=3)

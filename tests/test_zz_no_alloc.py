@@ -54,6 +54,11 @@ def test_noalloc_argmax_matches_workspace_argmax_twice_in_a_row():
         torch.cuda.synchronize()
         assert torch.equal(idx, idx2) and torch.equal(val, val2), f"call {call}"
         assert int(idx[tokens // 2]) == 77 + offset
+        # and, independently of this library's other arg-max, against the plain PyTorch statement of the same rule
+        # (largest value, lowest index on ties)
+        from libtbvcoll_b200.ops import reference as plain
+        want_val, want_idx = plain.argmax_first(logits)
+        assert torch.equal(idx, want_idx.to(idx.device) + offset) and torch.equal(val, want_val.to(val.device).float()), f"call {call}"
 
 
 def test_noalloc_argmax_rejects_more_rows_than_the_scratch_holds():
