@@ -278,6 +278,10 @@ def run_ours(args, rank, world, local):
                     "sequence_parallel_chunks": eng.sp_chunks, "note": "wall clock with synchronize, second call, not part of the metric"},
         "baseline_note": "vs_baseline divides by the reference's published 170.9 tok/s (Qwen2.5-7B, vLLM TP=2, 2x gfx1151 laptops)",
     }
+    if comm is not None:
+        # the library's own device time stamps of the collectives of the last replays (kernel entry -> all peers' data seen -> done)
+        _, wait_us, reduce_us, _, _, n_coll = comm.stats5()
+        out["collective_device_us"] = {"wait_for_peers": round(wait_us, 2), "reduce_and_norm": round(reduce_us, 2), "calls_sampled": int(n_coll)}
     if world > 1 and not args.no_extras:
         # the same engine (same weights, same kernels) with the collectives on NCCL at its default settings
         tp_n = TPGroup(rank, world, None)

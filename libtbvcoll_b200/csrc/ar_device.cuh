@@ -915,9 +915,12 @@ __device__ __forceinline__ void rmsnorm_row_store(const float (*h)[8], int nunit
 // thread plays the "virtual" threads threadIdx.x + j * blockDim.x.  Sums are formed in the
 // order of the nt-thread CTA (per-unit, 32-lane butterfly per virtual warp, warps in order), so
 // the result has the same bits as rmsnorm_row_store with blockDim.x == nt.  blockDim.x % 32 == 0.
+// `gpre`: this thread's gamma units already in registers (loaded before a wait so that the load's round trip is not
+// paid after it), or null to load them here.
 template <int VPT>
 __device__ __forceinline__ void rmsnorm_row_store_virtual(const float (*h)[8], int nunits_row, int hidden, float eps,
-                                                          const uint4* __restrict__ gamma, uint4* y_row, float* sh, int nt) {
+                                                          const uint4* __restrict__ gamma, uint4* y_row, float* sh, int nt,
+                                                          const uint4* gpre = nullptr) {
   const int lane = threadIdx.x & 31, nvw = nt >> 5;
   __syncthreads();  // protect sh from the previous use
 #pragma unroll
@@ -942,7 +945,7 @@ __device__ __forceinline__ void rmsnorm_row_store_virtual(const float (*h)[8], i
     const int u = threadIdx.x + j * blockDim.x;
     if (u < nunits_row) {
       float g[8], o[8];
-      Pack<__nv_bfloat16>::unpack(gamma[u], g);
+      Pack<__nv_bfloat16>::unpack(gpre ? gpre[j] : gamma[u], g);
 #pragma unroll
       for (int i = 0; i < 8; i++) {
         float n = __bfloat162float(__float2bfloat16_rn(h[j][i] * rs));
@@ -1020,7 +1023,8 @@ __device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __
 // packets and the packets of all peers are pulled with one batch of loads.  Runs with at most 512
 // threads (128 registers each for the batch); a hidden size whose plain norm kernel uses more
 // threads is handled by two virtual threads per thread, same bits.  hidden <= 8192.
-constexpr int kLLNormVPT = 2;
+constexpr int kLLNormVPT = 2;   // the largest VPT instantiated: hidden <= 8 * 2 * 512
+template <int VPT>
 __device__ inline void ar_rmsnorm_ll_body(const RankCtx& c, const __nv_bfloat16* __restrict__ x,
                                           const __nv_bfloat16* residual, const __nv_bfloat16* __restrict__ gamma,
                                           __nv_bfloat16* residual_out, __nv_bfloat16* y, int tokens, int hidden, float eps,
@@ -1043,10 +1047,24 @@ __device__ inline void ar_rmsnorm_ll_body(const RankCtx& c, const __nv_bfloat16*
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
   const unsigned peers = ((1u << c.world) - 1u) & ~(1u << c.rank);
   unsigned long long t_ready = 0;
-  for (int row = chan; row < tokens; row += nchan) {
-    float h[kLLNormVPT][8];
+  // gamma does not depend on the row: fetch this thread's units once, while the packets are in flight
+  uint4 gpre[VPT];
 #pragma unroll
-    for (int j = 0; j < kLLNormVPT; j++) {
+  for (int j = 0; j < VPT; j++) {
+    const int u = threadIdx.x + j * blockDim.x;
+    gpre[j] = u < upr ? reinterpret_cast<const uint4*>(gamma)[u] : make_uint4(0, 0, 0, 0);
+  }
+  for (int row = chan; row < tokens; row += nchan) {
+    float h[VPT][8];
+    // the residual units of this row too: their round trip overlaps the packets' flight instead of following it
+    uint4 rpre[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+      const int u = threadIdx.x + j * blockDim.x;
+      rpre[j] = u < upr ? reinterpret_cast<const uint4*>(residual)[size_t(row) * upr + u] : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
       const int u = threadIdx.x + j * blockDim.x;
       if (u < upr) {
         const size_t off = size_t(row) * upr + u;
@@ -1056,7 +1074,7 @@ __device__ inline void ar_rmsnorm_ll_body(const RankCtx& c, const __nv_bfloat16*
         float acc[8];
         ll_sum_unit<__nv_bfloat16>(c, got, peers, mine, acc);
         float res[8];
-        Pack<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(residual)[off], res);
+        Pack<__nv_bfloat16>::unpack(rpre[j], res);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           float s = __bfloat162float(__float2bfloat16_rn(acc[i]));
@@ -1066,8 +1084,8 @@ __device__ inline void ar_rmsnorm_ll_body(const RankCtx& c, const __nv_bfloat16*
       }
     }
     if (row == chan && threadIdx.x == 0 && chan == 0) { t_ready = globaltimer(); c.dm->bc[2] = ci.seq; }
-    rmsnorm_row_store_virtual<kLLNormVPT>(h, upr, hidden, eps, reinterpret_cast<const uint4*>(gamma),
-                                          reinterpret_cast<uint4*>(y) + size_t(row) * upr, sh_red, norm_threads);
+    rmsnorm_row_store_virtual<VPT>(h, upr, hidden, eps, reinterpret_cast<const uint4*>(gamma),
+                                          reinterpret_cast<uint4*>(y) + size_t(row) * upr, sh_red, norm_threads, gpre);
   }
   call_end(c, ci, nchan, t_enter, t_ready, size_t(tokens) * hidden * 2, TBV_ALGO_LL);
 }

@@ -241,6 +241,7 @@ __global__ void __launch_bounds__(1024) k_ar_rmsnorm_local(const RankCtx* ctxs, 
                   static_cast<__nv_bfloat16*>(p.aux_out[r]), static_cast<__nv_bfloat16*>(p.out[r]), tokens, hidden, eps,
                   gridDim.x, blockIdx.x, &sh_seq, sh_red);
 }
+template <int VPT>
 __global__ void __launch_bounds__(512) k_ar_rmsnorm_ll(const __grid_constant__ RankCtx c, const __nv_bfloat16* x,
                                                        const __nv_bfloat16* residual, const __nv_bfloat16* gamma,
                                                        __nv_bfloat16* residual_out, __nv_bfloat16* y, int tokens, int hidden,
@@ -249,8 +250,9 @@ __global__ void __launch_bounds__(512) k_ar_rmsnorm_ll(const __grid_constant__ R
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
   __shared__ float sh_red[32];
-  ar_rmsnorm_ll_body(c, x, residual, gamma, residual_out, y, tokens, hidden, eps, gridDim.x, blockIdx.x, norm_threads, &sh_seq, sh_red);
+  ar_rmsnorm_ll_body<VPT>(c, x, residual, gamma, residual_out, y, tokens, hidden, eps, gridDim.x, blockIdx.x, norm_threads, &sh_seq, sh_red);
 }
+template <int VPT>
 __global__ void __launch_bounds__(512) k_ar_rmsnorm_ll_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p,
                                                              const __nv_bfloat16* gamma, int tokens, int hidden, float eps,
                                                              int norm_threads) {
@@ -260,7 +262,7 @@ __global__ void __launch_bounds__(512) k_ar_rmsnorm_ll_local(const RankCtx* ctxs
   __shared__ float sh_red[32];
   const int r = blockIdx.y;
   if (r == p.mute) return;
-  ar_rmsnorm_ll_body(ctxs[r], static_cast<const __nv_bfloat16*>(p.in[r]), static_cast<const __nv_bfloat16*>(p.aux[r]), gamma,
+  ar_rmsnorm_ll_body<VPT>(ctxs[r], static_cast<const __nv_bfloat16*>(p.in[r]), static_cast<const __nv_bfloat16*>(p.aux[r]), gamma,
                      static_cast<__nv_bfloat16*>(p.aux_out[r]), static_cast<__nv_bfloat16*>(p.out[r]), tokens, hidden, eps,
                      gridDim.x, blockIdx.x, norm_threads, &sh_seq, sh_red);
 }
@@ -649,7 +651,11 @@ static bool check_err(tbv_comm* c) {
 // Fold finished calls' device timestamps into the statistics (lazy: runs in the getters).
 static void harvest_trace(tbv_comm* c) {
   if (c->cpu || c->ranks.empty()) return;
+  // The device's own count of completed collectives: calls replayed from a CUDA graph never pass through the
+  // host, so the host-side counter would miss them.  (Synchronous copy; the getters are off the hot path.)
   unsigned long long upto = c->host_seq;
+  DevState ds;
+  if (cudaMemcpy(&ds, c->ranks[0].st, sizeof(ds), cudaMemcpyDeviceToHost) == cudaSuccess && ds.seq > upto) upto = ds.seq;
   if (upto == c->trace_read) return;
   c->trace_host.resize(kTraceN);
   // device -> host copy of the ring (the getters are off the hot path)
@@ -872,11 +878,13 @@ static int gpu_ar_rmsnorm(tbv_comm* c, const void* const* xs, const void* const*
     const RankCtx* ctxs = c->ctxs_dev;
     int ntv = nt;
     void* args[] = {(void*)&ctxs, (void*)&p, (void*)&g, (void*)&tokens, (void*)&hidden, (void*)&eps, (void*)&ntv};
-    e = cudaLaunchCooperativeKernel(ll ? (void*)k_ar_rmsnorm_ll_local : (void*)k_ar_rmsnorm_local, dim3(nchan, c->world), dim3(threads), args, 0, st);
+    void* fn = !ll ? (void*)k_ar_rmsnorm_local : (hidden <= 8 * 512 ? (void*)k_ar_rmsnorm_ll_local<1> : (void*)k_ar_rmsnorm_ll_local<2>);
+    e = cudaLaunchCooperativeKernel(fn, dim3(nchan, c->world), dim3(threads), args, 0, st);
   } else if (c->world == 1) {
     return TBV_FALLBACK;  // nothing to reduce: the caller uses the plain fused add+norm op
   } else if (ll) {
-    e = pdl::launch(k_ar_rmsnorm_ll, dim3(nchan), dim3(threads), 0, st, 1, c->ranks[0].ctx,
+    auto kern = hidden <= 8 * 512 ? k_ar_rmsnorm_ll<1> : k_ar_rmsnorm_ll<2>;   // one 16-byte unit per thread where the row fits
+    e = pdl::launch(kern, dim3(nchan), dim3(threads), 0, st, 1, c->ranks[0].ctx,
                     static_cast<const __nv_bfloat16*>(xs[0]), static_cast<const __nv_bfloat16*>(residuals[0]), g,
                     static_cast<__nv_bfloat16*>(residual_outs[0]), static_cast<__nv_bfloat16*>(ys[0]), tokens, hidden, eps, nt);
   } else {
