@@ -53,6 +53,30 @@ k_gemm_qkv_rope(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int kvh = head < ra.nq ? -1 : (head < ra.nq + ra.nkv ? head - ra.nq : head - ra.nq - ra.nkv);
   __nv_bfloat16* cache = head < ra.nq ? nullptr : (head < ra.nq + ra.nkv ? ra.k_cache : ra.v_cache);
 
+  // Split-K form: the rotation of an output piece needs its token's position, then the cos / sin entries of that
+  // position, then the cache slot — a chain of dependent global loads.  The epilogue threads fetch them for their first
+  // piece while the MMAs run (after their own dependency wait: positions and slots are written by the previous step),
+  // instead of after the reduction.
+  const int pf_half = S > 1 ? 64 / S : 0, pf_q4 = pf_half / 4 > 0 ? pf_half / 4 : 1;
+  const int pf_idx = int(threadIdx.x) - 64;
+  bool pf_ok = false;
+  int pf_pos = 0;
+  long long pf_slot = -1;
+  float4 pf_cos = make_float4(1.f, 1.f, 1.f, 1.f), pf_sin = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (S > 1 && warp >= 2 && pf_idx < rows * pf_q4 && pf_half >= 4) {
+    pdl::grid_dependency_wait();
+    const int t = pf_idx / pf_q4, d = split * pf_half + (pf_idx % pf_q4) * 4;
+    int pos = ra.positions[n0 + t];
+    pos = pos < 0 ? 0 : (pos >= ra.max_pos ? ra.max_pos - 1 : pos);
+    pf_pos = pos;
+    if (rot) {
+      pf_cos = *reinterpret_cast<const float4*>(ra.cos_sin + size_t(pos) * 128 + d);
+      pf_sin = *reinterpret_cast<const float4*>(ra.cos_sin + size_t(pos) * 128 + 64 + d);
+    }
+    if (cache && ra.slot_mapping) pf_slot = ra.slot_mapping[n0 + t];
+    pf_ok = true;
+  }
+
   if (warp >= 2) {
     const int quarter = warp & 3, ml = quarter * 32 + lane;
     bool ok = nkb > 0 ? mbar_wait(smem_u32(&s.accum), 0, abortp, p.limit_ns) : true;
@@ -124,15 +148,24 @@ k_gemm_qkv_rope(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (r == 0) { lo[0] = a.x; lo[1] = a.y; lo[2] = a.z; lo[3] = a.w; hi[0] = b.x; hi[1] = b.y; hi[2] = b.z; hi[3] = b.w; }
           else { lo[0] += a.x; lo[1] += a.y; lo[2] += a.z; lo[3] += a.w; hi[0] += b.x; hi[1] += b.y; hi[2] += b.z; hi[3] += b.w; }
         }
-        int pos = ra.positions[n0 + t];
-        pos = pos < 0 ? 0 : (pos >= ra.max_pos ? ra.max_pos - 1 : pos);
+        const bool pre = pf_ok && idx == pf_idx;   // this thread's first piece: its position, cos / sin and slot are in registers
+        int pos = pf_pos;
+        float cs[4] = {pf_cos.x, pf_cos.y, pf_cos.z, pf_cos.w}, sn[4] = {pf_sin.x, pf_sin.y, pf_sin.z, pf_sin.w};
+        if (!pre) {
+          pos = ra.positions[n0 + t];
+          pos = pos < 0 ? 0 : (pos >= ra.max_pos ? ra.max_pos - 1 : pos);
+          if (rot) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) { cs[e] = ra.cos_sin[size_t(pos) * 128 + d + e]; sn[e] = ra.cos_sin[size_t(pos) * 128 + 64 + d + e]; }
+          }
+        }
         __nv_bfloat16 ol[4], oh[4];
 #pragma unroll
         for (int e = 0; e < 4; e++) {
           const float x1 = bfr(lo[e] + (p.bias ? __bfloat162float(p.bias[m0 + d + e]) : 0.f));
           const float x2 = bfr(hi[e] + (p.bias ? __bfloat162float(p.bias[m0 + d + 64 + e]) : 0.f));
           float o1 = x1, o2 = x2;
-          if (rot) rotate(x1, x2, bfr(ra.cos_sin[size_t(pos) * 128 + d + e]), bfr(ra.cos_sin[size_t(pos) * 128 + 64 + d + e]), o1, o2);
+          if (rot) rotate(x1, x2, bfr(cs[e]), bfr(sn[e]), o1, o2);
           ol[e] = __float2bfloat16_rn(o1);
           oh[e] = __float2bfloat16_rn(o2);
         }
@@ -141,7 +174,7 @@ k_gemm_qkv_rope(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         *reinterpret_cast<uint2*>(dst) = vl;
         *reinterpret_cast<uint2*>(dst + 64) = vh;
         if (cache) {
-          const long long slot = ra.slot_mapping ? ra.slot_mapping[n0 + t] : -1;
+          const long long slot = pre ? pf_slot : (ra.slot_mapping ? ra.slot_mapping[n0 + t] : -1);
           if (slot >= 0) {
             __nv_bfloat16* cd = cache + (size_t(slot) * ra.nkv + kvh) * 128 + d;
             *reinterpret_cast<uint2*>(cd) = vl;
