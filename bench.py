@@ -245,6 +245,11 @@ def run_ours(args, rank, world, local):
     ms_all, prefill_ms, splits, clocks = decode_arm(eng, prompts, new_tokens, B, L, args, world, repeats, ClockSampler(local))
     ms = statistics.median(ms_all)
     value = B / (ms * 1e-3)
+    phases = None
+    if comm is not None:
+        # per-phase device times of the collectives of the last replayed steps, every rank's stamps compared call by call
+        from libtbvcoll_b200.bench_allreduce import trace_breakdown
+        phases = trace_breakdown(comm, calls=1024)
 
     # ---- end to end through the public API: Engine.generate, host loop ----
     eng.generate(prompts, 4)                       # warm the host-loop graph
@@ -281,7 +286,8 @@ def run_ours(args, rank, world, local):
     if comm is not None:
         # the library's own device time stamps of the collectives of the last replays (kernel entry -> all peers' data seen -> done)
         _, wait_us, reduce_us, _, _, n_coll = comm.stats5()
-        out["collective_device_us"] = {"wait_for_peers": round(wait_us, 2), "reduce_and_norm": round(reduce_us, 2), "calls_sampled": int(n_coll)}
+        out["collective_device_us"] = {"wait_for_peers": round(wait_us, 2), "reduce_and_norm": round(reduce_us, 2), "calls_sampled": int(n_coll),
+                                       "phases_all_ranks": phases}
     if world > 1 and not args.no_extras:
         # the same engine (same weights, same kernels) with the collectives on NCCL at its default settings
         tp_n = TPGroup(rank, world, None)

@@ -70,6 +70,42 @@ def graph_us(fn, inner, world):
     return float(t[0])
 
 
+def trace_breakdown(comm, calls=256):
+    """Where the device time of the last `calls` collectives went, from every rank's own time stamps
+    (Comm.trace: kernel entry, own payload issued, every source's payload seen, kernel done; channel 0).
+    The GPUs' timers are not synchronised, so only differences taken on one rank are used; ranks are then
+    compared call by call.  The rank that waited least after its own push was the last to push: its wait is
+    the flight + poll time of the exchange, and the spread between ranks is their arrival skew.  All in us."""
+    rows = comm.trace(0, 1024)[-calls:]
+    n = torch.tensor([len(rows)], dtype=torch.int64, device="cuda")
+    dist.all_reduce(n, op=dist.ReduceOp.MIN)
+    n = int(n)
+    if n < 2:
+        return None
+    mine = torch.tensor(rows[-n:], dtype=torch.int64, device="cuda")
+    world = dist.get_world_size()
+    every = torch.empty((world, n, 5), dtype=torch.int64, device="cuda")
+    dist.all_gather_into_tensor(every, mine)
+    if not bool((every[:, :, 0] == every[0:1, :, 0]).all()):
+        return None                                   # ranks hold different calls: nothing to align
+    t = every.double() * 1e-3
+    enter, pushed, ready, done = t[:, :, 1], t[:, :, 2], t[:, :, 3], t[:, :, 4]
+    has_push = bool((every[:, :, 2] > 0).all())
+    wait = ready - (pushed if has_push else enter)
+    gap = enter[:, 1:] - done[:, :-1]                 # end of one call to the entry of the next, same rank
+    period = done[:, 1:] - done[:, :-1]
+    r2 = lambda v: round(float(v), 2)
+    return {"calls": n,
+            "push_issue": r2((pushed - enter).mean()) if has_push else None,
+            "wait_after_push_least_waiting_rank": r2(wait.min(dim=0).values.mean()),
+            "wait_after_push_mean_rank": r2(wait.mean()),
+            "wait_after_push_most_waiting_rank": r2(wait.max(dim=0).values.mean()),
+            "reduce_store_done": r2((done - ready).mean()),
+            "gap_to_next_call_median": r2(gap.median()),
+            "gap_to_next_call_p90": r2(gap.flatten().quantile(0.9)),
+            "period_median": r2(period.median())}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-tokens", type=int, default=8192)
@@ -77,6 +113,8 @@ def main():
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--json", default="")
     ap.add_argument("--algos", default="auto,ll,oneshot,twoshot,nvls")
+    ap.add_argument("--trace", action="store_true", help="add the per-phase device-time breakdown of the graph-replayed calls to every row")
+    ap.add_argument("--no-nccl", action="store_true")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", os.environ["RANK"]))
     torch.cuda.set_device(local)
@@ -119,6 +157,14 @@ def main():
             row[algo] = {"p50_us": round(p50, 2), "p99_us": round(p99, 2), "graph_us": round(graph_us(lambda: comm.all_reduce(x, out), inner, world), 2),
                          "exact_vs_fixed_order_oracle": exact,
                          "busbw_GBs": round(2 * (world - 1) / world * nbytes / p50 / 1e3, 1)}
+            if args.trace:
+                row[algo]["phases_us"] = trace_breakdown(comm, calls=10 * inner)   # the last replays of the graph
+        if args.no_nccl:
+            rows.append(row)
+            if rank == 0:
+                print(json.dumps(row), flush=True)
+            tokens *= 2
+            continue
         y = x.clone()
         p50, p99 = p50_us(lambda: dist.all_reduce(y), inner, groups, world)
         row["nccl"] = {"p50_us": round(p50, 2), "p99_us": round(p99, 2), "graph_us": round(graph_us(lambda: dist.all_reduce(y), inner, world), 2), "busbw_GBs": round(2 * (world - 1) / world * nbytes / p50 / 1e3, 1)}

@@ -36,6 +36,7 @@ struct TraceRec {
   unsigned long long seq, t_enter, t_ready, t_done;
   unsigned long long nbytes;
   unsigned int algo, nchan;
+  unsigned long long t_pushed;  // channel 0, thread 0: its own packets / payload stores have been issued (0 where a kernel does not stamp it)
 };
 
 // Device-resident diagnostics written on every call: breadcrumbs and the timing ring.  They
@@ -71,6 +72,7 @@ enum : unsigned { kWherePhase0 = 1, kWherePhase1 = 2, kWhereFused = 3,
 // Everything a kernel needs to talk to the other ranks; passed by value.
 struct RankCtx {
   int rank, world, nslot, debug_tag;
+  int ll_wide;                     // LL packets move as one 32-byte store / load per unit instead of two 16-byte ones
   unsigned long long cap;          // bytes per (slot, source-rank) region
   unsigned long long slot_stride;  // bytes per slot = (world + 1) * cap
   unsigned long long wdog_ns;      // bound on every device-side wait
@@ -373,7 +375,7 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   }
   __syncthreads();
   publish(c, ci, 0, chan);
-  if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
+  if (chan == 0 && threadIdx.x == 0) { c.dm->bc[1] = ci.seq; c.dm->ring[ci.seq & (kTraceN - 1)].t_pushed = globaltimer(); }
   wait_all(c, ci, 0, chan, kWherePhase0);
   unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[2] = ci.seq;
@@ -418,13 +420,39 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
 __device__ __forceinline__ void st_v4(void* p, unsigned a, unsigned b, unsigned c2, unsigned d) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c2), "r"(d) : "memory");
 }
+// 256-bit forms (sm_100): one instruction and one fully written 32-byte sector per unit.  Nothing is
+// assumed about their atomicity beyond 8 bytes: every 8-byte piece still carries its own flag.
+__device__ __forceinline__ void st_v8(void* p, unsigned a, unsigned b, unsigned c2, unsigned d, unsigned e, unsigned f,
+                                      unsigned g, unsigned h) {
+  asm volatile("st.volatile.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a), "r"(b), "r"(c2), "r"(d), "r"(e),
+               "r"(f), "r"(g), "r"(h)
+               : "memory");
+}
+__device__ __forceinline__ void ld_volatile_v8(const void* p, uint4& lo, uint4& hi) {
+  asm volatile("ld.volatile.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+               : "l"(p)
+               : "memory");
+}
+__device__ __forceinline__ void ll_load_unit(const RankCtx& c, const char* p, uint4& lo, uint4& hi) {
+  if (c.ll_wide) {
+    ld_volatile_v8(p, lo, hi);
+  } else {
+    lo = ld_volatile_v4(p);
+    hi = ld_volatile_v4(p + 16);
+  }
+}
 // push one 16-byte input unit `v` as two LL lines (32 bytes) at line index u of every peer's region
 __device__ __forceinline__ void ll_push_unit(const RankCtx& c, int slot, size_t u, const uint4& v, unsigned want) {
   for (int d = 1; d < c.world; d++) {
     const int p = (c.rank + d) % c.world;
     char* dst = ll_region(c, p, slot, c.rank) + u * 32;
-    st_v4(dst, v.x, want, v.y, want);
-    st_v4(dst + 16, v.z, want, v.w, want);
+    if (c.ll_wide) {
+      st_v8(dst, v.x, want, v.y, want, v.z, want, v.w, want);
+    } else {
+      st_v4(dst, v.x, want, v.y, want);
+      st_v4(dst + 16, v.z, want, v.w, want);
+    }
   }
 }
 // Pull unit u (two LL lines) of every source rank in `mask` from this rank's own LL area.  All
@@ -439,11 +467,7 @@ __device__ __forceinline__ void ll_pull_all(const RankCtx& c, int slot, size_t u
   const char* base = c.ll[c.rank] + size_t(slot) * c.world * c.ll_cap + u * 32;
 #pragma unroll
   for (int r = 0; r < TBV_MAXRANK; r++)
-    if ((mask >> r) & 1u) {
-      const char* p = base + size_t(r) * c.ll_cap;
-      lo[r] = ld_volatile_v4(p);
-      hi[r] = ld_volatile_v4(p + 16);
-    }
+    if ((mask >> r) & 1u) ll_load_unit(c, base + size_t(r) * c.ll_cap, lo[r], hi[r]);
   unsigned pending = mask, spins = 0;
   unsigned long long t0 = 0;
   for (;;) {
@@ -465,11 +489,7 @@ __device__ __forceinline__ void ll_pull_all(const RankCtx& c, int slot, size_t u
     }
 #pragma unroll
     for (int r = 0; r < TBV_MAXRANK; r++)
-      if ((still >> r) & 1u) {
-        const char* p = base + size_t(r) * c.ll_cap;
-        lo[r] = ld_volatile_v4(p);
-        hi[r] = ld_volatile_v4(p + 16);
-      }
+      if ((still >> r) & 1u) ll_load_unit(c, base + size_t(r) * c.ll_cap, lo[r], hi[r]);
     pending = still;
   }
 #pragma unroll
@@ -512,6 +532,7 @@ __device__ void ar_oneshot_ll_body(const RankCtx& c, const T* __restrict__ in, T
     const uint4 v = (u == uf) ? first : ld_unit(in, u, in_al);
     ll_push_unit(c, ci.slot, u, v, ci.want);
   }
+  if (chan == 0 && threadIdx.x == 0) { c.dm->bc[1] = ci.seq; c.dm->ring[ci.seq & (kTraceN - 1)].t_pushed = globaltimer(); }
   const unsigned peers = ((1u << c.world) - 1u) & ~(1u << c.rank);
   unsigned long long t_ready = 0;
   for (size_t u = uf; u < u1; u += blockDim.x) {
@@ -584,7 +605,7 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
     }
     __syncthreads();
     publish(c, ci, 0, chan);
-    if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
+    if (chan == 0 && threadIdx.x == 0) { c.dm->bc[1] = ci.seq; c.dm->ring[ci.seq & (kTraceN - 1)].t_pushed = globaltimer(); }
     wait_all(c, ci, 0, chan, kWherePhase0);
     if (threadIdx.x == 0 && chan == 0) { t_ready = globaltimer(); c.dm->bc[2] = ci.seq; }
   }
@@ -815,7 +836,7 @@ __device__ void ar_nvls_body(const RankCtx& c, const T* __restrict__ in, T* out,
   }
   __syncthreads();
   publish(c, ci, 0, chan);
-  if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
+  if (chan == 0 && threadIdx.x == 0) { c.dm->bc[1] = ci.seq; c.dm->ring[ci.seq & (kTraceN - 1)].t_pushed = globaltimer(); }
   wait_all(c, ci, 0, chan, kWherePhase0);
   unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   if (direct) {
@@ -983,7 +1004,7 @@ __device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __
   }
   __syncthreads();
   publish(c, ci, 0, chan);
-  if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
+  if (chan == 0 && threadIdx.x == 0) { c.dm->bc[1] = ci.seq; c.dm->ring[ci.seq & (kTraceN - 1)].t_pushed = globaltimer(); }
   wait_all(c, ci, 0, chan, kWhereFused);
   unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   for (int row = chan; row < tokens; row += nchan) {
@@ -1044,7 +1065,7 @@ __device__ inline void ar_rmsnorm_ll_body(const RankCtx& c, const __nv_bfloat16*
       ll_push_unit(c, ci.slot, size_t(row) * upr + u, v, ci.want);
     }
   }
-  if (chan == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
+  if (chan == 0 && threadIdx.x == 0) { c.dm->bc[1] = ci.seq; c.dm->ring[ci.seq & (kTraceN - 1)].t_pushed = globaltimer(); }
   const unsigned peers = ((1u << c.world) - 1u) & ~(1u << c.rank);
   unsigned long long t_ready = 0;
   // gamma does not depend on the row: fetch this thread's units once, while the packets are in flight

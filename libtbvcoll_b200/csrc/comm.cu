@@ -68,6 +68,7 @@ Knobs Knobs::from_env() {
   k.nvls_min = env_long("TBV_NVLS_MIN", LONG_MAX);  // auto never picks the switch-reduced kernel unless asked
   k.nvls_direct_max = env_long("TBV_NVLS_DIRECT_MAX", 1l << 20);
   k.ce = int(env_long("TBV_CE", 0));
+  k.ll_wide = int(env_long("TBV_LL_WIDE", 1)) != 0;
   const char* a = getenv("TBV_ALGO");
   if (a) {
     if (!strcmp(a, "oneshot")) k.algo = TBV_ALGO_ONESHOT;
@@ -320,6 +321,7 @@ static void fill_ctx(tbv_comm* c, GpuRank& g, int rank) {
   x.world = c->world;
   x.nslot = c->knobs.nslot;
   x.debug_tag = c->knobs.tag;
+  x.ll_wide = c->knobs.ll_wide;
   x.cap = c->cap;
   x.slot_stride = size_t(c->world + 1) * c->cap;
   x.ll_cap = c->ll_cap;
@@ -1178,6 +1180,32 @@ void tbv_comm_hist(tbv_comm* c) {
 int tbv_comm_breadcrumbs(tbv_comm* c, int r, unsigned long long out[8]) {
   if (!c || c->cpu || r < 0 || r >= int(c->ranks.size())) return TBV_FAIL;
   return cudaMemcpy(out, c->ranks[r].dm->bc, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? TBV_OK : TBV_FAIL;
+}
+// The timing ring of (emulated) rank r as rows of five numbers: sequence number, then %globaltimer stamps (ns)
+// of channel 0 / thread 0 at kernel entry, own payload issued, every source's payload seen, kernel done.  Only
+// completed calls that are still in the ring are returned, oldest first, at most `max_rows`; returns the row
+// count or TBV_FAIL.  A stamp a kernel does not take reads 0.  Synchronous copy; nothing is reset.
+int tbv_comm_trace(tbv_comm* c, int r, unsigned long long* out, int max_rows) {
+  if (!c || c->cpu || r < 0 || r >= int(c->ranks.size()) || !out || max_rows < 0) return TBV_FAIL;
+  std::vector<TraceRec> ring(kTraceN);
+  DevState ds;
+  if (cudaMemcpy(&ds, c->ranks[r].st, sizeof(ds), cudaMemcpyDeviceToHost) != cudaSuccess) return TBV_FAIL;
+  if (cudaMemcpy(ring.data(), c->ranks[r].dm->ring, sizeof(TraceRec) * kTraceN, cudaMemcpyDeviceToHost) != cudaSuccess) return TBV_FAIL;
+  const unsigned long long upto = ds.seq;
+  unsigned long long from = upto > kTraceN ? upto - kTraceN + 1 : 1;
+  if (upto - from + 1 > (unsigned long long)max_rows) from = upto - max_rows + 1;
+  int n = 0;
+  for (unsigned long long s = from; s <= upto; s++) {
+    const TraceRec& t = ring[s & (kTraceN - 1)];
+    if (t.seq != s) continue;
+    unsigned long long* row = out + size_t(n++) * 5;
+    row[0] = s;
+    row[1] = t.t_enter;
+    row[2] = (t.t_pushed >= t.t_enter && t.t_pushed <= t.t_done) ? t.t_pushed : 0;   // a stale stamp of an older call does not fall inside this one
+    row[3] = t.t_ready;
+    row[4] = t.t_done;
+  }
+  return n;
 }
 // %globaltimer stamps (ns) of the last fused GEMM + all-reduce + norm call on (emulated) rank r:
 // [0] first finisher resident, [1] its dependency wait passed, [2] this rank's GEMM CTAs have all pushed,

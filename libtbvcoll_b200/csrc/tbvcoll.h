@@ -130,6 +130,8 @@ int tbv_comm_mute_rank(tbv_comm* c, int r, int n);
 int tbv_bounds_checked_build(void);
 // Device time stamps of the last fused GEMM + all-reduce + norm call on (emulated) rank r (see comm.cu).
 int tbv_comm_timestamps(tbv_comm* c, int r, unsigned long long out[8]);
+// Per-call device time stamps from the timing ring: rows of {seq, enter, pushed, ready, done} (ns); returns the row count.
+int tbv_comm_trace(tbv_comm* c, int r, unsigned long long* out, int max_rows);
 // TBV_TAG=1 diagnostic: every flag a rank raises is preceded by a sequence stamp in a word of
 // its own next to the flag; the receiver compares it after it has seen the flag.  Totals since
 // the communicator was created (synchronous device-to-host copy).

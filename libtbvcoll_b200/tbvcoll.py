@@ -110,6 +110,8 @@ def load_library(so: Optional[str] = None) -> ctypes.CDLL:
     l.tbv_comm_breadcrumbs.restype = ctypes.c_int
     l.tbv_comm_timestamps.argtypes = [c_vp, ctypes.c_int, c_ullp]
     l.tbv_comm_timestamps.restype = ctypes.c_int
+    l.tbv_comm_trace.argtypes = [c_vp, ctypes.c_int, c_ullp, ctypes.c_int]
+    l.tbv_comm_trace.restype = ctypes.c_int
     for n in ("tbv_comm_create", "tbv_comm_create_local", "tbv_comm_destroy", "tbv_comm_allreduce", "tbv_comm_allreduce_local",
               "tbv_comm_allreduce_rmsnorm", "tbv_comm_allreduce_rmsnorm_local", "tbv_comm_reduce_scatter", "tbv_comm_all_gather",
               "tbv_comm_sync", "tbv_comm_set_algo", "tbv_comm_set_nchan", "tbv_comm_set_wdog", "tbv_comm_skip_next", "tbv_comm_ctx"):
@@ -420,6 +422,16 @@ class Comm:
         if self._l.tbv_comm_timestamps(self._h, r, a) != 0:
             raise RuntimeError("tbv_comm_timestamps failed")
         return list(a)
+
+    def trace(self, r: int = 0, max_rows: int = 1024):
+        """Per-call device time stamps still held in the timing ring, oldest first: a list of
+        (seq, t_enter, t_pushed, t_ready, t_done) in ns of the GPU's own timer (channel 0, thread 0; a stamp a
+        kernel does not take is 0).  The timers of different GPUs are not synchronised: compare differences."""
+        a = (ctypes.c_ulonglong * (5 * max_rows))()
+        n = self._l.tbv_comm_trace(self._h, r, a, max_rows)
+        if n < 0:
+            raise RuntimeError("tbv_comm_trace failed")
+        return [tuple(a[5 * i:5 * i + 5]) for i in range(n)]
 
     def stats5(self):
         v = [ctypes.c_double() for _ in range(5)]
