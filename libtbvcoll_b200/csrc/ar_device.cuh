@@ -931,40 +931,62 @@ __device__ __forceinline__ void rmsnorm_row_store(const float (*h)[8], int nunit
   }
 }
 
-// The same row normalisation run by a CTA of a different size.  `nt` is the thread count the
-// plain op uses for this hidden size (one 16-byte unit per thread: hidden <= 8192); each real
-// thread plays the "virtual" threads threadIdx.x + j * blockDim.x.  Sums are formed in the
-// order of the nt-thread CTA (per-unit, 32-lane butterfly per virtual warp, warps in order), so
-// the result has the same bits as rmsnorm_row_store with blockDim.x == nt.  blockDim.x % 32 == 0.
-// `gpre`: this thread's gamma units already in registers (loaded before a wait so that the load's round trip is not
-// paid after it), or null to load them here.
+// The same row normalisation run by CTAs of a different size, or by the CTAs of a cluster that share one row.
+// `nt` is the thread count the plain op uses for this hidden size (one 16-byte unit per thread: hidden <= 8192);
+// this CTA is part `part` of `nparts` and owns the units [part * per, (part + 1) * per), per = row units / nparts
+// (a multiple of 32, so no 32-unit group is shared by two CTAs); each real thread plays the "virtual" threads
+// part * per + threadIdx.x + j * blockDim.x.  Sums are formed in the order of the nt-thread CTA (per unit, 32-lane
+// butterfly per virtual warp, warps in order), so the result has the same bits as rmsnorm_row_store with
+// blockDim.x == nt.  With nparts > 1 every CTA stores its warps' partial sums into the `sh` array of every CTA of
+// the cluster (distributed shared memory) and one cluster barrier orders them before they are read; `sh` holds two
+// sets of 32 partials used in turn (`phase` = this call's count within the kernel), which makes that one barrier
+// per row enough.  `gpre`: this thread's gamma units already in registers (loaded before a wait so that the load's
+// round trip is not paid after it), or null to load them here.  blockDim.x % 32 == 0.
 template <int VPT>
 __device__ __forceinline__ void rmsnorm_row_store_virtual(const float (*h)[8], int nunits_row, int hidden, float eps,
                                                           const uint4* __restrict__ gamma, uint4* y_row, float* sh, int nt,
-                                                          const uint4* gpre = nullptr) {
+                                                          const uint4* gpre = nullptr, int part = 0, int nparts = 1,
+                                                          int phase = 0) {
   const int lane = threadIdx.x & 31, nvw = nt >> 5;
-  __syncthreads();  // protect sh from the previous use
+  const int per = nunits_row / nparts, u_base = part * per;
+  float* buf = sh + (phase & 1) * 32;
+  if (nparts == 1) __syncthreads();  // protect sh from the previous use (a cluster alternates between two sets instead)
 #pragma unroll
   for (int j = 0; j < VPT; j++) {
-    const int vt = threadIdx.x + j * blockDim.x;
+    const int li = threadIdx.x + j * blockDim.x, vt = u_base + li;
     float ss = 0.f;
-    if (vt < nunits_row) {
+    if (li < per && vt < nunits_row) {
 #pragma unroll
       for (int i = 0; i < 8; i++) ss += h[j][i] * h[j][i];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     const int vw = vt >> 5;
-    if (lane == 0 && vw < nvw) sh[vw] = ss;
+    if (lane == 0 && vw < nvw && li < per) {
+      if (nparts == 1) {
+        buf[vw] = ss;
+      } else {
+        const unsigned mine = unsigned(__cvta_generic_to_shared(buf + vw));
+        for (int q = 0; q < nparts; q++) {
+          unsigned remote;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(mine), "r"(q));
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(ss) : "memory");
+        }
+      }
+    }
   }
-  __syncthreads();
+  if (nparts == 1) {
+    __syncthreads();
+  } else {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
   float tot = 0.f;
-  for (int i = 0; i < nvw; i++) tot += sh[i];
+  for (int i = 0; i < nvw; i++) tot += buf[i];
   const float rs = rsqrtf(tot / float(hidden) + eps);
 #pragma unroll
   for (int j = 0; j < VPT; j++) {
-    const int u = threadIdx.x + j * blockDim.x;
-    if (u < nunits_row) {
+    const int li = threadIdx.x + j * blockDim.x, u = u_base + li;
+    if (li < per && u < nunits_row) {
       float g[8], o[8];
       Pack<__nv_bfloat16>::unpack(gpre ? gpre[j] : gamma[u], g);
 #pragma unroll
@@ -1045,50 +1067,59 @@ __device__ inline void ar_rmsnorm_body(const RankCtx& c, const __nv_bfloat16* __
 // threads (128 registers each for the batch); a hidden size whose plain norm kernel uses more
 // threads is handled by two virtual threads per thread, same bits.  hidden <= 8192.
 constexpr int kLLNormVPT = 2;   // the largest VPT instantiated: hidden <= 8 * 2 * 512
+// LL form of the fused all-reduce + residual + RMSNorm.  Channel c owns rows c, c + nchan, ...; a row is shared by
+// the `nparts` CTAs of a cluster (blockIdx.z = part), each of which pushes, pulls, adds and normalises its own
+// 1 / nparts of the row's units and exchanges only the per-warp sums of squares (see rmsnorm_row_store_virtual).
+// Why parts: an SM hands one 32-byte sector per clock to the fabric, so a CTA that pushes a whole 8 KB row to seven
+// peers (112 KB of packets) spends 2 us on the push alone (measured on 8 GPUs; it grows by 0.3-0.4 us per peer);
+// four CTAs on four SMs spend a quarter of that, and pull a quarter of the packets each.
 template <int VPT>
 __device__ inline void ar_rmsnorm_ll_body(const RankCtx& c, const __nv_bfloat16* __restrict__ x,
                                           const __nv_bfloat16* residual, const __nv_bfloat16* __restrict__ gamma,
                                           __nv_bfloat16* residual_out, __nv_bfloat16* y, int tokens, int hidden, float eps,
-                                          int nchan, int chan, int norm_threads, unsigned long long* sh_seq, float* sh_red) {
-  unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
-  const int upr = hidden / 8;
+                                          int nchan, int chan, int part, int nparts, int norm_threads,
+                                          unsigned long long* sh_seq, float* sh_red) {
+  const bool lead = threadIdx.x == 0 && chan == 0 && part == 0;
+  unsigned long long t_enter = lead ? globaltimer() : 0;
+  const int upr = hidden / 8, per = upr / nparts, u_base = part * per;
   if (!TBV_GUARD(c, size_t(tokens) * hidden * 4, c.guard_ll_cap, kGuardLLBytes, chan)) tokens = 0;
   // first row's first unit: loaded before the sequence number is known
   uint4 first = make_uint4(0, 0, 0, 0);
-  if (chan < tokens && int(threadIdx.x) < upr) first = reinterpret_cast<const uint4*>(x)[size_t(chan) * upr + threadIdx.x];
+  if (chan < tokens && int(threadIdx.x) < per) first = reinterpret_cast<const uint4*>(x)[size_t(chan) * upr + u_base + threadIdx.x];
   CallInfo ci = call_begin(c, sh_seq);
-  if (chan == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
+  if (lead) c.dm->bc[0] = ci.seq;
   for (int row = chan; row < tokens; row += nchan) {
-    const uint4* src = reinterpret_cast<const uint4*>(x) + size_t(row) * upr;
-    for (int u = threadIdx.x; u < upr; u += blockDim.x) {
-      const uint4 v = (row == chan && u == int(threadIdx.x)) ? first : src[u];
-      ll_push_unit(c, ci.slot, size_t(row) * upr + u, v, ci.want);
+    const uint4* src = reinterpret_cast<const uint4*>(x) + size_t(row) * upr + u_base;
+    for (int li = threadIdx.x; li < per; li += blockDim.x) {
+      const uint4 v = (row == chan && li == int(threadIdx.x)) ? first : src[li];
+      ll_push_unit(c, ci.slot, size_t(row) * upr + u_base + li, v, ci.want);
     }
   }
-  if (chan == 0 && threadIdx.x == 0) { c.dm->bc[1] = ci.seq; c.dm->ring[ci.seq & (kTraceN - 1)].t_pushed = globaltimer(); }
+  if (lead) { c.dm->bc[1] = ci.seq; c.dm->ring[ci.seq & (kTraceN - 1)].t_pushed = globaltimer(); }
   const unsigned peers = ((1u << c.world) - 1u) & ~(1u << c.rank);
   unsigned long long t_ready = 0;
   // gamma does not depend on the row: fetch this thread's units once, while the packets are in flight
   uint4 gpre[VPT];
 #pragma unroll
   for (int j = 0; j < VPT; j++) {
-    const int u = threadIdx.x + j * blockDim.x;
-    gpre[j] = u < upr ? reinterpret_cast<const uint4*>(gamma)[u] : make_uint4(0, 0, 0, 0);
+    const int li = threadIdx.x + j * blockDim.x;
+    gpre[j] = li < per ? reinterpret_cast<const uint4*>(gamma)[u_base + li] : make_uint4(0, 0, 0, 0);
   }
-  for (int row = chan; row < tokens; row += nchan) {
+  int iter = 0;
+  for (int row = chan; row < tokens; row += nchan, iter++) {
     float h[VPT][8];
     // the residual units of this row too: their round trip overlaps the packets' flight instead of following it
     uint4 rpre[VPT];
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
-      const int u = threadIdx.x + j * blockDim.x;
-      rpre[j] = u < upr ? reinterpret_cast<const uint4*>(residual)[size_t(row) * upr + u] : make_uint4(0, 0, 0, 0);
+      const int li = threadIdx.x + j * blockDim.x;
+      rpre[j] = li < per ? reinterpret_cast<const uint4*>(residual)[size_t(row) * upr + u_base + li] : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
-      const int u = threadIdx.x + j * blockDim.x;
-      if (u < upr) {
-        const size_t off = size_t(row) * upr + u;
+      const int li = threadIdx.x + j * blockDim.x;
+      if (li < per) {
+        const size_t off = size_t(row) * upr + u_base + li;
         const uint4 mine = (row == chan && j == 0) ? first : reinterpret_cast<const uint4*>(x)[off];
         uint4 got[TBV_MAXRANK];
         ll_pull_all(c, ci.slot, off, ci.want, peers, chan, ci.seq, got);
@@ -1104,11 +1135,11 @@ __device__ inline void ar_rmsnorm_ll_body(const RankCtx& c, const __nv_bfloat16*
         reinterpret_cast<uint4*>(residual_out)[off] = Pack<__nv_bfloat16>::pack(h[j]);
       }
     }
-    if (row == chan && threadIdx.x == 0 && chan == 0) { t_ready = globaltimer(); c.dm->bc[2] = ci.seq; }
+    if (row == chan && lead) { t_ready = globaltimer(); c.dm->bc[2] = ci.seq; }
     rmsnorm_row_store_virtual<VPT>(h, upr, hidden, eps, reinterpret_cast<const uint4*>(gamma),
-                                          reinterpret_cast<uint4*>(y) + size_t(row) * upr, sh_red, norm_threads, gpre);
+                                   reinterpret_cast<uint4*>(y) + size_t(row) * upr, sh_red, norm_threads, gpre, part, nparts, iter);
   }
-  call_end(c, ci, nchan, t_enter, t_ready, size_t(tokens) * hidden * 2, TBV_ALGO_LL);
+  call_end(c, ci, nchan * nparts, t_enter, t_ready, size_t(tokens) * hidden * 2, TBV_ALGO_LL);
 }
 
 }  // namespace tbv

@@ -69,6 +69,8 @@ Knobs Knobs::from_env() {
   k.nvls_direct_max = env_long("TBV_NVLS_DIRECT_MAX", 1l << 20);
   k.ce = int(env_long("TBV_CE", 0));
   k.ll_wide = int(env_long("TBV_LL_WIDE", 1)) != 0;
+  k.ll_spread = int(env_long("TBV_LL_SPREAD", 0));
+  k.ll_threads = int(env_long("TBV_LL_THREADS", 0));
   const char* a = getenv("TBV_ALGO");
   if (a) {
     if (!strcmp(a, "oneshot")) k.algo = TBV_ALGO_ONESHOT;
@@ -242,6 +244,7 @@ __global__ void __launch_bounds__(1024) k_ar_rmsnorm_local(const RankCtx* ctxs, 
                   static_cast<__nv_bfloat16*>(p.aux_out[r]), static_cast<__nv_bfloat16*>(p.out[r]), tokens, hidden, eps,
                   gridDim.x, blockIdx.x, &sh_seq, sh_red);
 }
+// grid (row channels, 1 or emulated ranks, parts); the parts of a row form a cluster along z
 template <int VPT>
 __global__ void __launch_bounds__(512) k_ar_rmsnorm_ll(const __grid_constant__ RankCtx c, const __nv_bfloat16* x,
                                                        const __nv_bfloat16* residual, const __nv_bfloat16* gamma,
@@ -250,8 +253,9 @@ __global__ void __launch_bounds__(512) k_ar_rmsnorm_ll(const __grid_constant__ R
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
-  __shared__ float sh_red[32];
-  ar_rmsnorm_ll_body<VPT>(c, x, residual, gamma, residual_out, y, tokens, hidden, eps, gridDim.x, blockIdx.x, norm_threads, &sh_seq, sh_red);
+  __shared__ float sh_red[64];
+  ar_rmsnorm_ll_body<VPT>(c, x, residual, gamma, residual_out, y, tokens, hidden, eps, gridDim.x, blockIdx.x, blockIdx.z, gridDim.z,
+                          norm_threads, &sh_seq, sh_red);
 }
 template <int VPT>
 __global__ void __launch_bounds__(512) k_ar_rmsnorm_ll_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p,
@@ -260,12 +264,12 @@ __global__ void __launch_bounds__(512) k_ar_rmsnorm_ll_local(const RankCtx* ctxs
   __shared__ unsigned long long sh_seq;
   pdl::launch_dependents();
   pdl::grid_dependency_wait();  // before the device sequence number or any input is read
-  __shared__ float sh_red[32];
+  __shared__ float sh_red[64];
   const int r = blockIdx.y;
-  if (r == p.mute) return;
+  if (r == p.mute) return;      // a whole emulated rank, i.e. whole clusters
   ar_rmsnorm_ll_body<VPT>(ctxs[r], static_cast<const __nv_bfloat16*>(p.in[r]), static_cast<const __nv_bfloat16*>(p.aux[r]), gamma,
-                     static_cast<__nv_bfloat16*>(p.aux_out[r]), static_cast<__nv_bfloat16*>(p.out[r]), tokens, hidden, eps,
-                     gridDim.x, blockIdx.x, norm_threads, &sh_seq, sh_red);
+                          static_cast<__nv_bfloat16*>(p.aux_out[r]), static_cast<__nv_bfloat16*>(p.out[r]), tokens, hidden, eps,
+                          gridDim.x, blockIdx.x, blockIdx.z, gridDim.z, norm_threads, &sh_seq, sh_red);
 }
 
 template <typename T>
@@ -310,7 +314,7 @@ static int pick_nchan(const tbv_comm* c, int algo, size_t units_per_rankchunk, i
   size_t n = (units_per_rankchunk + per_chan_units - 1) / per_chan_units;
   // two-shot: 64 channels keep the latency of mid-size messages low; from 4096 units (64 KiB) per channel on,
   // bandwidth is what counts and more CTAs put more bytes in flight
-  int cap = (algo == TBV_ALGO_ONESHOT || algo == TBV_ALGO_LL) ? 32 : (units_per_rankchunk >= size_t(64) * 4096 ? 128 : 64);
+  int cap = algo == TBV_ALGO_LL ? 64 : (algo == TBV_ALGO_ONESHOT ? 32 : (units_per_rankchunk >= size_t(64) * 4096 ? 128 : 64));
   return int(std::max<size_t>(1, std::min<size_t>(n, size_t(std::min(cap, maxchan)))));
 }
 
@@ -802,7 +806,14 @@ static int gpu_collective(tbv_comm* c, const void* const* ins, void* const* outs
   size_t per_rank_units = oneshot_like ? units : (units + c->world - 1) / c->world;
   if (mode != 0 && per_rank_units * unit != nbytes) return TBV_FALLBACK;  // chunks must be exactly the blocks
   int threads = 512;
-  if (per_rank_units < 512) threads = int(std::max<size_t>(32, (per_rank_units + 31) / 32 * 32));
+  if (algo == TBV_ALGO_LL) {
+    // An SM hands one 32-byte sector per clock to the fabric: keep what one CTA pushes (threads x 32 bytes x peers)
+    // near 28 KB and let more SMs push instead (measured on 8 GPUs: 512 threads spend 2 us in the push, growing with the peers)
+    const int fit = int(28672 / (32 * size_t(c->world - 1)));
+    threads = c->knobs.ll_threads > 0 ? c->knobs.ll_threads : (fit >= 512 ? 512 : (fit >= 256 ? 256 : 128));
+    threads = std::max(32, std::min(512, threads / 32 * 32));
+  }
+  if (per_rank_units < size_t(threads)) threads = int(std::max<size_t>(32, (per_rank_units + 31) / 32 * 32));
   int nchan = pick_nchan(c, algo, per_rank_units, threads);
   cudaError_t e;
   if (c->local) {
@@ -870,7 +881,18 @@ static int gpu_ar_rmsnorm(tbv_comm* c, const void* const* xs, const void* const*
   cudaError_t e;
   const bool ll = (c->knobs.algo == TBV_ALGO_AUTO || c->knobs.algo == TBV_ALGO_LL) && nbytes * 2 <= c->ll_cap &&
                   long(nbytes) <= c->knobs.ll_max && hidden <= 8 * kLLNormVPT * 512;
-  const int threads = ll ? std::min(nt, 512) : nt;
+  // LL form: the CTAs of a cluster share a row so that no SM pushes (or pulls) more than about 28 KB of packets
+  int parts = 1;
+  if (ll) {
+    const int upr = hidden / 8;
+    int want = c->knobs.ll_spread > 0 ? c->knobs.ll_spread : int((size_t(c->world - 1) * upr * 32 + 28671) / 28672);
+    if (c->local) want = std::min(want, std::max(1, maxchan));
+    while (parts * 2 <= 8 && parts < want && upr % (parts * 2 * 32) == 0) parts *= 2;
+    if (c->local) nchan = std::max(1, std::min(tokens, maxchan / parts));
+  }
+  const int per = hidden / 8 / parts;
+  const int threads = ll ? std::min((per + 31) / 32 * 32, 512) : nt;
+  const bool one_unit = ll && per <= threads;     // one 16-byte unit per thread where the part fits
   const __nv_bfloat16* g = static_cast<const __nv_bfloat16*>(gamma);
   if (c->local) {
     LocalPtrs p{};
@@ -880,13 +902,27 @@ static int gpu_ar_rmsnorm(tbv_comm* c, const void* const* xs, const void* const*
     const RankCtx* ctxs = c->ctxs_dev;
     int ntv = nt;
     void* args[] = {(void*)&ctxs, (void*)&p, (void*)&g, (void*)&tokens, (void*)&hidden, (void*)&eps, (void*)&ntv};
-    void* fn = !ll ? (void*)k_ar_rmsnorm_local : (hidden <= 8 * 512 ? (void*)k_ar_rmsnorm_ll_local<1> : (void*)k_ar_rmsnorm_ll_local<2>);
-    e = cudaLaunchCooperativeKernel(fn, dim3(nchan, c->world), dim3(threads), args, 0, st);
+    void* fn = !ll ? (void*)k_ar_rmsnorm_local : (one_unit ? (void*)k_ar_rmsnorm_ll_local<1> : (void*)k_ar_rmsnorm_ll_local<2>);
+    // cooperative: the emulated ranks wait for one another, so every CTA has to be resident
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(nchan, c->world, parts);
+    cfg.blockDim = dim3(threads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = unsigned(parts);
+    cfg.attrs = attr;
+    cfg.numAttrs = parts > 1 ? 2 : 1;
+    e = cudaLaunchKernelExC(&cfg, fn, args);
   } else if (c->world == 1) {
     return TBV_FALLBACK;  // nothing to reduce: the caller uses the plain fused add+norm op
   } else if (ll) {
-    auto kern = hidden <= 8 * 512 ? k_ar_rmsnorm_ll<1> : k_ar_rmsnorm_ll<2>;   // one 16-byte unit per thread where the row fits
-    e = pdl::launch(kern, dim3(nchan), dim3(threads), 0, st, 1, c->ranks[0].ctx,
+    auto kern = one_unit ? k_ar_rmsnorm_ll<1> : k_ar_rmsnorm_ll<2>;
+    e = pdl::launch(kern, dim3(nchan, 1, parts), dim3(threads), 0, st, parts, c->ranks[0].ctx,
                     static_cast<const __nv_bfloat16*>(xs[0]), static_cast<const __nv_bfloat16*>(residuals[0]), g,
                     static_cast<__nv_bfloat16*>(residual_outs[0]), static_cast<__nv_bfloat16*>(ys[0]), tokens, hidden, eps, nt);
   } else {

@@ -45,38 +45,46 @@ def test_exact_all_dtypes_sizes(world, algo):
         c.destroy()
 
 
-@pytest.mark.parametrize("wide", ["0", "1"])
-def test_ll_packet_width_and_call_trace(monkeypatch, wide):
-    """LL packets as one 32-byte store / load per unit (the default) and as two 16-byte ones give the same
-    bits, with and without the fused residual + norm; the per-call trace holds ordered device time stamps."""
+@pytest.mark.parametrize("wide,spread,threads", [("1", "0", "0"), ("0", "0", "0"), ("1", "1", "512"), ("1", "2", "64"), ("1", "8", "128")])
+def test_ll_packet_width_row_sharing_and_call_trace(monkeypatch, wide, spread, threads):
+    """LL packets as one 32-byte store / load per unit (the default) or as two 16-byte ones, a row of the fused
+    residual + norm shared by a cluster of 1 / 2 / 4 / 8 CTAs, the plain LL kernel with 64 - 512 threads per CTA:
+    all give the bits of the fixed-order oracle followed by the plain norm operator; the per-call trace holds
+    ordered device time stamps."""
     from libtbvcoll_b200 import ops
     from libtbvcoll_b200.tbvcoll import Comm
     monkeypatch.setenv("TBV_LL_WIDE", wide)
-    world, T, H = 8, 5, 4096
+    monkeypatch.setenv("TBV_LL_SPREAD", spread)
+    monkeypatch.setenv("TBV_LL_THREADS", threads)
+    world = 8
     c = Comm.local(world, 0, cap_bytes=1 << 18)
     c.set_algo("ll")
     try:
-        ins = [gen(900 + r, T * H, torch.bfloat16) for r in range(world)]
-        outs = [torch.empty_like(t) for t in ins]
-        for _ in range(6):
-            assert c.all_reduce_local(ins, outs)
-        torch.cuda.synchronize()
-        want = oracle(ins)
-        assert all(torch.equal(o, want) for o in outs)
-        res = gen(77, T * H, torch.bfloat16).view(T, H)
-        gamma = gen(78, H, torch.bfloat16)
-        xs = [t.view(T, H) for t in ins]
-        r_out = [torch.empty(T, H, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
-        ys = [torch.empty(T, H, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
-        assert c.all_reduce_rmsnorm_local(xs, [res] * world, gamma, 1e-5, r_out, ys)
-        torch.cuda.synchronize()
-        h = (want.view(T, H).float() + res.float()).to(torch.bfloat16)
-        y_want = torch.empty_like(h)
-        ops.rmsnorm(h, gamma, 1e-5, out=y_want)
-        for r in range(world):
-            assert torch.equal(r_out[r], h) and torch.equal(ys[r], y_want)
+        calls = 0
+        for T, H in ((5, 4096), (3, 8192), (2, 1024)):
+            ins = [gen(900 + r, T * H, torch.bfloat16) for r in range(world)]
+            outs = [torch.empty_like(t) for t in ins]
+            for _ in range(3):
+                assert c.all_reduce_local(ins, outs)
+            torch.cuda.synchronize()
+            want = oracle(ins)
+            assert all(torch.equal(o, want) for o in outs)
+            res = gen(77, T * H, torch.bfloat16).view(T, H)
+            gamma = gen(78, H, torch.bfloat16)
+            xs = [t.view(T, H) for t in ins]
+            r_out = [torch.empty(T, H, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+            ys = [torch.empty(T, H, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+            for _ in range(2):
+                assert c.all_reduce_rmsnorm_local(xs, [res] * world, gamma, 1e-5, r_out, ys)
+            torch.cuda.synchronize()
+            h = (want.view(T, H).float() + res.float()).to(torch.bfloat16)
+            y_want = torch.empty_like(h)
+            ops.rmsnorm(h, gamma, 1e-5, out=y_want)
+            for r in range(world):
+                assert torch.equal(r_out[r], h) and torch.equal(ys[r], y_want), (T, H, r)
+            calls += 5
         rows = c.trace(0)
-        assert len(rows) == 7 and [r[0] for r in rows] == list(range(1, 8))
+        assert len(rows) == calls and [r[0] for r in rows] == list(range(1, calls + 1))
         for seq, t_enter, t_pushed, t_ready, t_done in rows:
             assert 0 < t_enter <= t_pushed <= t_ready <= t_done, rows
         assert len(c.trace(3, max_rows=2)) == 2 and not c.err()
