@@ -90,20 +90,22 @@ def trace_breakdown(comm, calls=256):
         return None                                   # ranks hold different calls: nothing to align
     t = every.double() * 1e-3
     enter, pushed, ready, done = t[:, :, 1], t[:, :, 2], t[:, :, 3], t[:, :, 4]
-    has_push = bool((every[:, :, 2] > 0).all())
-    wait = ready - (pushed if has_push else enter)
     gap = enter[:, 1:] - done[:, :-1]                 # end of one call to the entry of the next, same rank
     period = done[:, 1:] - done[:, :-1]
+    stamped = (every[:, :, 2] > 0).all(dim=0)         # calls whose kernel stamps the end of its push (on every rank)
     r2 = lambda v: round(float(v), 2)
-    return {"calls": n,
-            "push_issue": r2((pushed - enter).mean()) if has_push else None,
-            "wait_after_push_least_waiting_rank": r2(wait.min(dim=0).values.mean()),
-            "wait_after_push_mean_rank": r2(wait.mean()),
-            "wait_after_push_most_waiting_rank": r2(wait.max(dim=0).values.mean()),
-            "reduce_store_done": r2((done - ready).mean()),
-            "gap_to_next_call_median": r2(gap.median()),
-            "gap_to_next_call_p90": r2(gap.flatten().quantile(0.9)),
-            "period_median": r2(period.median())}
+    out = {"calls": n, "calls_with_push_stamp": int(stamped.sum()),
+           "enter_to_all_sources_seen": r2((ready - enter).mean()),
+           "reduce_store_done": r2((done - ready).mean()),
+           "gap_to_next_call_median": r2(gap.median()), "gap_to_next_call_p90": r2(gap.flatten().quantile(0.9)),
+           "period_median": r2(period.median())}
+    if bool(stamped.any()):
+        wait = (ready - pushed)[:, stamped]
+        out.update({"push_issue": r2((pushed - enter)[:, stamped].mean()),
+                    "wait_after_push_least_waiting_rank": r2(wait.min(dim=0).values.mean()),
+                    "wait_after_push_mean_rank": r2(wait.mean()),
+                    "wait_after_push_most_waiting_rank": r2(wait.max(dim=0).values.mean())})
+    return out
 
 
 def main():
