@@ -343,6 +343,31 @@ __device__ __forceinline__ void wait_all(const RankCtx& c, const CallInfo& ci, i
   __syncthreads();
 }
 
+// Unit `idx` of the regions that the source ranks in `mask` own in `owner`'s slot memory: every load is issued
+// before any value is used (fully unrolled, constant indices), so a reduce step pays one memory round trip and
+// not one per source rank.  The sum itself stays in rank order (sum_units_rank_order).
+__device__ __forceinline__ void gather_units(const RankCtx& c, int owner, int slot, size_t idx, unsigned mask,
+                                             uint4 (&got)[TBV_MAXRANK]) {
+#pragma unroll
+  for (int r = 0; r < TBV_MAXRANK; r++)
+    if ((mask >> r) & 1u) got[r] = ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, owner, slot, r)) + idx);
+}
+// rank-ordered fp32 sum of one unit: `mine` stands in for every rank below the world size whose bit is not set in `mask`
+template <typename T>
+__device__ __forceinline__ void sum_units_rank_order(const RankCtx& c, const uint4 (&got)[TBV_MAXRANK], unsigned mask,
+                                                     const uint4& mine, float* acc) {
+#pragma unroll
+  for (int r = 0; r < TBV_MAXRANK; r++) {
+    if (r < c.world) {
+      const uint4 v = ((mask >> r) & 1u) ? got[r] : mine;
+      float f[Pack<T>::N];
+      Pack<T>::unpack(v, f);
+#pragma unroll
+      for (int i = 0; i < Pack<T>::N; i++) acc[i] = (r == 0) ? f[i] : acc[i] + f[i];
+    }
+  }
+}
+
 // ---- one-shot all-reduce ------------------------------------------------------------
 // VEC: 16-byte units (nbytes % 16 == 0); otherwise one element per unit.  io: kInAligned /
 // kOutAligned say whether the caller's tensors can be accessed 16 bytes at a time.
@@ -381,21 +406,16 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[2] = ci.seq;
 
   // reduce in rank order, fp32, one rounding
+  const unsigned peers = ((1u << c.world) - 1u) & ~(1u << c.rank);
   for (size_t u = u0 + threadIdx.x; u < u1; u += blockDim.x) {
     if (VEC) {
       float acc[Pack<T>::N];
 #pragma unroll
       for (int i = 0; i < Pack<T>::N; i++) acc[i] = 0.f;
       uint4 mine = ld_unit(in, u, in_al);
-      for (int r = 0; r < c.world; r++) {
-        uint4 v = (r == c.rank)
-                      ? mine
-                      : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, ci.slot, r)) + u);
-        float f[Pack<T>::N];
-        Pack<T>::unpack(v, f);
-#pragma unroll
-        for (int i = 0; i < Pack<T>::N; i++) acc[i] = (r == 0) ? f[i] : acc[i] + f[i];
-      }
+      uint4 got[TBV_MAXRANK];
+      gather_units(c, c.rank, ci.slot, u, peers, got);
+      sum_units_rank_order<T>(c, got, peers, mine, acc);
       st_unit(out, u, Pack<T>::pack(acc), out_al);
     } else {
       float acc = 0.f;
@@ -496,20 +516,10 @@ __device__ __forceinline__ void ll_pull_all(const RankCtx& c, int slot, size_t u
   for (int r = 0; r < TBV_MAXRANK; r++)
     if ((mask >> r) & 1u) out[r] = make_uint4(lo[r].x, lo[r].z, hi[r].x, hi[r].z);
 }
-// rank-ordered fp32 sum of one unit: `mine` stands in for this rank unless its bit is set in `mask`
 template <typename T>
 __device__ __forceinline__ void ll_sum_unit(const RankCtx& c, const uint4 (&got)[TBV_MAXRANK], unsigned mask, const uint4& mine,
                                             float* acc) {
-#pragma unroll
-  for (int r = 0; r < TBV_MAXRANK; r++) {
-    if (r < c.world) {
-      const uint4 v = ((mask >> r) & 1u) ? got[r] : mine;
-      float f[Pack<T>::N];
-      Pack<T>::unpack(v, f);
-#pragma unroll
-      for (int i = 0; i < Pack<T>::N; i++) acc[i] = (r == 0) ? f[i] : acc[i] + f[i];
-    }
-  }
+  sum_units_rank_order<T>(c, got, mask, mine, acc);
 }
 
 template <typename T>
@@ -613,6 +623,7 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   {
     // reduce my chunk; write it out and (all-reduce) push it to every peer's result region
     size_t len = chunk_len(me), b = sub_begin(len), e = sub_end(len);
+    const unsigned others = ((1u << W) - 1u) & ~(1u << me);
     for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) {
       if (VEC) {
         uint4 res;
@@ -623,14 +634,9 @@ __device__ void ar_twoshot_body(const RankCtx& c, const T* __restrict__ in, T* o
 #pragma unroll
           for (int k = 0; k < Pack<T>::N; k++) acc[k] = 0.f;
           const uint4 mine = ld_unit(in, cu * me + i, in_al);
-          for (int r = 0; r < W; r++) {
-            uint4 v = (r == me) ? mine
-                                : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, me, ci.slot, r)) + i);
-            float f[Pack<T>::N];
-            Pack<T>::unpack(v, f);
-#pragma unroll
-            for (int k = 0; k < Pack<T>::N; k++) acc[k] = (r == 0) ? f[k] : acc[k] + f[k];
-          }
+          uint4 got[TBV_MAXRANK];
+          gather_units(c, me, ci.slot, i, others, got);
+          sum_units_rank_order<T>(c, got, others, mine, acc);
           res = Pack<T>::pack(acc);
         }
         if (mode == 1) {
@@ -730,18 +736,15 @@ __device__ void ar_ce_phase_a(const RankCtx& c, const T* __restrict__ in, T* out
   if (chan == 0 && threadIdx.x == 0) { c.dm->bc[2] = ci.seq; c.dm->ts[1] = globaltimer(); }
   const uint4* mine = reinterpret_cast<const uint4*>(in) + cu * me;
   uint4* dst = reinterpret_cast<uint4*>(out) + cu * me;
+  const unsigned others = ((1u << W) - 1u) & ~(1u << me);
   for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) {
     float acc[Pack<T>::N];
 #pragma unroll
     for (int k = 0; k < Pack<T>::N; k++) acc[k] = 0.f;
     const uint4 own = mine[i];
-    for (int r = 0; r < W; r++) {
-      const uint4 v = (r == me) ? own : ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, me, ci.slot, r)) + i);
-      float f[Pack<T>::N];
-      Pack<T>::unpack(v, f);
-#pragma unroll
-      for (int k = 0; k < Pack<T>::N; k++) acc[k] = (r == 0) ? f[k] : acc[k] + f[k];
-    }
+    uint4 got[TBV_MAXRANK];
+    gather_units(c, me, ci.slot, i, others, got);
+    sum_units_rank_order<T>(c, got, others, own, acc);
     dst[i] = Pack<T>::pack(acc);
   }
 }

@@ -130,13 +130,10 @@ k_rs_reduce_norm(const RankCtx* ctxs, const __grid_constant__ RsPtrs ptrs, const
     if (u < upr) {
       const size_t off = size_t(row) * upr + u;
       float acc[8];
-      for (int r = 0; r < c.world; r++) {
-        uint4 v = ld_volatile_v4(reinterpret_cast<const uint4*>(slot_region(c, c.rank, slot, r)) + off);
-        float f[8];
-        Pack<__nv_bfloat16>::unpack(v, f);
-#pragma unroll
-        for (int i = 0; i < 8; i++) acc[i] = (r == 0) ? f[i] : acc[i] + f[i];
-      }
+      uint4 got[TBV_MAXRANK];
+      const unsigned all = (1u << c.world) - 1u;
+      gather_units(c, c.rank, slot, off, all, got);
+      sum_units_rank_order<__nv_bfloat16>(c, got, all, got[0], acc);
       if (mode == 0) {
         reinterpret_cast<uint4*>(ptrs.out[er])[off] = Pack<__nv_bfloat16>::pack(acc);
       } else {
