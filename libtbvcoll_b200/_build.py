@@ -78,10 +78,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                 print(log, file=sys.stderr)
     newest = max(o.stat().st_mtime for o in objs)
     if force or not LIB.exists() or LIB.stat().st_mtime < newest:
-        cmd = [nvcc(), *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-lrt", "-lpthread", "-ldl"]
-        p = subprocess.run(cmd, capture_output=True, text=True)
-        if p.returncode != 0:
-            raise RuntimeError(f"link failed:\n{p.stdout}\n{p.stderr}")
+        _link(LIB, objs)
     # standalone microbenchmark executable (counterpart of the reference's ar2/armr binaries)
     proto = CSRC / "proto" / "arbench.cu"
     if proto.exists() and (force or not AR_BENCH.exists() or AR_BENCH.stat().st_mtime < max(proto.stat().st_mtime, LIB.stat().st_mtime)):
@@ -91,6 +88,18 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if p.returncode != 0:
             raise RuntimeError(f"arbench build failed:\n{p.stdout}\n{p.stderr}")
     return LIB
+
+
+def _link(target: Path, objs) -> None:
+    """Link under a temporary name and rename into place: a reader (a process that has the library mapped, a copy
+    of the tree being taken) sees the old file or the new one, never a half-written one."""
+    tmp = target.with_name(target.name + f".tmp{os.getpid()}")
+    cmd = [nvcc(), *ARCH, "-shared", "-o", str(tmp), *map(str, objs), "-lrt", "-lpthread", "-ldl"]
+    p = subprocess.run(cmd, capture_output=True, text=True)
+    if p.returncode != 0:
+        tmp.unlink(missing_ok=True)
+        raise RuntimeError(f"link failed:\n{p.stdout}\n{p.stderr}")
+    os.replace(tmp, target)
 
 
 def build_bounds(force: bool = False) -> Path:
@@ -103,10 +112,7 @@ def build_bounds(force: bool = False) -> Path:
         objs = [o for o, _ in ex.map(lambda s: _compile(s, force, False, hdr_m, bounds=True), srcs)]
     newest = max(o.stat().st_mtime for o in objs)
     if force or not LIB_BOUNDS.exists() or LIB_BOUNDS.stat().st_mtime < newest:
-        cmd = [nvcc(), *ARCH, "-shared", "-o", str(LIB_BOUNDS), *map(str, objs), "-lrt", "-lpthread", "-ldl"]
-        p = subprocess.run(cmd, capture_output=True, text=True)
-        if p.returncode != 0:
-            raise RuntimeError(f"link failed:\n{p.stdout}\n{p.stderr}")
+        _link(LIB_BOUNDS, objs)
     return LIB_BOUNDS
 
 

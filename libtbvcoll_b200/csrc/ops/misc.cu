@@ -225,6 +225,15 @@ int tbv_op_decode_advance(const void* next_ids, void* ids, void* positions, void
   return e == cudaSuccess ? 0 : -1;
 }
 
+// One plain asynchronous copy on `stream` (pinned host <-> device, or device <-> device): what a serving loop uses to
+// bring a step's packed inputs in and the sampled tokens out.  It can be captured into a CUDA graph together with the
+// step's kernels, so that a step costs the host one graph launch.
+int tbv_op_copy_async(void* dst, const void* src, size_t bytes, void* stream) {
+  if (!dst || !src) return -2;
+  if (bytes == 0) return 0;
+  return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)) == cudaSuccess ? 0 : -1;
+}
+
 int tbv_op_rope_kv(void* qkv, const void* positions, const void* cos_sin, const void* slot_mapping, void* k_cache, void* v_cache,
                    int tokens, int nq, int nkv, int D, int max_pos, void* stream) {
   if (tokens <= 0) return 0;

@@ -57,6 +57,17 @@ def prefill_rows(prompts: Sequence[Sequence[int]], tables: np.ndarray, block_siz
     return total, seq_all, pos_all, ids_all, slots_all, is_last
 
 
+class _GraphChain:
+    """Graphs that are always replayed one after the other on the current stream."""
+
+    def __init__(self, graphs):
+        self.graphs = list(graphs)
+
+    def replay(self) -> None:
+        for g in self.graphs:
+            g.replay()
+
+
 class Engine:
     def __init__(self, cfg: ModelConfig, tp: Optional[TPGroup] = None, device="cuda:0", weights: Optional[Dict[str, torch.Tensor]] = None,
                  source=None, seed: int = 0, max_batch: int = 8, max_seq_len: int = 1024, block_size: int = 16,
@@ -75,17 +86,24 @@ class Engine:
         self.model = LlamaTP(cfg, self.tp, weights, self.device, max_tokens=max(prefill_chunk, max_batch), max_batch=max_batch,
                              num_blocks=num_blocks, block_size=block_size, max_attn_splits=max_attn_splits)
         dev, B = self.device, max_batch
-        # static decode inputs/outputs (graph-captured addresses) and their pinned mirrors
-        self.ids = torch.zeros(B, dtype=torch.int64, device=dev)
-        self.positions = torch.zeros(B, dtype=torch.int32, device=dev)
-        self.slots = torch.zeros(B, dtype=torch.int64, device=dev)
-        self.ctx = torch.ones(B, dtype=torch.int32, device=dev)
+        # Static decode inputs (graph-captured addresses): ONE device block and ONE pinned mirror, so that a step's inputs
+        # cross PCIe as a single copy:  ids int64[B] | cache slots int64[B] | positions int32[B] | context lengths int32[B]
+        self.in_d = torch.zeros(24 * B, dtype=torch.uint8, device=dev)
+        self.in_h = torch.zeros(24 * B, dtype=torch.uint8).pin_memory()
+        carve = lambda buf: (buf[0:8 * B].view(torch.int64), buf[8 * B:16 * B].view(torch.int64),
+                             buf[16 * B:20 * B].view(torch.int32), buf[20 * B:24 * B].view(torch.int32))
+        self.ids, self.slots, self.positions, self.ctx = carve(self.in_d)
+        self.ids_h, self.slots_h, self.pos_h, self.ctx_h = carve(self.in_h)
+        self.ctx.fill_(1)
+        self.ctx_h.fill_(1)
         self.out_tokens = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.out_h = torch.zeros(B, dtype=torch.int64).pin_memory()
+        self.h2d_bytes_per_step, self.d2h_bytes_per_step = 24 * B, 8 * B
+        # serving loop: layers in a short first graph of a step (0 = one graph per step, the default: measured 3.327 ms per step
+        # with 0, 3.323 / 3.327 / 3.348 with 1 / 2 / 4 head layers on the 8B shape; replaying the graph costs the host 13 us); see capture()
+        self.serve_head_layers = int(os.environ.get("TBV_SERVE_HEAD", "0"))
         self.step_counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.history = torch.zeros(max_seq_len, B, dtype=torch.int64, device=dev)
-        pin = lambda n, dt: torch.zeros(n, dtype=dt).pin_memory()
-        self.ids_h, self.pos_h = pin(B, torch.int64), pin(B, torch.int32)
-        self.slots_h, self.ctx_h, self.out_h = pin(B, torch.int64), pin(B, torch.int32), pin(B, torch.int64)
         # Sequence-parallel prefill (GEMM->reduce-scatter, all-gather->GEMM) for chunks whose row count divides evenly.
         # Off by default: measured slower than the all-reduce path, whose GEMMs are the persistent many-token kernel
         # (8 x 512 tokens, 8B shape, TP=2: 62.7 vs 39.9 ms; 16384 tokens, 70B shape, TP=8: 1623 vs 559 ms).  TBV_SP_PREFILL=1
@@ -142,10 +160,10 @@ class Engine:
         return first
 
     # ---- decode -------------------------------------------------------------------------------
-    def _decode_step(self, B: int, splits: int, advance: bool) -> None:
+    def _decode_step(self, B: int, splits: int, advance: bool, layer_begin: int = 0, layer_end: Optional[int] = None) -> None:
         self.model.forward(B, self.ids[:B], self.positions[:B], self.slots[:B], self.bm.tables, self.ctx[:B], None, None, B,
-                           self.out_tokens, attn_splits=splits)
-        if advance:
+                           self.out_tokens, attn_splits=splits, layer_begin=layer_begin, layer_end=layer_end)
+        if advance and (layer_end is None or layer_end == self.cfg.num_layers):
             ops.decode_advance(self.out_tokens[:B], self.ids[:B], self.positions[:B], self.ctx[:B], self.slots[:B], self.bm.tables,
                                self.block_size, self.history, self.step_counter)
 
@@ -158,24 +176,38 @@ class Engine:
             s *= 2
         return min(s, self.model.max_attn_splits)
 
-    def capture(self, B: int, splits: int, advance: bool) -> torch.cuda.CUDAGraph:
-        """Capture one decode step (all layers, both collectives per layer, sampling) as a graph."""
-        key = (B, splits, advance)
+    def capture(self, B: int, splits: int, advance: bool, io: bool = False):
+        """Capture one decode step (all layers, both collectives per layer, sampling) as a graph.  ``io=True`` is the
+        serving form: the step starts with the copy of the packed inputs from pinned memory and ends with the copy of
+        the sampled tokens back to pinned memory, so that a step costs the host one graph launch.  With
+        ``serve_head_layers`` > 0 it is captured as TWO graphs, a short head (copy in, embedding, the first layers) and
+        the rest, so that the launch of the long tail overlaps the head's execution (the host cannot launch a step
+        before it has read the previous step's tokens).  The returned object has ``replay()``."""
+        key = (B, splits, advance, io)
         if key in self.graphs:
             return self.graphs[key]
+        L = self.cfg.num_layers
+        head = min(max(0, self.serve_head_layers), L) if io else 0
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream(self.device))
+        parts = []
         with torch.cuda.stream(s):
             self._decode_step(B, splits, False)      # eager warm-up: idempotent (no advance)
             s.synchronize()
             n0 = ops.launch_count + self.tp.launches
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=s):
-                self._decode_step(B, splits, advance)
+            for lo, hi in ([(0, head), (head, L)] if 0 < head < L else [(0, L)]):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=s):
+                    if io and lo == 0:
+                        ops.copy_async(self.in_d, self.in_h)
+                    self._decode_step(B, splits, advance, lo, hi)
+                    if io and hi == L:
+                        ops.copy_async(self.out_h, self.out_tokens)
+                parts.append(g)
             self.launches_per_step = ops.launch_count + self.tp.launches - n0
         torch.cuda.current_stream(self.device).wait_stream(s)
-        self.graphs[key] = g
-        return g
+        self.graphs[key] = parts[0] if len(parts) == 1 else _GraphChain(parts)
+        return self.graphs[key]
 
     def _load_decode_inputs(self, B: int, tokens, lens) -> None:
         """Stage one step's inputs in pinned memory (vectorised on the numpy views of the pinned
@@ -187,10 +219,7 @@ class Engine:
         self._ctx_np[:B] = pos + 1
         bs = self.block_size
         self._slots_np[:B] = self._tables_np[np.arange(B), pos // bs].astype(np.int64) * bs + pos % bs
-        self.ids[:B].copy_(self.ids_h[:B], non_blocking=True)
-        self.positions[:B].copy_(self.pos_h[:B], non_blocking=True)
-        self.slots[:B].copy_(self.slots_h[:B], non_blocking=True)
-        self.ctx[:B].copy_(self.ctx_h[:B], non_blocking=True)
+        ops.copy_async(self.in_d, self.in_h)
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int, loop: str = "host", use_graph: bool = True,
                  eos_id: Optional[int] = None) -> List[List[int]]:
@@ -223,23 +252,34 @@ class Engine:
             for b in range(B):
                 outs[b].extend(hist[:, b].tolist())
         else:
-            g = self.capture(B, splits, False) if use_graph else None
+            # Serving shape: every step copies its inputs from pinned memory to the device and reads the sampled tokens
+            # back.  Positions, cache slots and context lengths of all steps are laid out before the loop (they do not
+            # depend on what is sampled); a step then costs the host four small array writes, one graph launch (copy in,
+            # the step's kernels, copy out) and one stream synchronisation.
             import numpy as np
+            g = self.capture(B, splits, False, io=True) if use_graph else None
             cur = np.asarray(first, dtype=np.int64)
-            lens_np = np.asarray(lens, dtype=np.int64)
+            bs = self.block_size
+            pos_all = np.asarray(lens, dtype=np.int64)[None, :] + np.arange(steps, dtype=np.int64)[:, None]      # [steps, B]
+            slots_all = self._tables_np[np.arange(B)[None, :], pos_all // bs].astype(np.int64) * bs + pos_all % bs
+            pos32, ctx32 = pos_all.astype(np.int32), (pos_all + 1).astype(np.int32)
+            ids_np, slots_np, pos_np, ctx_np, out_np = self._ids_np, self._slots_np, self._pos_np, self._ctx_np, self._out_np
             done = np.zeros(B, dtype=bool)
             trace = []
-            stream = torch.cuda.current_stream(self.device)
-            for _ in range(steps):
-                self._load_decode_inputs(B, cur, lens_np)
+            sync = torch.cuda.current_stream(self.device).synchronize
+            for i in range(steps):
+                ids_np[:B] = cur
+                slots_np[:B] = slots_all[i]
+                pos_np[:B] = pos32[i]
+                ctx_np[:B] = ctx32[i]
                 if g is not None:
                     g.replay()
                 else:
+                    ops.copy_async(self.in_d, self.in_h)
                     self._decode_step(B, splits, False)
-                self.out_h[:B].copy_(self.out_tokens[:B], non_blocking=True)
-                stream.synchronize()
-                cur = self._out_np[:B].copy()
-                lens_np += 1
+                    ops.copy_async(self.out_h, self.out_tokens)
+                sync()
+                cur = out_np[:B].copy()
                 trace.append((cur, done.copy()))
                 if eos_id is not None:
                     done |= cur == eos_id

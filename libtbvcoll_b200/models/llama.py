@@ -67,19 +67,25 @@ class LlamaTP:
     # -- one forward pass over T token rows ----------------------------------------------------
     def forward(self, T: int, ids: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor, block_tables: torch.Tensor,
                 ctx_lens: torch.Tensor, seq_of_query: Optional[torch.Tensor], logit_rows: Optional[torch.Tensor], n_logits: int,
-                out_tokens: torch.Tensor, attn_splits: int = 1, prefill_tiles: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out_tokens: torch.Tensor, attn_splits: int = 1, prefill_tiles: Optional[torch.Tensor] = None,
+                layer_begin: int = 0, layer_end: Optional[int] = None) -> Optional[torch.Tensor]:
         """ids/positions/slot_mapping/ctx_lens: [T]; logit_rows: int64 [n_logits] rows whose next
-        token is wanted (None = all T rows, decode).  Writes greedy tokens to out_tokens[:n_logits]."""
+        token is wanted (None = all T rows, decode).  Writes greedy tokens to out_tokens[:n_logits].
+        ``layer_begin`` / ``layer_end`` run a slice of the model (the state between slices lives in this object's
+        static buffers): the embedding and first norm belong to the slice that starts at layer 0, the LM head and
+        the sampling to the slice that ends at the last layer; other slices return None."""
         cfg, w, tp = self.cfg, self.w, self.tp
-        assert T <= self.max_tokens and n_logits <= self.max_batch
+        layer_end = cfg.num_layers if layer_end is None else layer_end
+        assert T <= self.max_tokens and n_logits <= self.max_batch and 0 <= layer_begin <= layer_end <= cfg.num_layers
         h, xn, part, qkv, attn, act = self.h[:T], self.xn[:T], self.part[:T], self.qkv[:T], self.attn[:T], self.act[:T]
         q_view = qkv.view(T, self.nq + 2 * self.nkv, self.D)[:, : self.nq]
         attn_view = attn.view(T, self.nq, self.D)
 
-        ops.embedding(ids, w["embed"], vocab_start=tp.rank * self.vpr, out=h)
-        tp.all_reduce(h)
-        ops.rmsnorm(h, w["layers.0.input_norm"], cfg.rms_eps, out=xn)
-        for l in range(cfg.num_layers):
+        if layer_begin == 0:
+            ops.embedding(ids, w["embed"], vocab_start=tp.rank * self.vpr, out=h)
+            tp.all_reduce(h)
+            ops.rmsnorm(h, w["layers.0.input_norm"], cfg.rms_eps, out=xn)
+        for l in range(layer_begin, layer_end):
             p = f"layers.{l}."
             # qkv projection; RoPE and the KV-cache write happen in its epilogue
             ops.gemm_qkv_rope(xn, w[p + "qkv.weight"], qkv, positions, self.cos_sin, slot_mapping, self.k_cache[l], self.v_cache[l],
@@ -94,6 +100,8 @@ class LlamaTP:
             ops.gemm(part, w[p + "gate_up.weight"], out=act, epi=ops.EPI_SILU_MUL)
             nxt = w[f"layers.{l + 1}.input_norm"] if l + 1 < cfg.num_layers else w["norm"]
             tp.gemm_all_reduce_add_rmsnorm(act, w[p + "down.weight"], h, nxt, cfg.rms_eps, out=xn)                  # xn := norm(h) for the next layer
+        if layer_end < cfg.num_layers:
+            return None
         if logit_rows is None:
             xl = xn
         else:

@@ -53,6 +53,8 @@ def lib():
     l.tbv_op_argmax_merge.argtypes = [c_vp, c_vp, I, I, LL, c_vp, c_vp]
     l.tbv_op_decode_advance.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, c_vp, c_vp, I, c_vp]
     l.tbv_op_decode_advance.restype = I
+    l.tbv_op_copy_async.argtypes = [c_vp, c_vp, ctypes.c_size_t, c_vp]
+    l.tbv_op_copy_async.restype = I
     l.tbv_op_prefill_attention.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, I, I, I, F, c_vp]
     l.tbv_op_prefill_attention.restype = I
     l.tbv_op_attn_workspace.argtypes = [I, I, I, I]
@@ -268,6 +270,14 @@ def decode_advance(next_ids, ids, positions, ctx_lens, slot_mapping, block_table
                                      block_tables.shape[1], block_size, B, _p(history), _p(step_counter),
                                      history.shape[0] if history is not None else 0, _st()), "tbv_op_decode_advance")
     _count()
+
+
+def copy_async(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """dst <- src (same byte count, both contiguous; pinned host or device memory) as one asynchronous copy on the
+    current stream.  Unlike ``Tensor.copy_`` it involves no allocator bookkeeping, so it may be captured in a CUDA graph."""
+    nb = src.numel() * src.element_size()
+    assert nb == dst.numel() * dst.element_size() and dst.is_contiguous() and src.is_contiguous()
+    _chk(lib().tbv_op_copy_async(_p(dst), _p(src), nb, _st()), "tbv_op_copy_async")
 
 
 def attn_workspace(nq_rows: int, nq_heads: int, nkv: int, max_splits: int, device) -> torch.Tensor:
