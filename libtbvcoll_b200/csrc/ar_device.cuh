@@ -66,7 +66,8 @@ struct HostMirror {
 };
 
 enum : unsigned { kErrNone = 0, kErrTimeout = 1, kErrTag = 2, kErrBounds = 3 };
-enum : unsigned { kWherePhase0 = 1, kWherePhase1 = 2, kWhereFused = 3,
+enum : int { kWholeCall = 0, kPushHalf = 1, kReduceHalf = 2 };   // a one-shot call as one kernel, or split around stream wait-value operations
+enum : unsigned { kWherePhase0 = 1, kWherePhase1 = 2, kWhereFused = 3, kWhereStreamWait = 4,
                   kGuardSlotBytes = 16, kGuardLLBytes = 17, kGuardChannels = 18 };   // sites of the bounds-checked build
 
 // Everything a kernel needs to talk to the other ranks; passed by value.
@@ -373,9 +374,9 @@ __device__ __forceinline__ void sum_units_rank_order(const RankCtx& c, const uin
 // kOutAligned say whether the caller's tensors can be accessed 16 bytes at a time.
 template <typename T, bool VEC>
 __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* out, size_t nbytes,
-                                int nchan, int chan, int io, unsigned long long* sh_seq) {
+                                int nchan, int chan, int io, unsigned long long* sh_seq, int part = kWholeCall) {
   unsigned long long t_enter = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
-  CallInfo ci = call_begin(c, sh_seq);
+  CallInfo ci = call_begin(c, sh_seq);   // both halves of a split call read the same number: only call_end advances it
   const size_t unit_bytes = VEC ? 16 : sizeof(T);
   const size_t units = nbytes / unit_bytes;
   const size_t per = (units + nchan - 1) / nchan;
@@ -386,22 +387,30 @@ __device__ void ar_oneshot_body(const RankCtx& c, const T* __restrict__ in, T* o
   if (!(TBV_GUARD(c, nbytes, c.guard_cap, kGuardSlotBytes, chan) && TBV_GUARD(c, nchan, TBV_MAXCHAN, kGuardChannels, chan)))
     u1 = u0;   // bounds-checked build: nothing is moved after a violation
 
-  // push my range to every peer's [slot][src = me] region
-  for (size_t u = u0 + threadIdx.x; u < u1; u += blockDim.x) {
-    if (VEC) {
-      uint4 v = ld_unit(in, u, in_al);
-      for (int p = 0; p < c.world; p++)
-        if (p != c.rank) reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, c.rank))[u] = v;
-    } else {
-      T v = in[u];
-      for (int p = 0; p < c.world; p++)
-        if (p != c.rank) reinterpret_cast<T*>(slot_region(c, p, ci.slot, c.rank))[u] = v;
+  if (part != kReduceHalf) {
+    // push my range to every peer's [slot][src = me] region
+    for (size_t u = u0 + threadIdx.x; u < u1; u += blockDim.x) {
+      if (VEC) {
+        uint4 v = ld_unit(in, u, in_al);
+        for (int p = 0; p < c.world; p++)
+          if (p != c.rank) reinterpret_cast<uint4*>(slot_region(c, p, ci.slot, c.rank))[u] = v;
+      } else {
+        T v = in[u];
+        for (int p = 0; p < c.world; p++)
+          if (p != c.rank) reinterpret_cast<T*>(slot_region(c, p, ci.slot, c.rank))[u] = v;
+      }
     }
+    __syncthreads();
+    publish(c, ci, 0, chan);
+    if (chan == 0 && threadIdx.x == 0) { c.dm->bc[1] = ci.seq; c.dm->ring[ci.seq & (kTraceN - 1)].t_pushed = globaltimer(); }
+    if (part == kPushHalf) {        // the stream waits for the peers' flags (wait-value operations), then the reduce half runs
+      if (chan == 0 && threadIdx.x == 0) c.dm->ts[0] = t_enter;
+      return;
+    }
+    wait_all(c, ci, 0, chan, kWherePhase0);
+  } else if (chan == 0 && threadIdx.x == 0) {
+    t_enter = c.dm->ts[0];
   }
-  __syncthreads();
-  publish(c, ci, 0, chan);
-  if (chan == 0 && threadIdx.x == 0) { c.dm->bc[1] = ci.seq; c.dm->ring[ci.seq & (kTraceN - 1)].t_pushed = globaltimer(); }
-  wait_all(c, ci, 0, chan, kWherePhase0);
   unsigned long long t_ready = (threadIdx.x == 0 && chan == 0) ? globaltimer() : 0;
   if (chan == 0 && threadIdx.x == 0) c.dm->bc[2] = ci.seq;
 

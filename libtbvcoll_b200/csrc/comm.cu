@@ -69,6 +69,7 @@ Knobs Knobs::from_env() {
   k.nvls_direct_max = env_long("TBV_NVLS_DIRECT_MAX", 1l << 20);
   k.ce = int(env_long("TBV_CE", 0));
   k.ll_wide = int(env_long("TBV_LL_WIDE", 1)) != 0;
+  k.streamwait = int(env_long("TBV_STREAMWAIT", 0)) != 0;
   k.ll_spread = int(env_long("TBV_LL_SPREAD", 0));
   k.ll_threads = int(env_long("TBV_LL_THREADS", 0));
   const char* a = getenv("TBV_ALGO");
@@ -112,6 +113,7 @@ struct Drv {
   CUresult (*MulticastGetGranularity)(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity_flags);
   CUresult (*DeviceGetAttribute)(int*, CUdevice_attribute, CUdevice);
   CUresult (*GetErrorString)(CUresult, const char**);
+  CUresult (*StreamWaitValue32)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);   // optional (stream-wait debug mode)
 };
 Drv g_drv;
 std::once_flag g_drv_once;
@@ -148,6 +150,7 @@ const Drv& drv() {
     mc &= drv_sym("cuMulticastUnbind", &d.MulticastUnbind);
     mc &= drv_sym("cuMulticastGetGranularity", &d.MulticastGetGranularity);
     if (!mc) d.MulticastCreate = nullptr;
+    if (!drv_sym("cuStreamWaitValue32", &d.StreamWaitValue32)) d.StreamWaitValue32 = nullptr;
     d.ok = ok;
   });
   return g_drv;
@@ -184,6 +187,20 @@ __global__ void __launch_bounds__(512) k_ar_oneshot_local(const RankCtx* ctxs, c
   if (int(blockIdx.y) == p.mute) return;
   ar_oneshot_body<T, VEC>(ctxs[blockIdx.y], static_cast<const T*>(p.in[blockIdx.y]), static_cast<T*>(p.out[blockIdx.y]),
                           nbytes, gridDim.x, blockIdx.x, p.io, &sh_seq);
+}
+// One-shot all-reduce split around stream wait-value operations (TBV_STREAMWAIT=1): `part` = push half or reduce half.
+// Plain launches: nothing in them waits for another rank, so the emulated ranks need no co-residency either.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(512) k_ar_oneshot_half(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes, int io, int part) {
+  __shared__ unsigned long long sh_seq;
+  ar_oneshot_body<T, VEC>(c, in, out, nbytes, gridDim.x, blockIdx.x, io, &sh_seq, part);
+}
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(512) k_ar_oneshot_half_local(const RankCtx* ctxs, const __grid_constant__ LocalPtrs p, size_t nbytes, int part) {
+  __shared__ unsigned long long sh_seq;
+  if (int(blockIdx.y) == p.mute && part == kPushHalf) return;   // a rank that never publishes
+  ar_oneshot_body<T, VEC>(ctxs[blockIdx.y], static_cast<const T*>(p.in[blockIdx.y]), static_cast<T*>(p.out[blockIdx.y]),
+                          nbytes, gridDim.x, blockIdx.x, p.io, &sh_seq, part);
 }
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(512) k_ar_twoshot(const __grid_constant__ RankCtx c, const T* in, T* out, size_t nbytes, int mode, int io) {
@@ -769,6 +786,113 @@ static int take_mute(tbv_comm* c) {
 
 static size_t dtype_size(int dtype) { return dtype == TBV_F32 ? 4 : 2; }
 
+// ---- host-driven debug mode: the stream, not a kernel, waits for the peers (TBV_STREAMWAIT=1) ----------------
+// The reference's default wait was a stream memory operation (hipStreamWaitValue64 on the slot's flag,
+// step4/libtbvcoll.cpp:479-480); here the in-kernel bounded spin is the product path and this is the optional
+// counterpart for attribution and for looking at a stuck exchange from the host: push half (payload stores, fence,
+// flags), one cuStreamWaitValue32 per (source rank, channel) on this rank's own flag words, reduce half.  A stream
+// wait has no deadline of its own, so the HOST bounds it: the call polls the stream until TBV_WDOG expires, then
+// reads the flag words on a side stream, records which source never published (same error record as the device
+// watchdog), stores the awaited value into the missing words itself so that the stream drains, and fails the
+// communicator.  The call is therefore synchronous and reads the device's sequence number first: not for graphs.
+template <typename T>
+static cudaError_t launch_half_t(tbv_comm* c, bool vec, int nchan, int threads, const void* const* ins, void* const* outs, size_t nbytes,
+                                 int io, int part, int mute, cudaStream_t st) {
+  if (c->local) {
+    LocalPtrs p{};
+    for (int r = 0; r < c->world; r++) { p.in[r] = ins[r]; p.out[r] = outs[r]; }
+    p.io = io;
+    p.mute = mute;
+    if (vec) k_ar_oneshot_half_local<T, true><<<dim3(nchan, c->world), threads, 0, st>>>(c->ctxs_dev, p, nbytes, part);
+    else k_ar_oneshot_half_local<T, false><<<dim3(nchan, c->world), threads, 0, st>>>(c->ctxs_dev, p, nbytes, part);
+  } else {
+    const RankCtx& x = c->ranks[0].ctx;
+    if (vec) k_ar_oneshot_half<T, true><<<nchan, threads, 0, st>>>(x, static_cast<const T*>(ins[0]), static_cast<T*>(outs[0]), nbytes, io, part);
+    else k_ar_oneshot_half<T, false><<<nchan, threads, 0, st>>>(x, static_cast<const T*>(ins[0]), static_cast<T*>(outs[0]), nbytes, io, part);
+  }
+  return cudaGetLastError();
+}
+static cudaError_t launch_half(tbv_comm* c, int dtype, bool vec, int nchan, int threads, const void* const* ins, void* const* outs,
+                               size_t nbytes, int io, int part, int mute, cudaStream_t st) {
+  switch (dtype) {
+    case TBV_F32: return launch_half_t<float>(c, vec, nchan, threads, ins, outs, nbytes, io, part, mute, st);
+    case TBV_F16: return launch_half_t<__half>(c, vec, nchan, threads, ins, outs, nbytes, io, part, mute, st);
+    default: return launch_half_t<__nv_bfloat16>(c, vec, nchan, threads, ins, outs, nbytes, io, part, mute, st);
+  }
+}
+
+static int stream_wait_allreduce(tbv_comm* c, const void* const* ins, void* const* outs, size_t nbytes, int dtype, bool vec, int io,
+                                 cudaStream_t st) {
+  const Drv& d = drv();
+  if (!d.StreamWaitValue32) { c->stats.fallbacks++; return TBV_FALLBACK; }
+  const double t0 = now_us();
+  // the device's own sequence number (replayed graphs advance it without the host)
+  DevState ds;
+  if (cudaStreamSynchronize(st) != cudaSuccess || cudaMemcpy(&ds, c->ranks[0].st, sizeof(ds), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    c->sticky_err.store(1);
+    return TBV_FAIL;
+  }
+  const unsigned long long seq = ds.seq + 1;
+  const unsigned want = unsigned(seq);
+  const int slot = int(seq % (unsigned long long)c->knobs.nslot), W = c->world, nr = c->local ? W : 1;
+  const size_t units = nbytes / (vec ? 16 : dtype_size(dtype));
+  const int threads = units < 512 ? int(std::max<size_t>(32, (units + 31) / 32 * 32)) : 512;
+  const int nchan = int(std::max<size_t>(1, std::min<size_t>(4, units / 512)));
+  const int mute = take_mute(c);
+  auto flag_word = [&](int r, int src, int chan) {
+    return c->ranks[r].ctx.flags[c->ranks[r].ctx.rank] + ((size_t(slot) * 2 + 0) * W + src) * TBV_MAXCHAN + chan;   // flag_index(slot, phase 0, src, chan)
+  };
+  cudaError_t e = launch_half(c, dtype, vec, nchan, threads, ins, outs, nbytes, io, kPushHalf, mute, st);
+  for (int r = 0; r < nr && e == cudaSuccess; r++)
+    for (int src = 0; src < W; src++) {
+      if (src == c->ranks[r].ctx.rank) continue;
+      for (int ch = 0; ch < nchan; ch++)
+        if (d.StreamWaitValue32(st, CUdeviceptr(uintptr_t(flag_word(r, src, ch))), want, CU_STREAM_WAIT_VALUE_EQ) != CUDA_SUCCESS) e = cudaErrorUnknown;
+    }
+  if (e == cudaSuccess) e = launch_half(c, dtype, vec, nchan, threads, ins, outs, nbytes, io, kReduceHalf, -1, st);
+  if (e != cudaSuccess) {
+    c->errmsg = std::string("stream-wait mode: ") + cudaGetErrorString(e);
+    LOG("%s", c->errmsg.c_str());
+    c->sticky_err.store(1);
+    return TBV_FAIL;
+  }
+  c->host_seq++;
+  // the host's bound on the stream's wait
+  const double deadline = now_us() + c->knobs.wdog_s * 1e6;
+  cudaError_t q;
+  while ((q = cudaStreamQuery(st)) == cudaErrorNotReady && now_us() < deadline) usleep(20);
+  if (q == cudaErrorNotReady) {
+    if (!c->side_stream) cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking);
+    bool named = false;
+    for (int r = 0; r < nr; r++)
+      for (int src = 0; src < W; src++) {
+        if (src == c->ranks[r].ctx.rank) continue;
+        for (int ch = 0; ch < nchan; ch++) {
+          unsigned v = 0;
+          cudaMemcpyAsync(&v, flag_word(r, src, ch), sizeof(v), cudaMemcpyDeviceToHost, c->side_stream);
+          cudaStreamSynchronize(c->side_stream);
+          if (v == want) continue;
+          if (!named) {
+            named = true;
+            HostMirror* hm = c->ranks[r].hm;
+            hm->err_seq = seq; hm->where = kWhereStreamWait; hm->peer = unsigned(src); hm->chan = unsigned(ch);
+            hm->err = kErrTimeout;
+          }
+          cudaMemcpyAsync(flag_word(r, src, ch), &want, sizeof(want), cudaMemcpyHostToDevice, c->side_stream);   // let the stream drain
+          cudaStreamSynchronize(c->side_stream);
+        }
+      }
+    cudaStreamSynchronize(st);
+    c->sticky_err.store(1);
+    check_err(c);       // logs the record
+    return TBV_FAIL;
+  }
+  if (q != cudaSuccess) { c->sticky_err.store(1); return TBV_FAIL; }
+  if (check_err(c)) return TBV_FAIL;
+  c->stats.add_enq(now_us() - t0);
+  return TBV_OK;
+}
+
 // mode: 0 all-reduce (nbytes = tensor), 1 reduce-scatter (nbytes = output), 2 all-gather (nbytes = input)
 static int gpu_collective(tbv_comm* c, const void* const* ins, void* const* outs, size_t nbytes, int dtype, void* stream,
                           int mode) {
@@ -796,6 +920,7 @@ static int gpu_collective(tbv_comm* c, const void* const* ins, void* const* outs
     if (!aligned16(ins[r])) io &= ~kInAligned;
     if (!aligned16(outs[r])) io &= ~kOutAligned;
   }
+  if (c->knobs.streamwait && mode == 0) return stream_wait_allreduce(c, ins, outs, nbytes, dtype, vec, io, st);
   int algo = mode == 0 ? pick_algo(c, nbytes, vec) : TBV_ALGO_TWOSHOT;
   if (mode != 0 && !vec && (nbytes % dtype_size(dtype))) return TBV_FALLBACK;
   if (c->local && algo == TBV_ALGO_NVLS) algo = TBV_ALGO_TWOSHOT;
@@ -1035,6 +1160,7 @@ int tbv_comm_destroy(tbv_comm* c) {
       if (g.hm) cudaFreeHost(g.hm);
     }
     if (c->ctxs_dev) cudaFree(c->ctxs_dev);
+    if (c->side_stream) cudaStreamDestroy(c->side_stream);
     for (auto& kv : c->gather_maps) cudaFree(kv.second);   // tensor maps over this communicator's slot memory die with it
     c->gather_maps.clear();
   }

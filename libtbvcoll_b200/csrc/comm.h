@@ -36,6 +36,7 @@ struct Knobs {
   double init_timeout_s = 60.0;  // TBV_INIT_TIMEOUT
   long ll_max = -1;              // TBV_LL_MAX: largest message that uses flag-in-payload (LL) packets (-1: by world size)
   int ll_wide = 1;               // TBV_LL_WIDE: LL packets as one 32-byte store / load per unit (0 = two 16-byte ones)
+  int streamwait = 0;            // TBV_STREAMWAIT: 1 = host-driven debug mode, the stream waits for the peers' flags (wait-value operations)
   int ll_spread = 0;             // TBV_LL_SPREAD: CTAs (a cluster) that share one row in the LL all-reduce + norm (0 = from world size and row length)
   int ll_threads = 0;            // TBV_LL_THREADS: threads per CTA of the plain LL all-reduce (fewer threads = more SMs pushing; 0 = from world size)
   long nvls_min = 0x7fffffffffffffffl;  // TBV_NVLS_MIN: smallest message for the switch-reduced kernel in auto mode
@@ -84,6 +85,7 @@ struct tbv_comm {
   std::map<std::tuple<int, int, int, int>, void*> gather_maps;
   std::atomic<int> sticky_err{0};
   unsigned long long host_seq = 0, trace_read = 0;
+  cudaStream_t side_stream = nullptr;      // stream-wait debug mode: the host looks at (and releases) flag words beside a blocked stream
   std::vector<tbv::TraceRec> trace_host;   // staging for the timing ring
   void* last_stream = nullptr;
   std::vector<void*> streams_seen;

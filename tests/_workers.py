@@ -385,6 +385,44 @@ def gpu_peer_skips(rank, world, port):
     return res
 
 
+def gpu_stream_wait_mode(rank, world, port):
+    """TBV_STREAMWAIT=1 on real ranks: exact results, then rank 1 drops a call between steps and rank 0's HOST
+    watchdog ends the stream's wait-value operations (no kernel waits, nothing faults)."""
+    import time
+    import torch
+    os.environ["TBV_STREAMWAIT"] = "1"
+    os.environ["TBV_WDOG"] = "0.5"
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from libtbvcoll_b200.tbvcoll import Comm
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    c = Comm(rank, world, rank, "127.0.0.1", port, cap_bytes=1 << 20)
+    bad = []
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (8, 28672, 262144, 1001):
+            ins = [_gen_gpu(1234 + r, n, dtype, dev) for r in range(world)]
+            out = torch.empty_like(ins[rank])
+            assert c.all_reduce(ins[rank], out)
+            torch.cuda.synchronize()
+            if not torch.equal(out, oracle_sum(ins)):
+                bad.append((str(dtype), n))
+    res = {"bad": bad, "err_before": c.err()}
+    if rank == 1:
+        c.skip_next(1)
+    t0 = time.time()
+    failed = False
+    try:
+        c.all_reduce(torch.ones(1024, device=dev))
+    except RuntimeError:
+        failed = True
+    torch.cuda.synchronize()
+    res.update(elapsed=time.time() - t0, failed=failed, err=c.err(), last=c.last_error(),
+               alive=float((torch.ones(8, device=dev) * 2).sum().item()))
+    time.sleep(1.0)
+    c.destroy()
+    return res
+
+
 def gpu_fused_gemm_ar(rank, world, port):
     """fused row-parallel GEMM + all-reduce + residual + RMSNorm on real ranks"""
     import hashlib

@@ -285,6 +285,54 @@ def test_device_watchdog_when_one_emulated_rank_never_calls(kind):
         c.destroy()
 
 
+def test_stream_wait_value_mode_and_its_host_watchdog(monkeypatch):
+    """TBV_STREAMWAIT=1, the host-driven debug mode: push half, one stream wait-value operation per (source, channel)
+    on the receiver's own flag words, reduce half.  Same bits as the fixed-order oracle, also in place and after graph
+    replays have advanced the device's sequence number.  Then one emulated rank never publishes: the stream blocks,
+    the HOST's bound runs out, the missing source is named, the host stores the awaited value so that the stream
+    drains, the communicator is failed and the context stays usable.  Nothing faults or spins without a limit."""
+    import time
+    from libtbvcoll_b200.tbvcoll import Comm
+    monkeypatch.setenv("TBV_STREAMWAIT", "1")
+    world, silent = 4, 1
+    c = Comm.local(world, 0, cap_bytes=1 << 20)
+    try:
+        for dtype in (torch.float32, torch.float16, torch.bfloat16):
+            es = torch.tensor([], dtype=dtype).element_size()
+            for nbytes in (16, 57344, 1 << 20, 4096 + 16 * 7, 2 * 33):
+                ins = [gen(500 + r, nbytes // es, dtype) for r in range(world)]
+                outs = [torch.empty_like(t) for t in ins]
+                assert c.all_reduce_local(ins, outs)
+                torch.cuda.synchronize()
+                want = oracle(ins)
+                assert all(torch.equal(o, want) for o in outs), (dtype, nbytes)
+        ins = [gen(600 + r, 4096, torch.bfloat16) for r in range(world)]
+        want = oracle(ins)
+        assert c.all_reduce_local(ins, ins)                  # in place
+        torch.cuda.synchronize()
+        assert all(torch.equal(t, want) for t in ins) and not c.err()
+        rows = c.trace(0)
+        assert rows and all(0 < r[1] <= r[2] <= r[3] <= r[4] for r in rows)
+        c.set_wdog(0.2)
+        c.mute_rank(silent, 1)
+        xs = [gen(700 + r, 8192, torch.bfloat16) for r in range(world)]
+        outs = [torch.empty_like(t) for t in xs]
+        t0 = time.perf_counter()
+        with pytest.raises(RuntimeError):
+            c.all_reduce_local(xs, outs)
+        elapsed = time.perf_counter() - t0
+        assert 0.15 < elapsed < 5.0, elapsed
+        torch.cuda.synchronize()                             # the stream has drained
+        assert c.err()
+        last = c.last_error()
+        assert last["code"] == 1 and last["peer"] == silent and last["where"] == 4, last
+        with pytest.raises(RuntimeError):
+            c.all_reduce_local(xs, outs)
+        assert float((torch.ones(4, device=DEV) * 4).sum()) == 16.0
+    finally:
+        c.destroy()
+
+
 @pytest.mark.parametrize("world", [2, 8])
 def test_sequence_stamp_diagnostic(world, monkeypatch):
     """TBV_TAG=1: every flag is preceded by a sequence stamp in a word of its own; the receiver compares

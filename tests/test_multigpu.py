@@ -3,7 +3,7 @@ Run with 2 or more GPUs visible, e.g. ``pytest tests/test_multigpu.py -m gpu``."
 import pytest
 import torch
 
-from _workers import run_ranks, gpu_collectives, gpu_engine_tp, gpu_peer_skips, gpu_fused_gemm_ar, gpu_sp_kernels
+from _workers import run_ranks, gpu_collectives, gpu_engine_tp, gpu_peer_skips, gpu_fused_gemm_ar, gpu_sp_kernels, gpu_stream_wait_mode
 from conftest import free_port
 
 pytestmark = pytest.mark.gpu
@@ -50,6 +50,15 @@ def test_peer_drops_a_call_device_watchdog():
     assert r0["first"] == 2.0 and r0["err"] and r0["refused"] and r0["alive"] == 16.0
     assert 0.4 < r0["elapsed"] < 10
     assert r0["last"]["code"] == 1 and r0["last"]["peer"] == 1
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs >= 2 GPUs")
+def test_stream_wait_value_mode_real_ranks():
+    res = run_ranks(gpu_stream_wait_mode, 2, free_port(), timeout=120)
+    assert all(r["bad"] == [] and not r["err_before"] for r in res)
+    r0 = res[0]
+    assert r0["failed"] and r0["err"] and r0["alive"] == 16.0 and 0.4 < r0["elapsed"] < 10
+    assert r0["last"]["code"] == 1 and r0["last"]["peer"] == 1 and r0["last"]["where"] == 4
 
 
 @pytest.mark.skipif(NGPU < 2, reason="needs >= 2 GPUs")
