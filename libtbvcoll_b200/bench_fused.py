@@ -5,7 +5,7 @@ add + RMSNorm (eps 1e-5, gamma = 1), at TP = the number of ranks launched.
 Each form is timed on cold weights (distinct weight buffers cycled inside one CUDA graph,
 device time by CUDA events, max over ranks):
   fused    the library's fused form for the size: up to the LL packet limit ONE kernel (tcgen05 GEMM whose
-           epilogue stores LL packets into every rank's memory while finisher CTAs reduce + norm); above it,
+           epilogue stores LL packets into every rank's memory; the last CTAs to finish reduce + norm); above it,
            where the rows divide evenly, the sequence-parallel pair GEMM -> reduce-scatter (tile epilogues
            scatter over NVLink) + residual + norm on T/tp rows, then an all-gather of the normalised rows
   two      this library's GEMM, then its fused all-reduce + residual + RMSNorm kernel (or, above that kernel's
@@ -118,7 +118,7 @@ def main():
         t_f = time_graph([(lambda w=w: fused(w)) for w in ws], world) if form else float("nan")
         if args.stamps and form and form.startswith("one") and rank == 0:
             ts = comm.timestamps(0)            # of the last call of the graph just replayed
-            names = ("finisher resident", "dependency wait passed", "own GEMM CTAs pushed", "first row pulled", "rows normalised",
+            names = ("first tile resident", "first tile resident", "first finisher starts", "first row pulled", "rows normalised",
                      "last GEMM tile resident", "its accumulator done", "its packets issued")
             print(f"# T={T} stamps (us after the first): " + "; ".join(f"{n} {(v - ts[0]) / 1e3:+.1f}" for n, v in zip(names, ts)), flush=True)
         t_2 = time_graph([(lambda w=w: two(w)) for w in ws], world)

@@ -1373,9 +1373,9 @@ int tbv_comm_trace(tbv_comm* c, int r, unsigned long long* out, int max_rows) {
   return n;
 }
 // %globaltimer stamps (ns) of the last fused GEMM + all-reduce + norm call on (emulated) rank r:
-// [0] first finisher resident, [1] its dependency wait passed, [2] this rank's GEMM CTAs have all pushed,
-// [3] first row's packets of all ranks pulled, [4] rows normalised, [5] last GEMM tile's CTA resident,
-// [6] its accumulator complete, [7] its packets issued.  Synchronous copy.
+// [0] = [1] the first tile's CTA is resident, [2] the first finisher starts (all but the last few of this rank's CTAs have
+// pushed their tile), [3] its first row's packets of all ranks are pulled, [4] its rows are normalised, [5] the last tile's
+// CTA (in launch order) is resident, [6] its accumulator is complete, [7] its packets are issued.  Synchronous copy.
 int tbv_comm_timestamps(tbv_comm* c, int r, unsigned long long out[8]) {
   if (!c || c->cpu || r < 0 || r >= int(c->ranks.size())) return TBV_FAIL;
   return cudaMemcpy(out, c->ranks[r].dm->ts, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? TBV_OK : TBV_FAIL;

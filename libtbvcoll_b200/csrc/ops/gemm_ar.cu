@@ -2,19 +2,21 @@
 // RMSNorm that follows it, in ONE kernel over peer memory:
 //
 //   partial = X[T, K/tp] @ W[H, K/tp]^T            tcgen05 tiles, TMA-fed, TMEM accumulators
-//   GEMM CTAs: every finished tile slice is rounded to bf16 and stored straight into the LL
-//   packet area of EVERY rank (8-byte stores through the NVLink peer mappings, each carrying
-//   4 bytes of payload and the call's sequence number — the epilogue IS the transfer, there is
-//   no fence and no flag), after which the CTA gives its SM back;
-//   finisher CTAs (one per token row, resident from the start of the kernel, first in launch
-//   order): poll the row's packets of all ranks as they land, add the N copies in rank order in
+//   Every CTA is a GEMM CTA: a finished tile slice is rounded to bf16 and stored straight into the LL
+//   packet area of EVERY rank (8-byte pieces through the NVLink peer mappings, each carrying 4 bytes
+//   of payload and the call's sequence number — the epilogue IS the transfer, there is no fence and
+//   no flag).  The CTA then takes a ticket from a per-rank counter.  All but the last few give their
+//   SM back; the LAST min(T, 16) CTAs of a rank to finish stay as finishers, one or more token rows
+//   each: they poll the row's packets of all ranks as they land, add the N copies in rank order in
 //   fp32, round, add the residual, and apply RMSNorm.
 //
-// Nothing waits for a kernel boundary between the GEMM and the reduction, and the GEMM CTAs do
-// not stay for it: the next GEMM's CTAs take over their SMs and stream weights while the
-// finishers run.  This is what the reference's hook wraps as two separate steps
-// (RowParallelLinear, then GroupCoordinator.all_reduce: step3b/vllm_tp_bench.py:87-124) plus the
-// norm it lists as future work ("fuse k_acc + next RMSNorm", reports/12_references.md:136).
+// Nothing waits for a kernel boundary between the GEMM and the reduction, nobody sits idle while the
+// weights stream (an earlier form kept dedicated finisher CTAs resident from the start: they held
+// GEMM-sized shared-memory slots and delayed the last tiles), and the push is spread over every SM
+// that ran a tile — an SM hands only one 32-byte sector per clock to the fabric.  This is what the
+// reference's hook wraps as two separate steps (RowParallelLinear, then GroupCoordinator.all_reduce:
+// step3b/vllm_tp_bench.py:87-124) plus the norm it lists as future work ("fuse k_acc + next RMSNorm",
+// reports/12_references.md:136).
 //
 // Semantics are those of the unfused pipeline, bit for bit: the all-reduce operands are the bf16
 // partial sums, the sum is fp32 in rank order with one rounding, and the row normalisation forms
@@ -28,6 +30,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdio.h>
+
+#include <algorithm>
 
 #include "../comm.h"
 #include "gemm.cuh"
@@ -53,87 +57,29 @@ constexpr int kFusedThreads = 256;   // warps 0..5 have the GEMM roles; all 8 wa
 constexpr int kMaxFinishers = 16;    // finisher CTAs per rank (rows are dealt round robin beyond that)
 constexpr int kFusedVPT = 4;         // 16-byte units per finisher thread: hidden <= 8 * 4 * 256 = 8192
 
-// grid (fx + m_tiles, ranks, S), cluster (1, 1, S).  blockIdx.x < fx: finisher clusters.
+// grid (m_tiles, ranks, S), cluster (1, 1, S)
 __global__ void __launch_bounds__(kFusedThreads, 2)
 k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const RankCtx* ctxs, const __grid_constant__ FusedPtrs fp,
-                  const __nv_bfloat16* gamma, float eps, int fx, int finishers, int norm_threads, int mute) {
+                  const __nv_bfloat16* gamma, float eps, int finishers, int norm_threads, int mute) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ gemm::Smem s;
   __shared__ unsigned long long sh_seq;
-  __shared__ float sh_red[32];
+  __shared__ float sh_red[64];
+  __shared__ int sh_fid;
   const int er = blockIdx.y;  // (emulated) rank index into the per-rank arrays; 0 for a real rank
   if (er == mute) return;     // emulated world, host-made fault: this rank never makes the call
   const RankCtx& c = ctxs[er];
   const int S = p.splits;
   const int split = S > 1 ? int(cluster_ctarank()) : 0;
   const int T = p.N, H = p.M;
-  const unsigned n_cta = unsigned(finishers) + unsigned(gridDim.x - fx) * unsigned(S);
-
-  if (int(blockIdx.x) < fx) {
-    // ---------------- finisher: reduce + residual + RMSNorm of its token rows ----------------
-    const int fid = blockIdx.x * S + split;
-    if (fid >= finishers) return;   // padding CTA of the last finisher cluster
-    pdl::launch_dependents();
-    if (threadIdx.x == 0 && fid == 0) c.dm->ts[0] = tbv::globaltimer();   // finisher resident
-    pdl::grid_dependency_wait();    // the previous collective has completed: the device sequence number is stable
-    const unsigned long long t_enter = (threadIdx.x == 0 && fid == 0) ? tbv::globaltimer() : 0;
-    CallInfo ci = call_begin(c, &sh_seq);
-    if (fid == 0 && threadIdx.x == 0) c.dm->bc[0] = ci.seq;
-    // While this rank's own GEMM CTAs are still streaming weights, one thread watches a single counter with
-    // a back-off instead of 512 threads hammering the packet lines (which the weight stream shares the L2
-    // with).  All ranks run the same step, so the peers' packets are at most a flight time behind.
-    if (threadIdx.x == 0) {
-      const unsigned n_gemm = unsigned(gridDim.x - fx) * unsigned(S);
-      unsigned long long t0 = 0;
-      for (unsigned spins = 0; *(volatile unsigned*)&c.st->gemm_done < n_gemm; spins++) {
-        __nanosleep(200);
-        if ((spins & 63u) == 63u) {
-          const unsigned long long now = tbv::globaltimer();
-          if (t0 == 0) t0 = now;
-          else if (now - t0 > c.wdog_ns || *(volatile unsigned*)&c.st->err != 0u) break;   // the packet wait below reports it
-        }
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0 && fid == 0) { c.dm->ts[1] = t_enter; c.dm->ts[2] = tbv::globaltimer(); }   // dependency passed; own GEMM CTAs have pushed
-    const int upr = H / 8;
-    const unsigned all = (1u << c.world) - 1u;   // own rank included: its GEMM CTAs write packets here too
-    unsigned long long t_ready = 0;
-    for (int row = fid; row < T; row += finishers) {
-      float h[kFusedVPT][8];
-#pragma unroll
-      for (int j = 0; j < kFusedVPT; j++) {
-        const int u = threadIdx.x + j * blockDim.x;
-        if (u < upr) {
-          const size_t off = size_t(row) * upr + u;
-          uint4 got[TBV_MAXRANK];
-          ll_pull_all(c, ci.slot, off, ci.want, all, fid, ci.seq, got);
-          float acc[8];
-          ll_sum_unit<__nv_bfloat16>(c, got, all, got[0], acc);
-          float res[8];
-          Pack<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(fp.residual[er])[off], res);
-#pragma unroll
-          for (int i = 0; i < 8; i++) {
-            const float sum = __bfloat162float(__float2bfloat16_rn(acc[i]));
-            h[j][i] = __bfloat162float(__float2bfloat16_rn(sum + res[i]));
-          }
-          reinterpret_cast<uint4*>(fp.residual_out[er])[off] = Pack<__nv_bfloat16>::pack(h[j]);
-        }
-      }
-      if (row == fid && threadIdx.x == 0 && fid == 0) { t_ready = tbv::globaltimer(); c.dm->bc[2] = ci.seq; c.dm->ts[3] = t_ready; }   // first row's packets pulled
-      rmsnorm_row_store_virtual<kFusedVPT>(h, upr, H, eps, reinterpret_cast<const uint4*>(gamma),
-                                           reinterpret_cast<uint4*>(fp.y[er]) + size_t(row) * upr, sh_red, norm_threads);
-    }
-    if (threadIdx.x == 0 && fid == 0) c.dm->ts[4] = tbv::globaltimer();   // rows normalised
-    call_end(c, ci, n_cta, t_enter, t_ready, size_t(T) * H * 2, TBV_ALGO_LL);
-    return;
-  }
+  const unsigned n_cta = unsigned(gridDim.x) * unsigned(S);
 
   // ---------------- GEMM CTA: one 128-feature tile over its K range, pushed as LL packets ----------------
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tile = blockIdx.x - fx, m0 = m_tile * gemm::kBM;
+  const int m_tile = blockIdx.x, m0 = m_tile * gemm::kBM;
   const bool stamp = blockIdx.x == gridDim.x - 1 && cluster_ctarank() == 0;   // the last tile in launch order
   if (stamp && threadIdx.x == 0) c.dm->ts[5] = tbv::globaltimer();           // its CTA is resident
+  if (m_tile == 0 && split == 0 && threadIdx.x == 0) c.dm->ts[0] = tbv::globaltimer();   // the first tile's CTA is resident
   const int kb_per = (p.kb_total + S - 1) / S;
   const int kb0 = split * kb_per;
   int nkb = p.kb_total - kb0;
@@ -208,12 +154,50 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
   __syncwarp();
   if (S > 1) cluster_sync_all(); else __syncthreads();  // peers' shared memory is no longer needed; this CTA's packets are issued
   if (threadIdx.x == 0) {
-    atomicAdd(&c.st->gemm_done, 1u);
+    // ticket: the last `finishers` CTAs of this rank to get here reduce and normalise the rows
+    const unsigned old = atomicAdd(&c.st->gemm_done, 1u);
+    sh_fid = old + unsigned(finishers) >= n_cta ? int(old + unsigned(finishers) - n_cta) : -1;
     if (stamp) c.dm->ts[7] = tbv::globaltimer();     // its packets are issued
-  }  // tells this rank's finishers when to start looking at packets (a hint, not an ordering)
-  gemm::teardown(p, s);
-  if (m_tile == 0 && split == 0 && threadIdx.x == 0) c.dm->bc[1] = ci.seq;
-  call_end(c, ci, n_cta, 0, 0, size_t(T) * H * 2, TBV_ALGO_LL);
+    if (m_tile == 0 && split == 0) c.dm->bc[1] = ci.seq;
+  }
+  gemm::teardown(p, s);      // tensor memory goes back before any waiting starts
+  __syncthreads();
+  const int fid = sh_fid;
+  unsigned long long t_enter = 0, t_ready = 0;
+  if (fid >= 0) {
+    // ---------------- finisher: reduce + residual + RMSNorm of its token rows ----------------
+    const bool lead = fid == 0 && threadIdx.x == 0;
+    if (lead) { t_enter = c.dm->ts[0]; c.dm->bc[0] = ci.seq; c.dm->ts[1] = c.dm->ts[0]; c.dm->ts[2] = tbv::globaltimer(); }   // nearly all of this rank's tiles are pushed
+    const int upr = H / 8;
+    const unsigned all = (1u << c.world) - 1u;   // own rank included: its CTAs write packets here too
+    for (int row = fid; row < T; row += finishers) {
+      float h[kFusedVPT][8];
+#pragma unroll
+      for (int j = 0; j < kFusedVPT; j++) {
+        const int u = threadIdx.x + j * blockDim.x;
+        if (u < upr) {
+          const size_t off = size_t(row) * upr + u;
+          uint4 got[TBV_MAXRANK];
+          ll_pull_all(c, ci.slot, off, ci.want, all, fid, ci.seq, got);
+          float acc[8];
+          ll_sum_unit<__nv_bfloat16>(c, got, all, got[0], acc);
+          float res[8];
+          Pack<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(fp.residual[er])[off], res);
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const float sum = __bfloat162float(__float2bfloat16_rn(acc[i]));
+            h[j][i] = __bfloat162float(__float2bfloat16_rn(sum + res[i]));
+          }
+          reinterpret_cast<uint4*>(fp.residual_out[er])[off] = Pack<__nv_bfloat16>::pack(h[j]);
+        }
+      }
+      if (row == fid && lead) { t_ready = tbv::globaltimer(); c.dm->bc[2] = ci.seq; c.dm->ts[3] = t_ready; }   // first row's packets pulled
+      rmsnorm_row_store_virtual<kFusedVPT>(h, upr, H, eps, reinterpret_cast<const uint4*>(gamma),
+                                           reinterpret_cast<uint4*>(fp.y[er]) + size_t(row) * upr, sh_red, norm_threads);
+    }
+    if (lead) c.dm->ts[4] = tbv::globaltimer();   // rows normalised
+  }
+  call_end(c, ci, n_cta, t_enter, t_ready, size_t(T) * H * 2, TBV_ALGO_LL);
 }
 
 bool g_attr_done = false;
@@ -242,16 +226,15 @@ static int launch_fused(tbv_comm* c, const void* const* ws, const void* const* x
   int bn, splits, stages;
   tbvops::gemm_config(hidden, tokens, k_local, 0, &bn, &splits, &stages);
   if ((tokens + bn - 1) / bn != 1) return TBV_FALLBACK;
-  const int finishers = tokens < kMaxFinishers ? tokens : kMaxFinishers;
+  const int n_gemm = (hidden / 128) * splits;
+  const int finishers = std::min(std::min(tokens, kMaxFinishers), n_gemm);
   if (c->local) {
-    // Emulated ranks share one GPU and their CTAs wait on one another: keep every finisher and at least
-    // one more cluster resident at any time.
-    if (nr * ((finishers + splits - 1) / splits) * splits + splits > tbvops::sm_count()) return TBV_FALLBACK;
+    // Emulated ranks share one GPU and their finishers wait for the other ranks' tiles: every rank's finishers
+    // and at least one more cluster must fit on the GPU at the same time.
+    if (nr * finishers + splits > tbvops::sm_count()) return TBV_FALLBACK;
   }
-  const int fx = (finishers + splits - 1) / splits;
-  // Always the two-CTAs-per-SM shared-memory budget: the finisher CTAs inherit the launch configuration
-  // (cluster shape, dynamic shared memory) of the GEMM CTAs, and the next kernel's CTAs must find room beside
-  // this kernel's finishers, or they cannot stream their weights while the finishers wait for the peers.
+  // The two-CTAs-per-SM shared-memory budget: the next kernel's CTAs must find room beside this kernel's
+  // finishers, or they cannot stream their weights while the finishers wait for the peers.
   {
     const int stage_bytes = gemm::kATileBytes + bn * 128;
     const int fit = (108 * 1024) / stage_bytes;
@@ -280,9 +263,9 @@ static int launch_fused(tbv_comm* c, const void* const* ws, const void* const* x
   const RankCtx* ctxs = c->ctxs_dev;
   int mute = -1;
   if (c->local && c->mute_left.load() > 0) { c->mute_left.fetch_sub(1); mute = c->mute_rank; }
-  cudaError_t e = pdl::launch(k_gemm_ar_rmsnorm, dim3(fx + hidden / 128, nr, splits), dim3(kFusedThreads), smem,
+  cudaError_t e = pdl::launch(k_gemm_ar_rmsnorm, dim3(hidden / 128, nr, splits), dim3(kFusedThreads), smem,
                               static_cast<cudaStream_t>(stream), splits, maps, p, ctxs, fp, static_cast<const __nv_bfloat16*>(gamma), eps,
-                              fx, finishers, tbvops::norm_threads(hidden), mute);
+                              finishers, tbvops::norm_threads(hidden), mute);
   if (e != cudaSuccess) {
     fprintf(stderr, "[tbvcoll] fused gemm+all-reduce launch failed: %s\n", cudaGetErrorString(e));
     c->sticky_err.store(1);

@@ -220,10 +220,11 @@ def test_fused_gemm_allreduce_residual_rmsnorm_emulated(world, T, H, K):
         c.destroy()
 
 
-def test_fused_gemm_allreduce_declines_large_messages_on_shape_alone():
+def test_fused_gemm_allreduce_declines_large_messages_on_shape_alone(monkeypatch):
     """Above the LL packet limit the call is declined (the caller composes GEMM + collective); the answer
     depends on the shape and the knobs only, so all ranks agree on it."""
     from libtbvcoll_b200.tbvcoll import Comm
+    monkeypatch.setenv("TBV_LL_MAX", str(256 << 10))
     T, H, K, world = 128, 4096, 256, 2
     c = Comm.local(world, 0, cap_bytes=T * H * 2)
     try:
