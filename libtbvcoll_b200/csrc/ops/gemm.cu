@@ -125,12 +125,7 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
       const uint32_t stage_addr = smem_u32(sm);
       for (int idx = te; idx < rows * q4; idx += 128) {
         const int t = idx / q4, f = split * fs + (idx % q4) * 4;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < S; r++) {
-          float4 v = ld_dsmem_f32x4(mapa_shared(stage_addr + uint32_t((t * 128 + f) * 4), uint32_t(r)));
-          if (r == 0) acc = v;
-          else { acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
-        }
+        float4 acc = dsmem_sum_f32x4(stage_addr + uint32_t((t * 128 + f) * 4), S);
         const int m = m0 + f;
         if (p.bias) {
           if (m + 0 < p.M) acc.x += __bfloat162float(p.bias[m + 0]);

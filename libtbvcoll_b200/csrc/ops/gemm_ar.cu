@@ -132,11 +132,7 @@ k_gemm_ar_rmsnorm(const __grid_constant__ Maps maps, const gemm::Params p, const
       const int t = idx / q4, f = split * fs + (idx % q4) * 4;
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       if (S > 1) {
-        for (int r = 0; r < S; r++) {
-          float4 v = ld_dsmem_f32x4(mapa_shared(stage_addr + uint32_t((t * 128 + f) * 4), uint32_t(r)));
-          if (r == 0) acc = v;
-          else { acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
-        }
+        acc = dsmem_sum_f32x4(stage_addr + uint32_t((t * 128 + f) * 4), S);
       } else {
         acc = *reinterpret_cast<const float4*>(stage_f + t * 128 + f);
       }

@@ -141,13 +141,9 @@ k_gemm_qkv_rope(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const uint32_t stage_addr = smem_u32(sm);
       for (int idx = te; idx < rows * q4; idx += 128) {
         const int t = idx / q4, d = split * half + (idx % q4) * 4;
-        float lo[4], hi[4];
-        for (int r = 0; r < S; r++) {
-          const float4 a = ld_dsmem_f32x4(mapa_shared(stage_addr + uint32_t((t * 128 + d) * 4), uint32_t(r)));
-          const float4 b = ld_dsmem_f32x4(mapa_shared(stage_addr + uint32_t((t * 128 + d + 64) * 4), uint32_t(r)));
-          if (r == 0) { lo[0] = a.x; lo[1] = a.y; lo[2] = a.z; lo[3] = a.w; hi[0] = b.x; hi[1] = b.y; hi[2] = b.z; hi[3] = b.w; }
-          else { lo[0] += a.x; lo[1] += a.y; lo[2] += a.z; lo[3] += a.w; hi[0] += b.x; hi[1] += b.y; hi[2] += b.z; hi[3] += b.w; }
-        }
+        const float4 a = dsmem_sum_f32x4(stage_addr + uint32_t((t * 128 + d) * 4), S);
+        const float4 b = dsmem_sum_f32x4(stage_addr + uint32_t((t * 128 + d + 64) * 4), S);
+        float lo[4] = {a.x, a.y, a.z, a.w}, hi[4] = {b.x, b.y, b.z, b.w};
         const bool pre = pf_ok && idx == pf_idx;   // this thread's first piece: its position, cos / sin and slot are in registers
         int pos = pf_pos;
         float cs[4] = {pf_cos.x, pf_cos.y, pf_cos.z, pf_cos.w}, sn[4] = {pf_sin.x, pf_sin.y, pf_sin.z, pf_sin.w};

@@ -174,5 +174,18 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
   asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
   return v;
 }
+// The float4 at shared-memory address `local_addr` of CTAs 0 .. S-1 of the cluster, added in CTA order (S <= 8).
+// Every load is issued before the first value is used: one distributed-shared-memory round trip, not S.
+__device__ __forceinline__ float4 dsmem_sum_f32x4(uint32_t local_addr, int S) {
+  float4 v[8];
+#pragma unroll
+  for (int r = 0; r < 8; r++)
+    if (r < S) v[r] = ld_dsmem_f32x4(mapa_shared(local_addr, uint32_t(r)));
+  float4 acc = v[0];
+#pragma unroll
+  for (int r = 1; r < 8; r++)
+    if (r < S) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
+  return acc;
+}
 
 }  // namespace sm100
