@@ -31,10 +31,10 @@ class TPGroup:
         self.fallback_group = fallback_group
         self.fused_norm_max_bytes = fused_norm_max_bytes
         self.local_stand_in = local_stand_in
-        # One-kernel GEMM + all-reduce + norm (LL packets from the GEMM epilogue, finisher CTAs reduce and
-        # normalise; same bits as the two-kernel form).  Off by default: measured slower than GEMM followed
-        # by the fused all-reduce + norm kernel (the finisher CTAs inherit the GEMM's cluster shape and shared
-        # memory, which keeps the next kernel's CTAs from becoming resident early).  TBV_FUSE_GEMM_AR=1 selects it.
+        # One-kernel GEMM + all-reduce + norm (LL packets from the GEMM epilogue, the last CTAs to finish reduce
+        # and normalise; same bits as the two-kernel form).  Off by default: measured 3 us per call slower than
+        # GEMM followed by the fused all-reduce + norm kernel (its finishers hold GEMM-sized slots while they wait
+        # for the peers, which delays the next kernel's weight prefetch).  TBV_FUSE_GEMM_AR=1 selects it.
         self.fuse_gemm = os.environ.get("TBV_FUSE_GEMM_AR", "0") == "1"
         self.calls = 0
         self.fallbacks = 0
