@@ -33,8 +33,8 @@ class TPGroup:
         self.local_stand_in = local_stand_in
         # One-kernel GEMM + all-reduce + norm (LL packets from the GEMM epilogue, the last CTAs to finish reduce
         # and normalise; same bits as the two-kernel form).  Off by default: measured 3 us per call slower than
-        # GEMM followed by the fused all-reduce + norm kernel (its finishers hold GEMM-sized slots while they wait
-        # for the peers, which delays the next kernel's weight prefetch).  TBV_FUSE_GEMM_AR=1 selects it.
+        # GEMM followed by the fused all-reduce + norm kernel (the next kernel's CTAs get their slots later and have
+        # half the time to prefetch weights before the call completes).  TBV_FUSE_GEMM_AR=1 selects it.
         self.fuse_gemm = os.environ.get("TBV_FUSE_GEMM_AR", "0") == "1"
         self.calls = 0
         self.fallbacks = 0
