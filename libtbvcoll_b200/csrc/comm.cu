@@ -374,8 +374,10 @@ static void compute_sizes(tbv_comm* c) {
   // shrinks with the world.  The receiver fetches the packets of all sources with one batch of loads,
   // so the cost of a call no longer grows with one memory round trip per peer.
   // Measured with 32-byte packets: 2 ranks, LL 6.1 / 8.1 / 13.4 us at 512 KB / 1 MB / 2 MB against 10.8 / 13.1 / 18.9 for the
-  // flag form; with more ranks every rank sends (world - 1) x 2 x the bytes, so the limit comes down.
-  if (c->knobs.ll_max < 0) c->knobs.ll_max = c->world <= 2 ? (2048 << 10) : (c->world <= 4 ? (512 << 10) : (256 << 10));
+  // flag form; 8 ranks, 7.6 / 8.5 us at 64 / 128 KB against 12.3 / 13.0.  With more ranks every rank sends (world - 1) x 2 x the
+  // bytes, so the limit comes down; 256 KB at 4 and 8 ranks continues the measured slope (+0.9 us per doubling at 8 ranks,
+  // one-shot 14.9 us at 256 KB) and has not been timed itself.
+  if (c->knobs.ll_max < 0) c->knobs.ll_max = c->world <= 2 ? (2048 << 10) : (256 << 10);
   c->knobs.ll_max = std::min<long>(c->knobs.ll_max, long(c->cap));   // no packet area beyond what a call may carry
   const size_t nflag = size_t(c->knobs.nslot + 1) * 2 * c->world * TBV_MAXCHAN;   // + the fixed slot of the copy-engine path
   c->tag_off = (nflag * sizeof(unsigned) + 255) & ~size_t(255);

@@ -36,6 +36,8 @@ struct Params {
   __nv_bfloat16* y;
   unsigned long long limit_ns;  // bound on every barrier wait
   int* err;                     // device flag: set to 1 if a wait gave up
+  const char* pf_ptr;           // weights of the GEMM that runs next (or null): see the producer's last step
+  unsigned long long pf_bytes;  // how much of them to ask into L2 (a multiple of 16), shared out over the CTAs
 };
 
 struct Smem {  // static shared state of one CTA
@@ -116,6 +118,22 @@ __device__ __forceinline__ uint8_t* mainloop(const CUtensorMap* tmA, const CUten
       tma_load_2d_hint(a_base + st * kATileBytes, tmA, (kb0 + i) * kBK, m0, fb, pol_w);
       tma_load_2d_hint(b_base + st * b_tile_bytes, tmB, (kb0 + i) * kBK, n0, fb, pol_x);
       issued = i + 1;
+    }
+    // This CTA's own weight tiles are all requested.  Between here and the moment the NEXT GEMM may start (this
+    // kernel's epilogue, the kernel boundary, an attention or all-reduce kernel in between) HBM would idle: the next
+    // kernel's CTAs get an SM slot only when this kernel's leave, and then fetch no more than their ring holds before
+    // their dependency wait.  So each CTA asks for its share of the next GEMM's weights to be brought into L2
+    // (126 MB); the requests queue behind this kernel's own loads, and the next kernel's TMA loads find them there.
+    if (p.pf_bytes && !*abortp) {
+      const unsigned long long ncta = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+      const unsigned long long id = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+      const unsigned long long per = ((p.pf_bytes + ncta - 1) / ncta + 4095ull) & ~4095ull;
+      const unsigned long long off = id * per;
+      if (off < p.pf_bytes) {
+        const unsigned long long n = p.pf_bytes - off < per ? p.pf_bytes - off : per;
+        for (unsigned long long o = 0; o < n; o += 4096ull)
+          l2_prefetch_bulk(p.pf_ptr + off + o, uint32_t(n - o < 4096ull ? n - o : 4096ull));
+      }
     }
     if (*abortp) {
       // gave up: let the copies already in flight land before this CTA's memory goes away

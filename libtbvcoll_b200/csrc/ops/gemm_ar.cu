@@ -251,6 +251,7 @@ static int launch_fused(tbv_comm* c, const void* const* ws, const void* const* x
   p.kb_total = (k_local + 63) / 64;
   p.limit_ns = 2000000000ull;
   p.err = tbvops::gemm_err_flag();
+  p.pf_bytes = tbvops::take_next_prefetch(&p.pf_ptr, (unsigned long long)hidden * (unsigned long long)k_local * 2ull);
   const size_t smem = size_t(stages) * (gemm::kATileBytes + bn * 128) + 1024;
   if (!g_attr_done) {
     if (cudaFuncSetAttribute(k_gemm_ar_rmsnorm, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) return TBV_FAIL;

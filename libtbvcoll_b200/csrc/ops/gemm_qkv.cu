@@ -193,6 +193,8 @@ bool g_attr = false;
 extern "C" int tbv_op_gemm_qkv_rope(const void* w, const void* x, void* qkv, const void* bias, int M, int N, int K, int ldx, int ldy,
                                     const void* positions, const void* cos_sin, const void* slot_mapping, void* k_cache, void* v_cache,
                                     int nq, int nkv, int max_pos, int splits_hint, void* stream) {
+  const char* pf_ptr = nullptr;   // an announcement holds for exactly one launch
+  const unsigned long long pf_bytes = tbvops::take_next_prefetch(&pf_ptr, (unsigned long long)(M > 0 ? M : 0) * (unsigned long long)(K > 0 ? K : 0) * 2ull);
   if (M != (nq + 2 * nkv) * 128 || N <= 0 || (K % 8) || (ldx % 8) || (ldy % 8)) return -2;
   int bn, splits, stages;
   tbvops::gemm_config(M, N, K, splits_hint, &bn, &splits, &stages);
@@ -206,6 +208,8 @@ extern "C" int tbv_op_gemm_qkv_rope(const void* w, const void* x, void* qkv, con
   p.y = static_cast<__nv_bfloat16*>(qkv);
   p.limit_ns = 2000000000ull;
   p.err = tbvops::gemm_err_flag();
+  p.pf_ptr = pf_ptr;
+  p.pf_bytes = pf_bytes;
   RopeArgs ra{static_cast<const int*>(positions), static_cast<const float*>(cos_sin), static_cast<const long long*>(slot_mapping),
               static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), nq, nkv, max_pos};
   if (!g_attr) {

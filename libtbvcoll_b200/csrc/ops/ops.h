@@ -6,6 +6,11 @@ namespace tbvops {
 int make_tensor_map_bf16(CUtensorMap* out, const void* ptr, unsigned long long rows, unsigned long long cols,
                          unsigned long long ld, unsigned box_rows, bool cache = true);
 int* gemm_err_flag();
+// The weights announced by tbv_op_gemm_prefetch_next for the next GEMM launch of this host thread: returns the byte count
+// (0 = none or `own_bytes`, the launch's own weight matrix, too small to give cover; capped by TBV_L2_PREFETCH_MB) and forgets
+// the announcement.
+unsigned long long take_next_prefetch(const char** ptr, unsigned long long own_bytes);
+void set_next_prefetch(const void* ptr, unsigned long long bytes);
 int sm_count();
 void gemm_config(int M, int N, int K, int splits_hint, int* bn_out, int* splits_out, int* stages_out);
 // many-token (prefill) persistent kernel, gemm_persist.cu

@@ -174,6 +174,10 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
   asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
   return v;
 }
+// Ask the memory system to bring `bytes` (a multiple of 16, from a 16-byte aligned address) into L2; nothing waits for it.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
 // The float4 at shared-memory address `local_addr` of CTAs 0 .. S-1 of the cluster, added in CTA order (S <= 8).
 // Every load is issued before the first value is used: one distributed-shared-memory round trip, not S.
 __device__ __forceinline__ float4 dsmem_sum_f32x4(uint32_t local_addr, int S) {

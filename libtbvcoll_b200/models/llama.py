@@ -20,6 +20,7 @@ All buffers are preallocated so a decode step can be captured in a CUDA graph.
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Optional
 
 import torch
@@ -60,6 +61,10 @@ class LlamaTP:
         self.cand_all = torch.zeros(tp.world, rec, dtype=torch.uint8, device=dev)
         self.cos_sin = ops.rope_cos_sin(self.D, cfg.max_position, cfg.rope_theta, dev, cfg.rope_scaling)
         self.scale = 1.0 / math.sqrt(self.D)
+        # Decode GEMMs may announce the next GEMM's weights (forward).  Edges: bit 0 qkv -> o_proj, 1 o_proj -> gate_up,
+        # 2 gate_up -> down, 3 down -> next layer's qkv (or the LM head).  Measured one edge at a time on the 8B shape: only
+        # o_proj -> gate_up pays (-3.0 % of the step at TP=1, -2.0 % at TP=2 shapes); the others are neutral or cost 0.5-1.7 %.
+        self.l2_prefetch = 0 if os.environ.get("TBV_L2_PREFETCH", "1") == "0" else int(os.environ.get("TBV_L2_PREFETCH_EDGES", "2"))
         # paged KV cache, one pair per layer: [num_blocks * block_size, nkv, D]
         self.k_cache = [torch.zeros(num_blocks * block_size, self.nkv, self.D, dtype=bf, device=dev) for _ in range(cfg.num_layers)]
         self.v_cache = [torch.zeros(num_blocks * block_size, self.nkv, self.D, dtype=bf, device=dev) for _ in range(cfg.num_layers)]
@@ -85,9 +90,14 @@ class LlamaTP:
             ops.embedding(ids, w["embed"], vocab_start=tp.rank * self.vpr, out=h)
             tp.all_reduce(h)
             ops.rmsnorm(h, w["layers.0.input_norm"], cfg.rms_eps, out=xn)
+        # Decode: every GEMM asks for the NEXT GEMM's weights to be brought into L2 while its own epilogue, the kernel
+        # boundary and the attention / all-reduce kernel in between would leave HBM idle (ops.prefetch_next).
+        pf = self.l2_prefetch if T <= 64 else 0
         for l in range(layer_begin, layer_end):
             p = f"layers.{l}."
             # qkv projection; RoPE and the KV-cache write happen in its epilogue
+            if pf & 1:
+                ops.prefetch_next(w[p + "o.weight"])
             ops.gemm_qkv_rope(xn, w[p + "qkv.weight"], qkv, positions, self.cos_sin, slot_mapping, self.k_cache[l], self.v_cache[l],
                               self.nq, self.nkv, bias=w.get(p + "qkv.bias"))
             if prefill_tiles is not None:
@@ -96,9 +106,15 @@ class LlamaTP:
             else:
                 ops.paged_attention(q_view, self.k_cache[l], self.v_cache[l], block_tables, ctx_lens, attn_view, self.scale,
                                     self.block_size, seq_of_query=seq_of_query, splits=attn_splits, workspace=self.attn_ws)
+            if pf & 2:
+                ops.prefetch_next(w[p + "gate_up.weight"])
             tp.gemm_all_reduce_add_rmsnorm(attn, w[p + "o.weight"], h, w[p + "post_norm"], cfg.rms_eps, out=part)   # part := norm(h), h += sum
+            if pf & 4:
+                ops.prefetch_next(w[p + "down.weight"])
             ops.gemm(part, w[p + "gate_up.weight"], out=act, epi=ops.EPI_SILU_MUL)
             nxt = w[f"layers.{l + 1}.input_norm"] if l + 1 < cfg.num_layers else w["norm"]
+            if pf & 8:
+                ops.prefetch_next(w[f"layers.{l + 1}.qkv.weight"] if l + 1 < cfg.num_layers else w["lm_head"])
             tp.gemm_all_reduce_add_rmsnorm(act, w[p + "down.weight"], h, nxt, cfg.rms_eps, out=xn)                  # xn := norm(h) for the next layer
         if layer_end < cfg.num_layers:
             return None

@@ -53,6 +53,8 @@ def lib():
     l.tbv_op_argmax_merge.argtypes = [c_vp, c_vp, I, I, LL, c_vp, c_vp]
     l.tbv_op_decode_advance.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, c_vp, c_vp, I, c_vp]
     l.tbv_op_decode_advance.restype = I
+    l.tbv_op_gemm_prefetch_next.argtypes = [c_vp, ctypes.c_size_t]
+    l.tbv_op_gemm_prefetch_next.restype = None
     l.tbv_op_copy_async.argtypes = [c_vp, c_vp, ctypes.c_size_t, c_vp]
     l.tbv_op_copy_async.restype = I
     l.tbv_op_prefill_attention.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, I, I, I, I, I, I, I, I, F, c_vp]
@@ -270,6 +272,15 @@ def decode_advance(next_ids, ids, positions, ctx_lens, slot_mapping, block_table
                                      block_tables.shape[1], block_size, B, _p(history), _p(step_counter),
                                      history.shape[0] if history is not None else 0, _st()), "tbv_op_decode_advance")
     _count()
+
+
+def prefetch_next(w: Optional[torch.Tensor]) -> None:
+    """Announce the weight matrix of the GEMM that will run AFTER the next ``gemm`` / ``gemm_qkv_rope`` call: the CTAs of
+    that next call ask for it (up to TBV_L2_PREFETCH_MB, default 32 MB) to be brought into L2 once their own weight
+    tiles are requested, so that HBM keeps streaming through the epilogue, the kernel boundary and whatever small kernel
+    runs in between.  Holds for one launch; decode-size kernels only (the many-token kernels ignore it)."""
+    if w is not None:
+        lib().tbv_op_gemm_prefetch_next(_p(w), w.numel() * w.element_size())
 
 
 def copy_async(dst: torch.Tensor, src: torch.Tensor) -> None:

@@ -326,3 +326,26 @@ def test_prefill_attention_query_tiled(ops, nq, nkv):
         assert (out[r0:r0 + n].float() - ref_o).abs().max().item() < 2e-2
         r0 += n
     assert (out.float() - want.float()).abs().max().item() < 2e-2
+
+
+def test_gemm_announcing_the_next_weights_changes_nothing_but_timing():
+    """ops.prefetch_next(w2) before a GEMM only asks for w2 to be brought into L2: same bits with and without, for the
+    plain, the SiLU-mul and the QKV + RoPE kernels, with sizes that are no multiple of the prefetch chunk; an
+    announcement holds for one launch."""
+    from libtbvcoll_b200 import ops
+    torch.manual_seed(7)
+    x = (torch.randn(8, 4096, device=DEV) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(2048, 4096, device=DEV) * 0.02).to(torch.bfloat16)      # 16 MB: above the default "own weights" threshold
+    big = torch.empty(100 * 1024 * 1024 + 4112, dtype=torch.uint8, device=DEV)      # more than the cap, odd tail
+    nxt = [big, big[16:16 + 1000 * 16], torch.empty(24, dtype=torch.bfloat16, device=DEV), big[: 3 * 4096 + 16]]
+    want = ops.gemm(x, w)
+    for t in nxt:
+        ops.prefetch_next(t)
+        got = ops.gemm(x, w)
+        assert torch.equal(got, want)
+    wg = (torch.randn(2048, 4096, device=DEV) * 0.02).to(torch.bfloat16)
+    want_g = ops.gemm(x, wg, epi=ops.EPI_SILU_MUL)
+    ops.prefetch_next(big)
+    assert torch.equal(ops.gemm(x, wg, epi=ops.EPI_SILU_MUL), want_g)
+    assert torch.equal(ops.gemm(x, w), want)          # no announcement pending: the plain launch again
+    torch.cuda.synchronize()
