@@ -70,23 +70,11 @@ def graph_us(fn, inner, world):
     return float(t[0])
 
 
-def trace_breakdown(comm, calls=256):
-    """Where the device time of the last `calls` collectives went, from every rank's own time stamps
-    (Comm.trace: kernel entry, own payload issued, every source's payload seen, kernel done; channel 0).
-    The GPUs' timers are not synchronised, so only differences taken on one rank are used; ranks are then
-    compared call by call.  The rank that waited least after its own push was the last to push: its wait is
-    the flight + poll time of the exchange, and the spread between ranks is their arrival skew.  All in us."""
-    rows = comm.trace(0, 1024)[-calls:]
-    n = torch.tensor([len(rows)], dtype=torch.int64, device="cuda")
-    dist.all_reduce(n, op=dist.ReduceOp.MIN)
-    n = int(n)
-    if n < 2:
-        return None
-    mine = torch.tensor(rows[-n:], dtype=torch.int64, device="cuda")
-    world = dist.get_world_size()
-    every = torch.empty((world, n, 5), dtype=torch.int64, device="cuda")
-    dist.all_gather_into_tensor(every, mine)
-    if not bool((every[:, :, 0] == every[0:1, :, 0]).all()):
+def phase_stats(every: torch.Tensor):
+    """The arithmetic of ``trace_breakdown``: ``every`` is int64 [ranks, calls, 5] of (seq, t_enter, t_pushed, t_ready, t_done)
+    in ns, each rank's stamps from its own timer.  Returns the per-phase means in us, or None when the ranks hold different calls."""
+    n = every.shape[1]
+    if n < 2 or not bool((every[:, :, 0] == every[0:1, :, 0]).all()):
         return None                                   # ranks hold different calls: nothing to align
     t = every.double() * 1e-3
     enter, pushed, ready, done = t[:, :, 1], t[:, :, 2], t[:, :, 3], t[:, :, 4]
@@ -106,6 +94,25 @@ def trace_breakdown(comm, calls=256):
                     "wait_after_push_mean_rank": r2(wait.mean()),
                     "wait_after_push_most_waiting_rank": r2(wait.max(dim=0).values.mean())})
     return out
+
+
+def trace_breakdown(comm, calls=256):
+    """Where the device time of the last `calls` collectives went, from every rank's own time stamps
+    (Comm.trace: kernel entry, own payload issued, every source's payload seen, kernel done; channel 0).
+    The GPUs' timers are not synchronised, so only differences taken on one rank are used; ranks are then
+    compared call by call.  The rank that waited least after its own push was the last to push: its wait is
+    the flight + poll time of the exchange, and the spread between ranks is their arrival skew.  All in us."""
+    rows = comm.trace(0, 1024)[-calls:]
+    n = torch.tensor([len(rows)], dtype=torch.int64, device="cuda")
+    dist.all_reduce(n, op=dist.ReduceOp.MIN)
+    n = int(n)
+    if n < 2:
+        return None
+    mine = torch.tensor(rows[-n:], dtype=torch.int64, device="cuda")
+    world = dist.get_world_size()
+    every = torch.empty((world, n, 5), dtype=torch.int64, device="cuda")
+    dist.all_gather_into_tensor(every, mine)
+    return phase_stats(every)
 
 
 def main():
