@@ -1011,11 +1011,13 @@ static int gpu_ar_rmsnorm(tbv_comm* c, const void* const* xs, const void* const*
   cudaError_t e;
   const bool ll = (c->knobs.algo == TBV_ALGO_AUTO || c->knobs.algo == TBV_ALGO_LL) && nbytes * 2 <= c->ll_cap &&
                   long(nbytes) <= c->knobs.ll_max && hidden <= 8 * kLLNormVPT * 512;
-  // LL form: the CTAs of a cluster share a row so that no SM pushes (or pulls) more than about 28 KB of packets
+  // LL form: the CTAs of a cluster can share a row (TBV_LL_SPREAD = 2, 4, 8) so that no SM pushes or pulls a whole row's packets.
+  // Measured on 8 GPUs in the engine with 4 CTAs per row: the push takes 1.85 instead of 2.95 us, the cluster barrier of the norm
+  // costs 0.7 us, and the step is the same (1.700 vs 1.690 ms); so one CTA per row stays the default.
   int parts = 1;
   if (ll) {
     const int upr = hidden / 8;
-    int want = c->knobs.ll_spread > 0 ? c->knobs.ll_spread : int((size_t(c->world - 1) * upr * 32 + 28671) / 28672);
+    int want = c->knobs.ll_spread > 0 ? c->knobs.ll_spread : 1;
     if (c->local) want = std::min(want, std::max(1, maxchan));
     while (parts * 2 <= 8 && parts < want && upr % (parts * 2 * 32) == 0) parts *= 2;
     if (c->local) nchan = std::max(1, std::min(tokens, maxchan / parts));

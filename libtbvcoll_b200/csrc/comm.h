@@ -37,7 +37,7 @@ struct Knobs {
   long ll_max = -1;              // TBV_LL_MAX: largest message that uses flag-in-payload (LL) packets (-1: by world size)
   int ll_wide = 1;               // TBV_LL_WIDE: LL packets as one 32-byte store / load per unit (0 = two 16-byte ones)
   int streamwait = 0;            // TBV_STREAMWAIT: 1 = host-driven debug mode, the stream waits for the peers' flags (wait-value operations)
-  int ll_spread = 0;             // TBV_LL_SPREAD: CTAs (a cluster) that share one row in the LL all-reduce + norm (0 = from world size and row length)
+  int ll_spread = 0;             // TBV_LL_SPREAD: CTAs (a cluster) that share one row in the LL all-reduce + norm (0 or 1 = one CTA per row, the default)
   int ll_threads = 0;            // TBV_LL_THREADS: threads per CTA of the plain LL all-reduce (fewer threads = more SMs pushing; 0 = from world size)
   long nvls_min = 0x7fffffffffffffffl;  // TBV_NVLS_MIN: smallest message for the switch-reduced kernel in auto mode
   long nvls_direct_max = 1l << 20;      // TBV_NVLS_DIRECT_MAX: up to here the switch-reduced kernel has every rank reduce the whole tensor (one pass)

@@ -45,7 +45,7 @@ def test_exact_all_dtypes_sizes(world, algo):
         c.destroy()
 
 
-@pytest.mark.parametrize("wide,spread,threads", [("1", "0", "0"), ("0", "0", "0"), ("1", "1", "512"), ("1", "2", "64"), ("1", "8", "128")])
+@pytest.mark.parametrize("wide,spread,threads", [("1", "0", "0"), ("0", "0", "0"), ("1", "4", "512"), ("1", "2", "64"), ("1", "8", "128")])
 def test_ll_packet_width_row_sharing_and_call_trace(monkeypatch, wide, spread, threads):
     """LL packets as one 32-byte store / load per unit (the default) or as two 16-byte ones, a row of the fused
     residual + norm shared by a cluster of 1 / 2 / 4 / 8 CTAs, the plain LL kernel with 64 - 512 threads per CTA:
