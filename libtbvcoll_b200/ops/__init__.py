@@ -278,7 +278,8 @@ def prefetch_next(w: Optional[torch.Tensor]) -> None:
     """Announce the weight matrix of the GEMM that will run AFTER the next ``gemm`` / ``gemm_qkv_rope`` call: the CTAs of
     that next call ask for it (up to TBV_L2_PREFETCH_MB, default 32 MB) to be brought into L2 once their own weight
     tiles are requested, so that HBM keeps streaming through the epilogue, the kernel boundary and whatever small kernel
-    runs in between.  Holds for one launch; decode-size kernels only (the many-token kernels ignore it)."""
+    runs in between.  Holds for one launch; decode-size kernels only (the many-token kernels ignore it).  ``w`` is read
+    by that launch: it must stay allocated until the launch has run (a weight, not a temporary)."""
     if w is not None:
         lib().tbv_op_gemm_prefetch_next(_p(w), w.numel() * w.element_size())
 
