@@ -12,7 +12,9 @@ def test_reference_symbols_are_exported():
                  "tbv_ar_init_n", "tbv_ar_cap64", "tbv_ar_sync", "tbv_comm_create", "tbv_comm_create_local", "tbv_comm_allreduce",
                  "tbv_comm_allreduce_rmsnorm", "tbv_comm_gemm_allreduce_rmsnorm", "tbv_comm_gemm_reduce_scatter",
                  "tbv_comm_allgather_gemm", "tbv_comm_reduce_scatter", "tbv_comm_all_gather", "tbv_op_gemm", "tbv_op_gemm_qkv_rope",
-                 "tbv_op_paged_attention", "tbv_op_prefill_attention", "tbv_op_rmsnorm", "tbv_op_argmax", "tbv_op_argmax_noalloc"):
+                 "tbv_op_paged_attention", "tbv_op_prefill_attention", "tbv_op_rmsnorm", "tbv_op_argmax", "tbv_op_argmax_noalloc",
+                 "tbv_comm_trace", "tbv_comm_timestamps", "tbv_comm_mute_rank", "tbv_comm_tag_counts", "tbv_op_gemm_prefetch_next",
+                 "tbv_op_copy_async"):
         assert isinstance(getattr(l, name), ctypes._CFuncPtr), name
 
 
